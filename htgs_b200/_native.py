@@ -1,0 +1,156 @@
+"""ctypes binding of libhtgs_b200.so (the C-ABI declared in include/htgs_b200.h).
+
+The library is the product: there is no CPU or PyTorch fallback.  Importing this
+module without the built library, or using it without a B200, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Dict, Optional
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libhtgs_b200.so")
+
+HTGS_OK = 0
+HTGS_ERR_INVALID_ARGUMENT = 1
+HTGS_ERR_UNSUPPORTED_MODE = 2
+HTGS_ERR_WORKSPACE_TOO_SMALL = 3
+HTGS_ERR_CUDA = 4
+HTGS_ERR_DEVICE_FLAG = 5
+
+
+class HtgsScene(ctypes.Structure):
+    _fields_ = [
+        ("positions", ctypes.c_void_p), ("scales", ctypes.c_void_p), ("rotations", ctypes.c_void_p),
+        ("opacities", ctypes.c_void_p), ("sh_0", ctypes.c_void_p), ("sh_rest", ctypes.c_void_p),
+        ("n_primitives", ctypes.c_int32), ("total_sh_bases", ctypes.c_int32),
+    ]
+
+
+class HtgsView(ctypes.Structure):
+    _fields_ = [
+        ("M", ctypes.c_void_p), ("VPM", ctypes.c_void_p), ("cam_position", ctypes.c_void_p),
+        ("mode", ctypes.c_int32), ("K", ctypes.c_int32), ("active_sh_bases", ctypes.c_int32),
+        ("width", ctypes.c_int32), ("height", ctypes.c_int32),
+        ("near_plane", ctypes.c_float), ("far_plane", ctypes.c_float), ("scale_modifier", ctypes.c_float),
+    ]
+
+
+class HtgsFrameInfo(ctypes.Structure):
+    _fields_ = [
+        ("n_instances", ctypes.c_uint32), ("n_visible", ctypes.c_uint32), ("key_bytes", ctypes.c_uint32),
+        ("end_bit", ctypes.c_uint32), ("reruns", ctypes.c_uint32), ("device_error", ctypes.c_uint32),
+        ("workspace_bytes", ctypes.c_uint64),
+    ]
+
+
+class HtgsIntermediates(ctypes.Structure):
+    _fields_ = [
+        ("n_touched", ctypes.c_void_p), ("bounds", ctypes.c_void_p), ("eval_records", ctypes.c_void_p),
+        ("cull_records", ctypes.c_void_p), ("keys_unsorted", ctypes.c_void_p), ("prims_unsorted", ctypes.c_void_p),
+        ("keys_sorted", ctypes.c_void_p), ("prims_sorted", ctypes.c_void_p), ("tile_ranges", ctypes.c_void_p),
+        ("n_tiles", ctypes.c_uint32), ("grid_width", ctypes.c_uint32), ("grid_height", ctypes.c_uint32),
+        ("key_bytes", ctypes.c_uint32),
+    ]
+
+
+class HtgsTrainState(ctypes.Structure):
+    _fields_ = [
+        ("per_primitive", ctypes.c_void_p), ("per_primitive_bytes", ctypes.c_size_t),
+        ("per_tile", ctypes.c_void_p), ("per_tile_bytes", ctypes.c_size_t),
+        ("per_instance", ctypes.c_void_p), ("per_instance_bytes", ctypes.c_size_t),
+        ("per_pixel", ctypes.c_void_p), ("per_pixel_bytes", ctypes.c_size_t),
+    ]
+
+
+class HtgsGradients(ctypes.Structure):
+    _fields_ = [
+        ("grad_positions", ctypes.c_void_p), ("grad_scales", ctypes.c_void_p), ("grad_rotations", ctypes.c_void_p),
+        ("grad_opacities", ctypes.c_void_p), ("grad_sh_0", ctypes.c_void_p), ("grad_sh_rest", ctypes.c_void_p),
+        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+        ("densification_info", ctypes.c_void_p), ("densification_rows", ctypes.c_int32),
+    ]
+
+
+class HtgsError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(message)
+        self.code = code
+
+
+_lib = None
+_lib_lock = threading.Lock()
+
+
+def lib():
+    """Loads the shared library (once).  Fails loudly if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lib_lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise ImportError(
+                        f"{LIB_PATH} is missing: build it with `python -m htgs_b200.build` (needs nvcc). "
+                        "htgs_b200 has no CPU or PyTorch fallback.")
+                l = ctypes.CDLL(LIB_PATH)
+                l.htgs_create.restype = ctypes.c_void_p
+                l.htgs_create.argtypes = [ctypes.c_int]
+                l.htgs_destroy.argtypes = [ctypes.c_void_p]
+                l.htgs_last_error.restype = ctypes.c_char_p
+                l.htgs_render_workspace_bytes.restype = ctypes.c_size_t
+                l.htgs_render_workspace_bytes.argtypes = [ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_uint64]
+                l.htgs_render.restype = ctypes.c_int
+                l.htgs_render.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
+                                          ctypes.POINTER(HtgsFrameInfo)]
+                l.htgs_render_host.restype = ctypes.c_int
+                l.htgs_render_host.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_void_p,
+                                               ctypes.c_int, ctypes.c_int, ctypes.POINTER(HtgsFrameInfo)]
+                l.htgs_get_intermediates.restype = ctypes.c_int
+                l.htgs_get_intermediates.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsIntermediates)]
+                l.htgs_memcpy_d2h.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+                l.htgs_memcpy_h2d.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+                _lib = l
+    return _lib
+
+
+def last_error() -> str:
+    msg = lib().htgs_last_error()
+    return msg.decode("utf-8", "replace") if msg else ""
+
+
+def check(code: int) -> None:
+    if code != HTGS_OK:
+        msg = last_error()
+        if code == HTGS_ERR_UNSUPPORTED_MODE:
+            raise RuntimeError(msg or "unsupported rasterizer mode")
+        raise HtgsError(code, f"htgs_b200 error {code}: {msg}")
+
+
+_contexts: Dict[int, int] = {}
+_ctx_lock = threading.Lock()
+
+
+def context(device_index: int) -> int:
+    """One library context per CUDA device of this process (created on first use)."""
+    ctx = _contexts.get(device_index)
+    if ctx is None:
+        with _ctx_lock:
+            ctx = _contexts.get(device_index)
+            if ctx is None:
+                ctx = lib().htgs_create(int(device_index))
+                if not ctx:
+                    raise RuntimeError(f"htgs_create({device_index}) failed: {last_error()}")
+                _contexts[device_index] = ctx
+    return ctx
+
+
+def exported_symbols():
+    """Names include/htgs_b200.h declares; used by the CPU-side test that the library exports them all."""
+    import re
+    header = os.path.join(os.path.dirname(_HERE), "include", "htgs_b200.h")
+    text = open(header).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(htgs_[a-z0-9_]+)\s*\(", text)))

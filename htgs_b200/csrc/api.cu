@@ -1,0 +1,332 @@
+// C-ABI layer: contexts, workspace carving and the stream-ordered frame drivers.
+// Host code only; the kernels live in preprocess.cu, binning.cu and blend.cu.
+//
+// A forward frame is: status reset -> preprocess -> scan of block sums -> instance
+// emission -> stable radix sort -> tile ranges -> blend -> asynchronous copy of the
+// 64-byte frame status to pinned host memory.  There is one host synchronisation, at
+// the end (the reference blocks in the middle of every frame to read the instance
+// count: rasterization/src/hybrid_blend/inference.cu:118-119).  The instance buffers are
+// sized speculatively; if a frame needs more, the kernels skip the instance stages, the
+// status says so, and the driver grows the workspace and runs the frame again.
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "kernels.h"
+
+using namespace htgs;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const std::string& msg) { g_last_error = msg; return code; }
+int fail_cuda(cudaError_t err, const char* what) {
+    g_last_error = std::string(what) + ": " + cudaGetErrorString(err);
+    return HTGS_ERR_CUDA;
+}
+
+constexpr size_t kAlign = 256;
+inline size_t align_up(size_t v) { return (v + kAlign - 1) & ~(kAlign - 1); }
+
+struct Carver {
+    unsigned char* base;
+    size_t offset = 0;
+    explicit Carver(void* b) : base(static_cast<unsigned char*>(b)) {}
+    template <typename T> T* take(size_t count) {
+        offset = align_up(offset);
+        T* p = base ? reinterpret_cast<T*>(base + offset) : nullptr;
+        offset += count * sizeof(T);
+        return p;
+    }
+    template <typename T> T* take_bytes(size_t bytes) {
+        offset = align_up(offset);
+        T* p = base ? reinterpret_cast<T*>(base + offset) : nullptr;
+        offset += bytes;
+        return p;
+    }
+};
+
+struct FrameLayout {
+    FrameStatus* status;
+    PrimBuffers prim;
+    InstBuffers inst;
+    uint2* tile_ranges;
+    size_t bytes;
+};
+
+FrameLayout carve_frame(void* blob, int n_primitives, int n_tiles, const SortPlan& plan, uint64_t instance_capacity, bool training) {
+    FrameLayout L{};
+    Carver c(blob);
+    const size_t n = size_t(n_primitives);
+    const size_t prim_blocks = (n + kPreprocessBlock - 1) / kPreprocessBlock;
+    L.status = c.take<FrameStatus>(1);
+    L.prim.n_touched = c.take<uint32_t>(n);
+    L.prim.bounds = c.take<ushort4>(n);
+    L.prim.eval = c.take<EvalRecord>(n);
+    L.prim.cull = c.take<CullRecord>(n);
+    L.prim.clamp = training ? c.take<uint8_t>(n) : nullptr;
+    L.prim.block_sums = c.take<uint32_t>(prim_blocks + 1);
+    L.prim.block_offsets = c.take<uint32_t>(prim_blocks + 1);
+    L.tile_ranges = c.take<uint2>(size_t(n_tiles));
+    const uint64_t cap = instance_capacity > 0xfffffff0ull ? 0xfffffff0ull : instance_capacity;
+    L.inst.capacity = uint32_t(cap);
+    L.inst.sort_blocks_cap = uint32_t((cap + kSortTile - 1) / kSortTile);
+    L.inst.keys[0] = c.take_bytes<void>(size_t(cap) * plan.key_bytes);
+    L.inst.keys[1] = c.take_bytes<void>(size_t(cap) * plan.key_bytes);
+    L.inst.prims[0] = c.take<uint32_t>(size_t(cap));
+    L.inst.prims[1] = c.take<uint32_t>(size_t(cap));
+    L.inst.radix_table = c.take<uint32_t>(size_t(kMaxRadixBins) * (L.inst.sort_blocks_cap + 1));
+    L.inst.digit_totals = c.take<uint32_t>(kMaxRadixBins);
+    L.bytes = align_up(c.offset);
+    return L;
+}
+
+int validate(const HtgsScene* scene, const HtgsView* view) {
+    if (!scene || !view) return fail(HTGS_ERR_INVALID_ARGUMENT, "scene and view must not be null");
+    if (view->mode < 0 || view->mode > 3) return fail(HTGS_ERR_UNSUPPORTED_MODE, "unsupported rasterizer mode");
+    if (scene->n_primitives < 0) return fail(HTGS_ERR_INVALID_ARGUMENT, "n_primitives must be >= 0");
+    if (view->width <= 0 || view->height <= 0) return fail(HTGS_ERR_INVALID_ARGUMENT, "width and height must be positive");
+    if (view->width > 65535 * 8 || view->height > 65535 * 8) return fail(HTGS_ERR_INVALID_ARGUMENT, "image too large for 16-bit tile coordinates");
+    if (scene->n_primitives > 0 && (!scene->positions || !scene->scales || !scene->rotations || !scene->opacities || !scene->sh_0))
+        return fail(HTGS_ERR_INVALID_ARGUMENT, "per-Gaussian input pointers must not be null");
+    if (scene->total_sh_bases < 0) return fail(HTGS_ERR_INVALID_ARGUMENT, "total_sh_bases must be >= 0");
+    const int a = view->active_sh_bases;
+    if (a != 1 && a != 4 && a != 9 && a != 16) return fail(HTGS_ERR_INVALID_ARGUMENT, "active_sh_bases must be 1, 4, 9 or 16");
+    if (a - 1 > scene->total_sh_bases) return fail(HTGS_ERR_INVALID_ARGUMENT, "active_sh_bases needs more coefficients than sh_rest holds");
+    if (a > 1 && !scene->sh_rest) return fail(HTGS_ERR_INVALID_ARGUMENT, "sh_rest must not be null when active_sh_bases > 1");
+    if (!view->M || !view->VPM || !view->cam_position) return fail(HTGS_ERR_INVALID_ARGUMENT, "camera pointers must not be null");
+    if ((view->mode == HTGS_MODE_HYBRID_BLEND || view->mode == HTGS_MODE_ALPHA_BLEND_FIRST_K) && view->K < 1)
+        return fail(HTGS_ERR_INVALID_ARGUMENT, "K must be >= 1");
+    return HTGS_OK;
+}
+
+}  // namespace
+
+struct HtgsContext {
+    int device = 0;
+    int sm_count = 0;
+    FrameStatus* host_status = nullptr;     // pinned
+    void* workspace = nullptr;              // internal grow-only workspace
+    size_t workspace_bytes = 0;
+    uint64_t instance_capacity = 0;         // capacity the internal workspace was last carved for
+    // staging buffers of htgs_render_host
+    void* host_path_buf = nullptr;
+    size_t host_path_bytes = 0;
+    cudaStream_t host_path_stream = nullptr;
+    // what the last frame used (htgs_get_intermediates)
+    FrameLayout last_layout{};
+    SortPlan last_plan{};
+    FrameGeometry last_geo{};
+    uint32_t last_n_instances = 0;
+    bool has_last = false;
+};
+
+extern "C" {
+
+int htgs_version(void) { return 100; }
+
+const char* htgs_last_error(void) { return g_last_error.c_str(); }
+
+HtgsContext* htgs_create(int device) {
+    int count = 0;
+    cudaError_t err = cudaGetDeviceCount(&count);
+    if (err != cudaSuccess || count == 0) { fail_cuda(err != cudaSuccess ? err : cudaErrorNoDevice, "htgs_create: no CUDA device"); return nullptr; }
+    if (device < 0 || device >= count) { fail(HTGS_ERR_INVALID_ARGUMENT, "htgs_create: bad device index"); return nullptr; }
+    if ((err = cudaSetDevice(device)) != cudaSuccess) { fail_cuda(err, "cudaSetDevice"); return nullptr; }
+    cudaDeviceProp prop;
+    if ((err = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) { fail_cuda(err, "cudaGetDeviceProperties"); return nullptr; }
+    if (prop.major != 10) { fail(HTGS_ERR_INVALID_ARGUMENT, "htgs_create: this library is built for sm_100a (B200) only"); return nullptr; }
+    HtgsContext* ctx = new HtgsContext();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if ((err = cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_status), sizeof(FrameStatus), cudaHostAllocDefault)) != cudaSuccess) {
+        fail_cuda(err, "cudaHostAlloc"); delete ctx; return nullptr;
+    }
+    std::memset(ctx->host_status, 0, sizeof(FrameStatus));
+    return ctx;
+}
+
+void htgs_destroy(HtgsContext* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->workspace) cudaFree(ctx->workspace);
+    if (ctx->host_path_buf) cudaFree(ctx->host_path_buf);
+    if (ctx->host_path_stream) cudaStreamDestroy(ctx->host_path_stream);
+    if (ctx->host_status) cudaFreeHost(ctx->host_status);
+    delete ctx;
+}
+
+size_t htgs_render_workspace_bytes(const HtgsScene* scene, const HtgsView* view, uint64_t instance_capacity) {
+    if (validate(scene, view) != HTGS_OK) return 0;
+    const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
+    const SortPlan plan = make_sort_plan(view->mode, geo.n_tiles);
+    return carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, instance_capacity, false).bytes;
+}
+
+static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const SortPlan& plan,
+                     const FrameLayout& L, const BlendOutputs& out, cudaStream_t stream) {
+    cudaError_t err;
+    if ((err = cudaMemsetAsync(L.status, 0, sizeof(FrameStatus), stream)) != cudaSuccess) return fail_cuda(err, "status reset");
+    if ((err = launch_preprocess(view.mode, false, scene, view, geo, L.prim, L.status, stream)) != cudaSuccess) return fail_cuda(err, "preprocess");
+    if ((err = launch_binning(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream)) != cudaSuccess) return fail_cuda(err, "binning");
+    const uint32_t* prims_sorted = L.inst.prims[plan.final_buffer];
+    if ((err = launch_blend_inference(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, out, L.status, ctx->sm_count, stream)) != cudaSuccess) return fail_cuda(err, "blend");
+    if ((err = cudaMemcpyAsync(ctx->host_status, L.status, sizeof(FrameStatus), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return fail_cuda(err, "status copy");
+    if ((err = cudaStreamSynchronize(stream)) != cudaSuccess) return fail_cuda(err, "frame synchronisation");
+    return HTGS_OK;
+}
+
+int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
+                int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    int rc = validate(scene, view);
+    if (rc != HTGS_OK) return rc;
+    if (!image || !depth) return fail(HTGS_ERR_INVALID_ARGUMENT, "image and depth must not be null");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    cudaError_t err;
+    int current = -1;
+    cudaGetDevice(&current);
+    if (current != ctx->device && (err = cudaSetDevice(ctx->device)) != cudaSuccess) return fail_cuda(err, "cudaSetDevice");
+
+    const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
+    const SortPlan plan = make_sort_plan(view->mode, geo.n_tiles);
+    const BlendOutputs out{image, depth, alpha, to_chw != 0, use_median_depth != 0};
+    const bool internal = workspace == nullptr;
+    uint32_t reruns = 0;
+
+    uint64_t capacity;
+    if (internal) {
+        capacity = ctx->instance_capacity ? ctx->instance_capacity : std::max<uint64_t>(uint64_t(scene->n_primitives) * 4, 1u << 20);
+    } else {
+        // largest capacity that fits the caller's workspace (the layout is monotone in capacity)
+        const size_t fixed = carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, 0, false).bytes;
+        if (workspace_bytes < fixed + 4096) {
+            if (info) { std::memset(info, 0, sizeof(*info)); info->workspace_bytes = fixed + 4096; }
+            return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "workspace too small for the per-Gaussian buffers");
+        }
+        const size_t per_inst = size_t(plan.key_bytes) * 2 + 8 + (size_t(kMaxRadixBins) * 4 + kSortTile - 1) / kSortTile;
+        capacity = (workspace_bytes - fixed - 8 * kAlign) / per_inst;
+        while (capacity > 0 && carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, capacity, false).bytes > workspace_bytes) capacity -= std::min<uint64_t>(capacity, 4096);
+    }
+
+    for (;;) {
+        FrameLayout L;
+        if (internal) {
+            const size_t need = carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, capacity, false).bytes;
+            if (need > ctx->workspace_bytes) {
+                if ((err = cudaStreamSynchronize(stream)) != cudaSuccess) return fail_cuda(err, "synchronise before growing the workspace");
+                if (ctx->workspace) cudaFree(ctx->workspace);
+                ctx->workspace = nullptr; ctx->workspace_bytes = 0;
+                const size_t grow = need + need / 8;
+                if ((err = cudaMalloc(&ctx->workspace, grow)) != cudaSuccess) return fail_cuda(err, "workspace allocation");
+                ctx->workspace_bytes = grow;
+            }
+            ctx->instance_capacity = capacity;
+            L = carve_frame(ctx->workspace, scene->n_primitives, geo.n_tiles, plan, capacity, false);
+        } else {
+            L = carve_frame(workspace, scene->n_primitives, geo.n_tiles, plan, capacity, false);
+        }
+        rc = run_frame(ctx, *scene, *view, geo, plan, L, out, stream);
+        if (rc != HTGS_OK) return rc;
+        const FrameStatus st = *ctx->host_status;
+        ctx->last_layout = L; ctx->last_plan = plan; ctx->last_geo = geo; ctx->last_n_instances = st.overflow ? 0 : st.n_instances; ctx->has_last = true;
+        const uint64_t needed_capacity = uint64_t(st.n_instances) + uint64_t(st.n_instances) / 4 + 4096;
+        if (info) {
+            info->n_instances = st.n_instances; info->n_visible = st.n_visible; info->key_bytes = uint32_t(plan.key_bytes);
+            info->end_bit = uint32_t(plan.end_bit); info->reruns = reruns; info->device_error = st.error;
+            info->workspace_bytes = carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, st.overflow ? needed_capacity : capacity, false).bytes;
+        }
+        if (st.error) return fail(HTGS_ERR_DEVICE_FLAG, "a kernel reported an internal error (bounded wait gave up)");
+        if (!st.overflow) return HTGS_OK;
+        if (st.n_instances == 0xffffffffu) return fail(HTGS_ERR_INVALID_ARGUMENT, "instance count does not fit 32 bits");
+        if (!internal) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "workspace too small for the instance buffers of this frame");
+        capacity = needed_capacity;
+        ++reruns;
+        if (reruns > 2) return fail(HTGS_ERR_CUDA, "frame still overflows after growing the workspace");
+    }
+}
+
+int htgs_get_intermediates(HtgsContext* ctx, HtgsIntermediates* out) {
+    if (!ctx || !out) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    if (!ctx->has_last) return fail(HTGS_ERR_INVALID_ARGUMENT, "no frame has been rendered on this context");
+    const FrameLayout& L = ctx->last_layout;
+    const SortPlan& p = ctx->last_plan;
+    out->n_touched = L.prim.n_touched;
+    out->bounds = reinterpret_cast<const uint16_t*>(L.prim.bounds);
+    out->eval_records = L.prim.eval;
+    out->cull_records = L.prim.cull;
+    const int unsorted = (p.n_passes == 0) ? 0 : (p.final_buffer ^ (p.n_passes & 1));   // emission always writes buffer 0
+    out->keys_unsorted = (p.n_passes == 1 || p.n_passes == 0) ? L.inst.keys[unsorted] : nullptr;   // overwritten by later passes otherwise
+    out->prims_unsorted = (p.n_passes == 1 || p.n_passes == 0) ? L.inst.prims[unsorted] : nullptr;
+    out->keys_sorted = L.inst.keys[p.final_buffer];
+    out->prims_sorted = L.inst.prims[p.final_buffer];
+    out->tile_ranges = reinterpret_cast<const uint32_t*>(L.tile_ranges);
+    out->n_tiles = uint32_t(ctx->last_geo.n_tiles);
+    out->grid_width = uint32_t(ctx->last_geo.grid_w);
+    out->grid_height = uint32_t(ctx->last_geo.grid_h);
+    out->key_bytes = uint32_t(p.key_bytes);
+    return HTGS_OK;
+}
+
+int htgs_render_host(HtgsContext* ctx, const HtgsScene* hs, const HtgsView* hv, float* host_image, float* host_depth,
+                     int to_chw, int use_median_depth, HtgsFrameInfo* info) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    int rc = validate(hs, hv);
+    if (rc != HTGS_OK) return rc;
+    if (!host_image || !host_depth) return fail(HTGS_ERR_INVALID_ARGUMENT, "image and depth must not be null");
+    cudaError_t err;
+    if ((err = cudaSetDevice(ctx->device)) != cudaSuccess) return fail_cuda(err, "cudaSetDevice");
+    if (!ctx->host_path_stream && (err = cudaStreamCreateWithFlags(&ctx->host_path_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail_cuda(err, "cudaStreamCreate");
+    cudaStream_t stream = ctx->host_path_stream;
+    const size_t n = size_t(hs->n_primitives), B = size_t(hs->total_sh_bases), P = size_t(hv->width) * hv->height;
+    Carver c(nullptr);
+    c.take<float>(n * 3); c.take<float>(n * 3); c.take<float>(n * 4); c.take<float>(n); c.take<float>(n * 3); c.take<float>(n * B * 3);
+    c.take<float>(16); c.take<float>(16); c.take<float>(4); c.take<float>(P * 3); c.take<float>(P);
+    const size_t need = align_up(c.offset);
+    if (need > ctx->host_path_bytes) {
+        if (ctx->host_path_buf) cudaFree(ctx->host_path_buf);
+        ctx->host_path_buf = nullptr; ctx->host_path_bytes = 0;
+        if ((err = cudaMalloc(&ctx->host_path_buf, need)) != cudaSuccess) return fail_cuda(err, "device staging allocation");
+        ctx->host_path_bytes = need;
+    }
+    Carver d(ctx->host_path_buf);
+    float* positions = d.take<float>(n * 3); float* scales = d.take<float>(n * 3); float* rotations = d.take<float>(n * 4);
+    float* opacities = d.take<float>(n); float* sh_0 = d.take<float>(n * 3); float* sh_rest = d.take<float>(n * B * 3);
+    float* M = d.take<float>(16); float* VPM = d.take<float>(16); float* cam = d.take<float>(4);
+    float* image = d.take<float>(P * 3); float* depth = d.take<float>(P);
+    auto up = [&](float* dst, const float* src, size_t count) -> cudaError_t {
+        return count ? cudaMemcpyAsync(dst, src, count * sizeof(float), cudaMemcpyHostToDevice, stream) : cudaSuccess;
+    };
+    if ((err = up(positions, hs->positions, n * 3)) != cudaSuccess || (err = up(scales, hs->scales, n * 3)) != cudaSuccess ||
+        (err = up(rotations, hs->rotations, n * 4)) != cudaSuccess || (err = up(opacities, hs->opacities, n)) != cudaSuccess ||
+        (err = up(sh_0, hs->sh_0, n * 3)) != cudaSuccess || (err = up(sh_rest, hs->sh_rest, n * B * 3)) != cudaSuccess ||
+        (err = up(M, hv->M, 16)) != cudaSuccess || (err = up(VPM, hv->VPM, 16)) != cudaSuccess || (err = up(cam, hv->cam_position, 3)) != cudaSuccess)
+        return fail_cuda(err, "host to device copy");
+    HtgsScene ds = *hs;
+    ds.positions = positions; ds.scales = scales; ds.rotations = rotations; ds.opacities = opacities; ds.sh_0 = sh_0; ds.sh_rest = sh_rest;
+    HtgsView dv = *hv;
+    dv.M = M; dv.VPM = VPM; dv.cam_position = cam;
+    rc = htgs_render(ctx, &ds, &dv, image, depth, nullptr, to_chw, use_median_depth, nullptr, 0, stream, info);
+    if (rc != HTGS_OK) return rc;
+    if ((err = cudaMemcpyAsync(host_image, image, P * 3 * sizeof(float), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return fail_cuda(err, "image copy");
+    if ((err = cudaMemcpyAsync(host_depth, depth, P * sizeof(float), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return fail_cuda(err, "depth copy");
+    if ((err = cudaStreamSynchronize(stream)) != cudaSuccess) return fail_cuda(err, "synchronise");
+    return HTGS_OK;
+}
+
+int htgs_memcpy_d2h(void* host_dst, const void* device_src, size_t bytes) {
+    if (bytes == 0) return HTGS_OK;
+    const cudaError_t err = cudaMemcpy(host_dst, device_src, bytes, cudaMemcpyDeviceToHost);
+    return err == cudaSuccess ? HTGS_OK : fail_cuda(err, "cudaMemcpy D2H");
+}
+
+int htgs_memcpy_h2d(void* device_dst, const void* host_src, size_t bytes) {
+    if (bytes == 0) return HTGS_OK;
+    const cudaError_t err = cudaMemcpy(device_dst, host_src, bytes, cudaMemcpyHostToDevice);
+    return err == cudaSuccess ? HTGS_OK : fail_cuda(err, "cudaMemcpy H2D");
+}
+
+}  // extern "C"

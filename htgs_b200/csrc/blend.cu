@@ -1,0 +1,447 @@
+// Per-tile blend kernels (inference) for the four blend modes.
+//
+// Replaces blend_cu of the reference
+//   HYBRID_BLEND               rasterization/include/hybrid_blend/kernels/inference.cuh:78-216
+//   ALPHA_BLEND_FIRST_K        rasterization/include/alpha_blend_first_k/kernels/inference.cuh:79-208
+//   ALPHA_BLEND_GLOBAL_ORDERING rasterization/include/alpha_blend_global_ordering/kernels/inference.cuh:78-176
+//   OIT_BLEND                  rasterization/include/oit_blend/kernels/inference.cuh:78-177
+// The per-fragment arithmetic (planes through the pixel ray, rho^2, G, alpha, depth of the point
+// of maximum contribution) and every threshold decision are kept operation for operation, and each
+// pixel still sees its tile's instances in list order, so results match the reference.  How the
+// work is organised is different:
+//
+//  1. Staging.  One thread per instance of a batch loads the Gaussian's conservative screen-space
+//     outline (32 bytes), tests it against the pixel rectangle of every warp of the tile, and - if any
+//     warp can be touched - starts ONE 80-byte bulk asynchronous copy (TMA, cp.async.bulk) of the
+//     evaluation record into shared memory, completion tracked by an mbarrier.  Warp ballots turn the
+//     per-rectangle results into one bit mask per warp.
+//  2. Candidate pass (overlaps the copies in flight).  Each pixel walks only the set bits of its warp's
+//     mask and evaluates the 7-flop outline test; pixels that may be touched push the batch slot into a
+//     per-pixel FIFO in shared memory.  No divergence: the mask is warp-uniform.
+//  3. Exact pass.  After the mbarrier completes, every lane drains its own FIFO, so (almost) every
+//     iteration of every lane is an accepted fragment: the expensive part (IEEE divide, expf, depth,
+//     K-buffer insertion) runs converged instead of once per Gaussian per warp.
+//  4. K-buffer.  Registers hold only (depth, slot) pairs; the payloads live in a shared-memory pool of
+//     K+1 slots per pixel, so an insertion moves 2 registers per level instead of 5-6.  The buffer
+//     references K slots, one is free: a new fragment is written to the free slot, the insertion
+//     chain carries (depth, slot) pairs exactly like the reference's swap chain carries whole
+//     fragments, and the slot that falls out of the chain becomes the free one.
+#include "kernels.h"
+
+namespace htgs {
+
+namespace {
+
+template <int MODE> struct TileShape {
+    static constexpr int tw = ModeTraits<MODE>::tile_w, th = ModeTraits<MODE>::tile_h;
+    static constexpr int threads = tw * th;
+    static constexpr int warps = threads / 32;
+    static constexpr int rows_per_warp = 32 / tw;
+    static constexpr int batch = threads;            // instances staged per iteration (one per thread)
+    static constexpr int mask_words = batch / 32;
+    static constexpr int chunk_words = mask_words < 2 ? mask_words : 2;   // candidate/exact passes alternate every 64 instances
+    static constexpr int chunk = chunk_words * 32;
+};
+
+// minimum over the integer pixel rectangle [x0,x1]x[y0,y1] of q = a dx^2 + b2 dx dy + c dy^2 <= 1 ?
+__device__ __forceinline__ bool outline_touches_rect(const float4& c0, float cc, float x0, float x1, float y0, float y1) {
+    const float cx = c0.x, cy = c0.y, a = c0.z, b2 = c0.w;
+    if (!(fabsf(cx) <= FLT_MAX)) return false;          // "reject everything" record
+    if (a == 0.0f && cc == 0.0f) return true;           // "accept everything" record
+    const float dx0 = x0 - cx, dx1 = x1 - cx, dy0 = y0 - cy, dy1 = y1 - cy;
+    if (dx0 <= 0.0f && dx1 >= 0.0f && dy0 <= 0.0f && dy1 >= 0.0f) return true;
+    const float ky = -0.5f * b2 / cc, kx = -0.5f * b2 / a;
+    float qmin = FLT_MAX;
+    {
+        const float dy = fminf(fmaxf(ky * dx0, dy0), dy1);
+        qmin = fminf(qmin, dx0 * (a * dx0 + b2 * dy) + cc * dy * dy);
+    }
+    {
+        const float dy = fminf(fmaxf(ky * dx1, dy0), dy1);
+        qmin = fminf(qmin, dx1 * (a * dx1 + b2 * dy) + cc * dy * dy);
+    }
+    {
+        const float dx = fminf(fmaxf(kx * dy0, dx0), dx1);
+        qmin = fminf(qmin, dx * (a * dx + b2 * dy0) + cc * dy0 * dy0);
+    }
+    {
+        const float dx = fminf(fmaxf(kx * dy1, dx0), dx1);
+        qmin = fminf(qmin, dx * (a * dx + b2 * dy1) + cc * dy1 * dy1);
+    }
+    return qmin <= 1.0f;
+}
+
+template <int MODE, int K> struct SmemLayout {
+    using TS = TileShape<MODE>;
+    static constexpr bool has_kbuffer = (MODE == HTGS_MODE_HYBRID_BLEND || MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K);
+    static constexpr int pool_elem = (MODE == HTGS_MODE_HYBRID_BLEND) ? 16 : (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K ? 8 : 0);
+    static constexpr size_t eval_off = 0;
+    static constexpr size_t eval_bytes = size_t(TS::batch) * sizeof(EvalRecord);
+    static constexpr size_t cull4_off = eval_off + eval_bytes;
+    static constexpr size_t cull4_bytes = size_t(TS::batch) * 16;
+    static constexpr size_t cullc_off = cull4_off + cull4_bytes;
+    static constexpr size_t cullc_bytes = size_t(TS::batch) * 4;
+    static constexpr size_t prim_off = cullc_off + cullc_bytes;
+    static constexpr size_t prim_bytes = size_t(TS::batch) * 4;
+    static constexpr size_t mask_off = prim_off + prim_bytes;
+    static constexpr size_t mask_bytes = size_t(TS::warps) * TS::mask_words * 4;
+    static constexpr size_t bar_off = (mask_off + mask_bytes + 15) & ~size_t(15);
+    static constexpr size_t fifo_off = bar_off + 16;
+    static constexpr size_t fifo_bytes = size_t(TS::chunk) * TS::threads;      // u8 [slot][thread]
+    static constexpr size_t pool_off = (fifo_off + fifo_bytes + 15) & ~size_t(15);
+    static constexpr size_t pool_bytes = has_kbuffer ? size_t(K + 1) * TS::threads * pool_elem : 0;
+    static constexpr size_t total = pool_off + pool_bytes;
+};
+
+// The shared per-fragment front end (hybrid_blend/kernels/inference.cuh:137-148).
+struct FragmentFront {
+    float3 m, d;
+    float numerator_rho2, denominator;
+};
+__device__ __forceinline__ FragmentFront fragment_front(const float4& VPMT1, const float4& VPMT2, const float4& VPMT4, float pixel_x, float pixel_y) {
+    FragmentFront f;
+    const float4 plane_x_diag = VPMT1 - VPMT4 * pixel_x;
+    const float4 plane_y_diag = VPMT2 - VPMT4 * pixel_y;
+    const float3 plane_x_diag_normal = f3(plane_x_diag);
+    const float3 plane_y_diag_normal = f3(plane_y_diag);
+    f.m = plane_x_diag.w * plane_y_diag_normal - plane_x_diag_normal * plane_y_diag.w;
+    f.d = cross(plane_x_diag_normal, plane_y_diag_normal);
+    f.numerator_rho2 = dot(f.m, f.m);
+    f.denominator = dot(f.d, f.d);
+    return f;
+}
+
+template <int MODE, int K>
+__global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kernel(
+    const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
+    const CullRecord* __restrict__ cull, float* __restrict__ image, float* __restrict__ depth_out, float* __restrict__ alpha_out,
+    uint32_t width, uint32_t height, uint32_t grid_w, bool to_chw, bool use_median_depth, FrameStatus* status)
+{
+    using MT = ModeTraits<MODE>;
+    using TS = TileShape<MODE>;
+    using SL = SmemLayout<MODE, K>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    EvalRecord* s_eval = reinterpret_cast<EvalRecord*>(smem + SL::eval_off);
+    float4* s_cull4 = reinterpret_cast<float4*>(smem + SL::cull4_off);
+    float* s_cullc = reinterpret_cast<float*>(smem + SL::cullc_off);
+    uint32_t* s_prim = reinterpret_cast<uint32_t*>(smem + SL::prim_off);
+    uint32_t* s_mask = reinterpret_cast<uint32_t*>(smem + SL::mask_off);
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + SL::bar_off);
+    uint8_t* s_fifo = smem + SL::fifo_off;
+    (void)s_prim;
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t warp = tid >> 5, lane = tid & 31;
+    const uint32_t tile_x = blockIdx.x, tile_y = blockIdx.y;
+    const uint32_t px_i = tile_x * TS::tw + (tid % TS::tw);
+    const uint32_t py_i = tile_y * TS::th + (tid / TS::tw);
+    const bool inside = px_i < width && py_i < height;
+    const float pixel_x = __uint2float_rn(px_i);
+    const float pixel_y = __uint2float_rn(py_i);
+
+    if (tid == 0) { mbar_init(s_bar, TS::threads); mbar_fence_init(); }
+
+    // ---- per-pixel state -------------------------------------------------------------------
+    [[maybe_unused]] float kd[SL::has_kbuffer ? K : 1];
+    [[maybe_unused]] uint32_t ks[SL::has_kbuffer ? K : 1];
+    [[maybe_unused]] float4* pool4 = reinterpret_cast<float4*>(smem + SL::pool_off);
+    [[maybe_unused]] float2* pool2 = reinterpret_cast<float2*>(smem + SL::pool_off);
+    [[maybe_unused]] uint32_t free_slot = K;
+    if constexpr (SL::has_kbuffer) {
+        #pragma unroll
+        for (int k = 0; k < K; ++k) {
+            kd[k] = FLT_MAX; ks[k] = k;
+            if constexpr (MODE == HTGS_MODE_HYBRID_BLEND) pool4[k * TS::threads + tid] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            else pool2[k * TS::threads + tid] = make_float2(0.0f, __uint_as_float(0xffffffffu));
+        }
+    }
+    // HYBRID tail / OIT accumulators / GLOBAL_ORDERING running blend
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);   // HB: premultiplied tail rgba; OIT: alpha-weighted rgb,depth; GO: rgb, depth
+    float acc_depth = 0.0f;                              // HB: depth * alpha of the tail; OIT: alpha sum
+    float transmittance = 1.0f;                          // HB: tail; OIT / GO: pixel
+    bool done = !inside;
+
+    const uint2 range = tile_ranges[tile_y * grid_w + tile_x];
+    uint32_t phase = 0;
+    bool wait_failed = false;
+    __syncthreads();
+
+    for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += TS::batch) {
+        if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) {
+            if (__syncthreads_count(done) == TS::threads) break;
+        } else {
+            __syncthreads();
+        }
+        // ---- 1. staging: one instance per thread ------------------------------------------------
+        {
+            const uint32_t inst = batch_begin + tid;
+            bool keep_any = false;
+            uint32_t keep_bits = 0;
+            uint32_t g = 0;
+            if (inst < range.y) {
+                g = __ldg(prims_sorted + inst);
+                const float4 c0 = ldg4(reinterpret_cast<const float*>(cull + g));
+                const float cc = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
+                const float x0 = float(tile_x * TS::tw), x1 = float(tile_x * TS::tw + TS::tw - 1);
+                #pragma unroll
+                for (int r = 0; r < TS::warps; ++r) {
+                    const float y0 = float(tile_y * TS::th + r * TS::rows_per_warp);
+                    const float y1 = y0 + float(TS::rows_per_warp - 1);
+                    if (outline_touches_rect(c0, cc, x0, x1, y0, y1)) keep_bits |= 1u << r;
+                }
+                keep_any = keep_bits != 0;
+                s_cull4[tid] = c0;
+                s_cullc[tid] = cc;
+            }
+            if (keep_any) {
+                mbar_arrive_expect_tx(s_bar, uint32_t(sizeof(EvalRecord)));
+                bulk_copy_g2s(s_eval + tid, eval + g, uint32_t(sizeof(EvalRecord)), s_bar);
+                if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) s_prim[tid] = g;
+            } else {
+                mbar_arrive(s_bar);
+            }
+            #pragma unroll
+            for (int r = 0; r < TS::warps; ++r) {
+                const uint32_t m = __ballot_sync(0xffffffffu, (keep_bits >> r) & 1u);
+                if (lane == 0) s_mask[r * TS::mask_words + warp] = m;
+            }
+        }
+        __syncthreads();
+        bool copies_landed = false;
+        #pragma unroll 1
+        for (int chunk_word = 0; chunk_word < TS::mask_words; chunk_word += TS::chunk_words) {
+        // ---- 2. candidate pass: outline test per pixel, only over this warp's kept instances -----
+        uint32_t n_cand = 0;
+        if (!done) {
+            #pragma unroll
+            for (int wd = 0; wd < TS::chunk_words; ++wd) {
+                uint32_t m = s_mask[warp * TS::mask_words + chunk_word + wd];
+                while (m) {
+                    const uint32_t j = (chunk_word + wd) * 32 + (__ffs(m) - 1);
+                    m &= m - 1;
+                    const float4 c0 = s_cull4[j];
+                    const float cc = s_cullc[j];
+                    const float dx = pixel_x - c0.x, dy = pixel_y - c0.y;
+                    const float q = dx * (c0.z * dx + c0.w * dy) + cc * dy * dy;
+                    if (q <= 1.0f) { s_fifo[n_cand * TS::threads + tid] = uint8_t(j); ++n_cand; }
+                }
+            }
+        }
+        // ---- 3. exact pass ------------------------------------------------------------------------
+        if (!copies_landed) {
+            if (!mbar_wait_bounded(s_bar, phase)) wait_failed = true;
+            phase ^= 1;
+            copies_landed = true;
+        }
+        const uint32_t n_iter = __reduce_max_sync(0xffffffffu, n_cand);
+        for (uint32_t it = 0; it < n_iter; ++it) {
+            if (it >= n_cand || done) continue;
+            const uint32_t j = s_fifo[it * TS::threads + tid];
+            const float4* rec = reinterpret_cast<const float4*>(s_eval + j);
+            const FragmentFront fr = fragment_front(rec[0], rec[1], rec[2], pixel_x, pixel_y);
+            const float numerator_rho2 = fr.numerator_rho2;
+            const float denominator = fr.denominator;
+            if (numerator_rho2 > MT::max_cutoff_sq * denominator) continue;
+            const float denominator_rcp = 1.0f / denominator;
+
+            if constexpr (MODE == HTGS_MODE_HYBRID_BLEND) {
+                const float4 rgba_in = rec[4];
+                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
+                if (alpha < MT::min_alpha) continue;
+                const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
+                const float4 MT3 = rec[3];
+                float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
+                float4 frag = make_float4(rgba_in.x * alpha, rgba_in.y * alpha, rgba_in.z * alpha, alpha);
+                if (depth < kd[K - 1] && alpha >= MT::min_alpha_core) {
+                    pool4[free_slot * TS::threads + tid] = frag;
+                    uint32_t slot = free_slot;
+                    #pragma unroll
+                    for (int k = 0; k < K; ++k) {
+                        if (depth < kd[k]) {
+                            const float td = kd[k]; kd[k] = depth; depth = td;
+                            const uint32_t ts = ks[k]; ks[k] = slot; slot = ts;
+                        }
+                    }
+                    free_slot = slot;                                 // whatever fell out of the chain (a real fragment or an empty entry)
+                    frag = pool4[slot * TS::threads + tid];
+                }
+                acc += frag;
+                if (!use_median_depth) acc_depth += depth * frag.w;
+                transmittance *= 1.0f - frag.w;
+            } else if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) {
+                const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
+                const float4 MT3 = rec[3];
+                float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
+                if (depth >= kd[K - 1]) continue;
+                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                const float alpha = fminf(rec[4].w * G, kMaxFragmentAlpha);
+                if (alpha < MT::min_alpha) continue;
+                pool2[free_slot * TS::threads + tid] = make_float2(alpha, __uint_as_float(s_prim[j]));
+                uint32_t slot = free_slot;
+                #pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    if (depth < kd[k]) {
+                        const float td = kd[k]; kd[k] = depth; depth = td;
+                        const uint32_t ts = ks[k]; ks[k] = slot; slot = ts;
+                    }
+                }
+                free_slot = slot;
+            } else if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) {
+                const float4 rgba_in = rec[4];
+                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                const float opacity = rgba_in.w;
+                const float alpha = fminf(opacity * G, kMaxFragmentAlpha);
+                if (alpha < MT::min_alpha) continue;
+                const float blending_weight = transmittance * alpha;
+                acc.x += blending_weight * rgba_in.x; acc.y += blending_weight * rgba_in.y; acc.z += blending_weight * rgba_in.z;
+                const float depth = rec[3].w;
+                if (use_median_depth) acc.w = (transmittance > 0.5f) ? depth : acc.w;
+                else acc.w += blending_weight * depth;
+                transmittance *= 1.0f - alpha;
+                if (transmittance < kTransmittanceThreshold) done = true;
+            } else {   // OIT_BLEND
+                const float4 rgba_in = rec[4];
+                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
+                if (alpha < MT::min_alpha) continue;
+                const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
+                const float4 MT3 = rec[3];
+                const float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
+                acc += alpha * make_float4(rgba_in.x, rgba_in.y, rgba_in.z, depth);
+                acc_depth += alpha;
+                transmittance *= 1.0f - alpha;
+            }
+        }
+        }   // chunk loop
+    }
+
+    if (wait_failed) atomicOr(&status->error, 1u);
+    if (!inside) return;
+
+    // ---- compositing --------------------------------------------------------------------------------
+    float3 rgb_pixel = make_float3(0.0f, 0.0f, 0.0f);
+    float depth_pixel = 0.0f;
+    float alpha_pixel = 0.0f;
+    if constexpr (MODE == HTGS_MODE_HYBRID_BLEND) {
+        // hybrid_blend/kernels/inference.cuh:174-199
+        float transmittance_core = 1.0f;
+        #pragma unroll
+        for (int k = 0; k < K; ++k) {
+            if (transmittance_core >= kTransmittanceThreshold) {
+                const float4 rgba_premultiplied = pool4[ks[k] * TS::threads + tid];
+                rgb_pixel += transmittance_core * f3(rgba_premultiplied);
+                const float depth = kd[k];
+                if (use_median_depth) depth_pixel = (transmittance_core > 0.5f && depth < FLT_MAX) ? depth : depth_pixel;
+                else depth_pixel += transmittance_core * rgba_premultiplied.w * depth;
+                transmittance_core *= 1.0f - rgba_premultiplied.w;
+            }
+        }
+        float total_alpha = 1.0f - transmittance_core;
+        if (transmittance_core >= kTransmittanceThreshold && acc.w >= MT::min_alpha) {
+            const float weight_tail = transmittance_core * (1.0f - transmittance);
+            rgb_pixel += weight_tail * (1.0f / acc.w) * f3(acc);
+            if (!use_median_depth) depth_pixel += weight_tail * (1.0f / acc.w) * acc_depth;
+            total_alpha += weight_tail;
+        }
+        if (!use_median_depth) depth_pixel = (total_alpha > 0.0f) ? depth_pixel / total_alpha : 0.0f;
+        alpha_pixel = total_alpha;
+    } else if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) {
+        // alpha_blend_first_k/kernels/inference.cuh:172-191
+        float t = 1.0f;
+        bool stop = false;
+        #pragma unroll
+        for (int k = 0; k < K; ++k) {
+            if (!stop && t >= kTransmittanceThreshold) {
+                const float2 cell = pool2[ks[k] * TS::threads + tid];
+                const uint32_t primitive_idx = __float_as_uint(cell.y);
+                if (primitive_idx == 0xffffffffu) { stop = true; }
+                else {
+                    const float alpha = cell.x;
+                    const float blending_weight = t * alpha;
+                    const float4 rgba = ldg4(reinterpret_cast<const float*>(eval + primitive_idx) + 16);
+                    rgb_pixel += blending_weight * f3(rgba);
+                    const float depth = kd[k];
+                    if (use_median_depth) depth_pixel = (t > 0.5f) ? depth : depth_pixel;
+                    else depth_pixel += blending_weight * depth;
+                    t *= 1.0f - alpha;
+                }
+            }
+        }
+        if (!use_median_depth) depth_pixel = (t < 1.0f) ? depth_pixel / (1.0f - t) : 0.0f;
+        alpha_pixel = 1.0f - t;
+    } else if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) {
+        rgb_pixel = f3(acc);
+        depth_pixel = acc.w;
+        if (!use_median_depth) depth_pixel = (transmittance < 1.0f) ? depth_pixel / (1.0f - transmittance) : 0.0f;
+        alpha_pixel = 1.0f - transmittance;
+    } else {
+        // oit_blend/kernels/inference.cuh:150-160
+        float4 rgbd_pixel = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (acc_depth >= MT::min_alpha) {
+            const float alpha = 1.0f - transmittance;
+            rgbd_pixel = alpha * (1.0f / acc_depth) * acc;
+            rgbd_pixel.w = rgbd_pixel.w / alpha;
+            alpha_pixel = alpha;
+        }
+        rgb_pixel = f3(rgbd_pixel);
+        depth_pixel = rgbd_pixel.w;
+    }
+
+    const uint32_t pixel_idx = width * py_i + px_i;
+    if (to_chw) {
+        const uint32_t n_pixels = width * height;
+        image[pixel_idx] = __saturatef(rgb_pixel.x);
+        image[n_pixels + pixel_idx] = __saturatef(rgb_pixel.y);
+        image[2 * n_pixels + pixel_idx] = __saturatef(rgb_pixel.z);
+    } else {
+        const uint32_t base_idx = 3 * pixel_idx;
+        image[base_idx] = __saturatef(rgb_pixel.x);
+        image[base_idx + 1] = __saturatef(rgb_pixel.y);
+        image[base_idx + 2] = __saturatef(rgb_pixel.z);
+    }
+    depth_out[pixel_idx] = depth_pixel;
+    if (alpha_out) alpha_out[pixel_idx] = alpha_pixel;
+}
+
+template <int MODE, int K>
+cudaError_t launch_mode_k(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                          const BlendOutputs& out, FrameStatus* status, cudaStream_t stream) {
+    using SL = SmemLayout<MODE, K>;
+    auto kernel = blend_inference_kernel<MODE, K>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SL::total));
+    if (err != cudaSuccess) return err;
+    const dim3 grid(geo.grid_w, geo.grid_h, 1);
+    kernel<<<grid, TileShape<MODE>::threads, SL::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, out.image, out.depth, out.alpha,
+                                                                  uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), out.to_chw,
+                                                                  out.use_median_depth, status);
+    return cudaGetLastError();
+}
+
+// K is rounded down to a power of two <= 32 (hybrid_blend/inference.cu:15-28)
+template <int MODE>
+cudaError_t launch_mode(int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                        const BlendOutputs& out, FrameStatus* status, cudaStream_t stream) {
+    if (K >= 32) return launch_mode_k<MODE, 32>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+    if (K >= 16) return launch_mode_k<MODE, 16>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+    if (K >= 8) return launch_mode_k<MODE, 8>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+    if (K >= 4) return launch_mode_k<MODE, 4>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+    if (K >= 2) return launch_mode_k<MODE, 2>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+    return launch_mode_k<MODE, 1>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+}
+
+}  // namespace
+
+cudaError_t launch_blend_inference(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
+                                   const uint2* tile_ranges, const BlendOutputs& out, FrameStatus* status, int sm_count, cudaStream_t stream) {
+    (void)sm_count;
+    switch (mode) {
+        case HTGS_MODE_HYBRID_BLEND: return launch_mode<HTGS_MODE_HYBRID_BLEND>(K, geo, prim, prims_sorted, tile_ranges, out, status, stream);
+        case HTGS_MODE_ALPHA_BLEND_FIRST_K: return launch_mode<HTGS_MODE_ALPHA_BLEND_FIRST_K>(K, geo, prim, prims_sorted, tile_ranges, out, status, stream);
+        case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: return launch_mode_k<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING, 1>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+        case HTGS_MODE_OIT_BLEND: return launch_mode_k<HTGS_MODE_OIT_BLEND, 1>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace htgs

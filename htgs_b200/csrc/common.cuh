@@ -1,0 +1,167 @@
+// Shared declarations of the sm_100a rasterizer core: per-mode constants, the
+// device-side data layout, small vector algebra and PTX wrappers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cfloat>
+
+#include "../../include/htgs_b200.h"
+
+namespace htgs {
+
+// ---------------------------------------------------------------------------
+// per-mode numerical constants; they are part of the numerical contract with
+// the reference (rasterization/include/*/config.h:15-29)
+// ---------------------------------------------------------------------------
+constexpr float kTransmittanceThreshold = 1e-4f;
+constexpr float kMaxFragmentAlpha = 1.0f;
+constexpr float kOneMinusAlphaEps = 1e-8f;
+
+template <int MODE> struct ModeTraits;
+template <> struct ModeTraits<HTGS_MODE_HYBRID_BLEND> {
+    static constexpr int tile_w = 8, tile_h = 8;
+    static constexpr float min_alpha_rcp = 255.0f;
+    static constexpr float min_alpha = 1.0f / 255.0f;
+    static constexpr float max_cutoff_sq = 11.0825270903f;
+    static constexpr float min_alpha_core = 1.0f / 20.0f;
+};
+template <> struct ModeTraits<HTGS_MODE_ALPHA_BLEND_FIRST_K> {
+    static constexpr int tile_w = 8, tile_h = 8;
+    static constexpr float min_alpha_rcp = 20.0f;
+    static constexpr float min_alpha = 1.0f / 20.0f;
+    static constexpr float max_cutoff_sq = 5.99146454711f;
+    static constexpr float min_alpha_core = 0.0f;
+};
+template <> struct ModeTraits<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING> {
+    static constexpr int tile_w = 16, tile_h = 16;
+    static constexpr float min_alpha_rcp = 255.0f;
+    static constexpr float min_alpha = 1.0f / 255.0f;
+    static constexpr float max_cutoff_sq = 11.0825270903f;
+    static constexpr float min_alpha_core = 0.0f;
+};
+template <> struct ModeTraits<HTGS_MODE_OIT_BLEND> {
+    static constexpr int tile_w = 8, tile_h = 8;
+    static constexpr float min_alpha_rcp = 255.0f;
+    static constexpr float min_alpha = 1.0f / 255.0f;
+    static constexpr float max_cutoff_sq = 11.0825270903f;
+    static constexpr float min_alpha_core = 0.0f;
+};
+
+inline int mode_tile_w(int mode) { return mode == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING ? 16 : 8; }
+inline int mode_tile_h(int mode) { return mode == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING ? 16 : 8; }
+
+// ---------------------------------------------------------------------------
+// data layout in HBM
+// ---------------------------------------------------------------------------
+// What the blend kernels need to evaluate one Gaussian at a pixel: 80 bytes,
+// 16-byte aligned, so one record moves to shared memory with a single bulk
+// asynchronous copy.  Rows of the 3x4 matrices (VP*M*T) and (M*T) of the
+// reference (kernel_utils.cuh:98-123, hybrid_blend/kernels/inference.cuh:57-74).
+struct __align__(16) EvalRecord {
+    float4 vpmt1;
+    float4 vpmt2;
+    float4 vpmt4;
+    float4 mt3;    // .w = view-space depth of the centre
+    float4 rgba;   // view-dependent colour (clamped at 0), opacity
+};
+static_assert(sizeof(EvalRecord) == 80, "EvalRecord must be 80 bytes");
+
+// Conservative screen-space outline of the fragment-acceptance region
+// { pixel : alpha(pixel) >= min_alpha }, an ellipse
+//   a*dx^2 + b2*dx*dy + c*dy^2 <= 1,  (dx,dy) = pixel - (cx,cy),
+// computed in float64, inflated by a safety margin (see preprocess.cu).  It
+// has no counterpart in the reference; it only removes (pixel, Gaussian)
+// pairs that the exact per-fragment test would reject anyway.
+struct __align__(16) CullRecord {
+    float cx, cy;
+    float a, b2;
+    float c;
+    float pad0, pad1, pad2;
+};
+static_assert(sizeof(CullRecord) == 32, "CullRecord must be 32 bytes");
+
+// Device-resident frame status, copied to the host at the end of a call.
+struct FrameStatus {
+    unsigned int n_instances;     // total (tile, Gaussian) instances of the frame
+    unsigned int overflow;        // 1 if n_instances exceeded the instance capacity of the workspace
+    unsigned int n_visible;       // Gaussians that survived culling
+    unsigned int error;           // bounded waits that gave up, bad arguments seen on the device, ...
+    unsigned int reserved[12];
+};
+
+struct CameraParams {             // read from device memory at kernel start (re-entrant, no __constant__ upload)
+    const float* M;               // [4,4] world -> view, row-major (only row 2 is used)
+    const float* VPM;             // [4,4] world -> screen
+    const float* cam_position;    // [3]
+};
+
+// ---------------------------------------------------------------------------
+// vector algebra.  The expression shapes (association order of sums of
+// products) follow the helper the reference uses (utils/helper_math.h: dot
+// 1267-1274, cross 1451-1454, normalize 1328-1332), so that the compiler's
+// multiply-add contraction yields the same rounding as the reference build.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float3 f3(const float4& a) { return make_float3(a.x, a.y, a.z); }
+__device__ __forceinline__ float dot(const float3& a, const float3& b) { return a.x * b.x + a.y * b.y + a.z * b.z; }
+__device__ __forceinline__ float dot(const float4& a, const float4& b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+__device__ __forceinline__ float3 cross(const float3& a, const float3& b) {
+    return make_float3(a.y * b.z - a.z * b.y, a.z * b.x - a.x * b.z, a.x * b.y - a.y * b.x);
+}
+__device__ __forceinline__ float3 operator*(const float3& a, float s) { return make_float3(a.x * s, a.y * s, a.z * s); }
+__device__ __forceinline__ float3 operator*(float s, const float3& a) { return make_float3(s * a.x, s * a.y, s * a.z); }
+__device__ __forceinline__ float3 operator*(const float3& a, const float3& b) { return make_float3(a.x * b.x, a.y * b.y, a.z * b.z); }
+__device__ __forceinline__ float3 operator+(const float3& a, const float3& b) { return make_float3(a.x + b.x, a.y + b.y, a.z + b.z); }
+__device__ __forceinline__ float3 operator-(const float3& a, const float3& b) { return make_float3(a.x - b.x, a.y - b.y, a.z - b.z); }
+__device__ __forceinline__ float3 operator+(float s, const float3& a) { return make_float3(s + a.x, s + a.y, s + a.z); }
+__device__ __forceinline__ float3 operator-(const float3& a) { return make_float3(-a.x, -a.y, -a.z); }
+__device__ __forceinline__ void operator+=(float3& a, const float3& b) { a.x += b.x; a.y += b.y; a.z += b.z; }
+__device__ __forceinline__ float4 operator*(const float4& a, const float4& b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+__device__ __forceinline__ float4 operator*(const float4& a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
+__device__ __forceinline__ float4 operator*(float s, const float4& a) { return make_float4(s * a.x, s * a.y, s * a.z, s * a.w); }
+__device__ __forceinline__ float4 operator-(const float4& a, const float4& b) { return make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w); }
+__device__ __forceinline__ float4 operator+(const float4& a, const float4& b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ void operator+=(float4& a, const float4& b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+__device__ __forceinline__ float3 normalize(const float3& v) { const float inv_len = rsqrtf(dot(v, v)); return v * inv_len; }
+__device__ __forceinline__ float length(const float3& v) { return sqrtf(dot(v, v)); }
+
+__device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+
+// ---------------------------------------------------------------------------
+// PTX wrappers: mbarrier + bulk asynchronous copy (TMA, non-tensor, no multicast)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls and reports failure instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// global -> shared bulk copy; src/dst 16-byte aligned, bytes a multiple of 16; completion is
+// signalled on the mbarrier as transferred bytes.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ unsigned int lanemask_lt() { unsigned int m; asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m)); return m; }
+
+}  // namespace htgs

@@ -1,0 +1,257 @@
+// Per-Gaussian preprocess: exact perspective-correct screen bounds, ray-evaluation
+// setup, SH -> RGB, view depth, plus two things the reference does not have:
+// the per-block instance count (which replaces a separate prefix-sum pass over
+// all Gaussians) and a conservative screen-space ellipse used by the blend
+// kernels to skip (pixel, Gaussian) pairs the exact test would reject.
+//
+// Replaces the sixteen preprocess_cu variants of the reference
+// (rasterization/include/*/kernels/{forward,inference}.cuh:10-76) and the device helpers
+// transform_and_cull / convert_sh_to_rgb (rasterization/include/kernel_utils.cuh:63-188).
+// The float expression shapes of the bounds computation are kept as in the reference so
+// that tile boxes are bit-identical; everything around them is new.
+#include "kernels.h"
+
+namespace htgs {
+
+namespace {
+
+struct Mat3 { float r11, r12, r13, r21, r22, r23, r31, r32, r33; };
+
+// rasterization/include/kernel_utils.cuh:30-42.  The multiply-add contraction of every entry is
+// written out with intrinsics: it is the rounding the reference build (nvcc 12.9, sm_100a, default
+// -fmad) was measured to produce for each entry, and the compiler cannot re-associate intrinsics.
+__device__ __forceinline__ Mat3 quat_to_mat(const float4& q) {
+    const float r = q.x, x = q.y, y = q.z, z = q.w;
+    const float yy_zz = __fadd_rn(__fmul_rn(y, y), __fmul_rn(z, z));
+    const float xx_zz = __fmaf_rn(x, x, __fmul_rn(z, z));
+    const float xx_yy = __fmaf_rn(x, x, __fmul_rn(y, y));
+    const float rz = __fmul_rn(r, z), rx = __fmul_rn(r, x), xz = __fmul_rn(x, z);
+    return {__fmaf_rn(-2.0f, yy_zz, 1.0f), __fmul_rn(2.0f, __fmaf_rn(x, y, -rz)), __fmul_rn(2.0f, __fmaf_rn(r, y, xz)),
+            __fmul_rn(2.0f, __fmaf_rn(x, y, rz)), __fmaf_rn(-2.0f, xx_zz, 1.0f), __fmul_rn(2.0f, __fmaf_rn(y, z, -rx)),
+            __fmul_rn(2.0f, __fmaf_rn(-r, y, xz)), __fmul_rn(2.0f, __fmaf_rn(y, z, rx)), __fmaf_rn(-2.0f, xx_yy, 1.0f)};
+}
+
+// Rows of (VP*M*T) and (M*T): kernel_utils.cuh:102,111,119,123 and hybrid_blend/kernels/inference.cuh:61.
+// As for the rotation matrix, the contraction of each dot product is pinned to what the reference build
+// was measured to round like: x*x' fused into y*y', then z*z' fused on top - except the first component
+// of the rows built from VPM row 4 and M row 3, where y*y' is fused into x*x'.
+__device__ __forceinline__ float dot3_pinned(const float3& a, const float3& b) {
+    return __fmaf_rn(a.z, b.z, __fmaf_rn(a.x, b.x, __fmul_rn(a.y, b.y)));
+}
+__device__ __forceinline__ float dot3_pinned_alt(const float3& a, const float3& b) {
+    return __fmaf_rn(a.z, b.z, __fmaf_rn(a.y, b.y, __fmul_rn(a.x, b.x)));
+}
+template <bool ALT_FIRST>
+__device__ __forceinline__ float4 row_times_T(const float4& row, const float3& u, const float3& v, const float3& w, const float3& p) {
+    const float3 r = f3(row);
+    return make_float4(ALT_FIRST ? dot3_pinned_alt(r, u) : dot3_pinned(r, u), dot3_pinned(r, v), dot3_pinned(r, w), __fadd_rn(dot3_pinned(r, p), row.w));
+}
+
+// rasterization/include/kernel_utils.cuh:140-188
+template <bool TRAIN>
+__device__ __forceinline__ float3 sh_to_rgb(const float* __restrict__ sh_0, const float* __restrict__ sh_rest, const float3& position,
+                                            const float3& cam_position, uint32_t idx, int active_sh_bases, int total_sh_bases,
+                                            uint8_t* clamp_bits) {
+    const float3 dc = make_float3(__ldg(sh_0 + 3 * size_t(idx)), __ldg(sh_0 + 3 * size_t(idx) + 1), __ldg(sh_0 + 3 * size_t(idx) + 2));
+    float3 result = 0.5f + 0.28209479177387814f * dc;
+    if (active_sh_bases > 1) {
+        const float* c = sh_rest + size_t(idx) * size_t(total_sh_bases) * 3;
+        auto coef = [&](int i) { return make_float3(__ldg(c + 3 * i), __ldg(c + 3 * i + 1), __ldg(c + 3 * i + 2)); };
+        const float3 dir = normalize(position - cam_position);
+        const float x = dir.x, y = dir.y, z = dir.z;
+        result = result + (-0.48860251190291987f * y) * coef(0)
+                        + (0.48860251190291987f * z) * coef(1)
+                        + (-0.48860251190291987f * x) * coef(2);
+        if (active_sh_bases > 4) {
+            const float xx = x * x, yy = y * y, zz = z * z;
+            const float xy = x * y, xz = x * z, yz = y * z;
+            result = result + (1.0925484305920792f * xy) * coef(3)
+                            + (-1.0925484305920792f * yz) * coef(4)
+                            + (0.94617469575755997f * zz - 0.31539156525251999f) * coef(5)
+                            + (-1.0925484305920792f * xz) * coef(6)
+                            + (0.54627421529603959f * xx - 0.54627421529603959f * yy) * coef(7);
+            if (active_sh_bases > 9) {
+                result = result + (0.59004358992664352f * y * (-3.0f * xx + yy)) * coef(8)
+                                + (2.8906114426405538f * xy * z) * coef(9)
+                                + (0.45704579946446572f * y * (1.0f - 5.0f * zz)) * coef(10)
+                                + (0.3731763325901154f * z * (5.0f * zz - 3.0f)) * coef(11)
+                                + (0.45704579946446572f * x * (1.0f - 5.0f * zz)) * coef(12)
+                                + (1.4453057213202769f * z * (xx - yy)) * coef(13)
+                                + (0.59004358992664352f * x * (-xx + 3.0f * yy)) * coef(14);
+            }
+        }
+    }
+    if constexpr (TRAIN) {
+        *clamp_bits = uint8_t((result.x < 0 ? 1 : 0) | (result.y < 0 ? 2 : 0) | (result.z < 0 ? 4 : 0));
+    }
+    return make_float3(fmaxf(0.0f, result.x), fmaxf(0.0f, result.y), fmaxf(0.0f, result.z));
+}
+
+// Conservative outline of { pixel : the exact per-fragment test can accept }.
+//
+// A fragment is accepted only if rho^2 <= max_cutoff_sq and opacity * exp(-rho^2 / 2) >= min_alpha, i.e.
+// rho^2 <= L with L = min(max_cutoff_sq, 2 ln(opacity / min_alpha)).  rho^2(pixel) is the squared distance
+// (in the Gaussian's unit frame) of the pixel ray to the centre, so the accepted set is the projected outline
+// of the ellipsoid |q|^2 <= L: an ellipse whose dual conic is C_ab = L * sum_i T_a[i] T_b[i] - T_a[3] T_b[3]
+// (rows a,b of VP*M*T).  Centre and shape are evaluated in float64 from the float32 rows the blend kernels use;
+// the shape matrix is inflated by (0.3 px)^2 and the quadratic form relaxed by 2% to cover the float32
+// rounding of the exact per-fragment evaluation.  An outline that is not a proper ellipse disables culling
+// for the Gaussian ("accept everything"), and L <= 0 rejects everything.
+template <int MODE>
+__device__ __forceinline__ CullRecord make_cull_record(const float4& t1, const float4& t2, const float4& t4, float opacity) {
+    using MT = ModeTraits<MODE>;
+    CullRecord rec = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};   // a = b2 = c = 0: every pixel passes
+    const double level = fmin(double(MT::max_cutoff_sq), 2.0 * log(double(opacity) * double(MT::min_alpha_rcp))) * 1.001 + 1e-4;
+    if (!(level > 0.0)) { rec.cx = __int_as_float(0x7f800000); return rec; }   // +inf: every comparison fails, nothing passes
+    auto conic = [&](const float4& a, const float4& b) {
+        return level * (double(a.x) * double(b.x) + double(a.y) * double(b.y) + double(a.z) * double(b.z)) - double(a.w) * double(b.w);
+    };
+    const double c44 = conic(t4, t4);
+    if (c44 == 0.0) return rec;
+    const double inv = 1.0 / c44;
+    const double cx = conic(t1, t4) * inv, cy = conic(t2, t4) * inv;
+    double sxx = cx * cx - conic(t1, t1) * inv;
+    double syy = cy * cy - conic(t2, t2) * inv;
+    const double sxy = cx * cy - conic(t1, t2) * inv;
+    if (!(sxx > 0.0) || !(syy > 0.0)) return rec;
+    const double det0 = sxx * syy - sxy * sxy;
+    if (!(det0 > 0.0)) return rec;
+    const double inflate = 0.09 + 1e-6 * (cx * cx + cy * cy);
+    sxx += inflate; syy += inflate;
+    const double det = sxx * syy - sxy * sxy;
+    const double relax = 1.0 / 1.02;
+    const double a = syy / det * relax, b2 = -2.0 * sxy / det * relax, c = sxx / det * relax;
+    if (!isfinite(a) || !isfinite(b2) || !isfinite(c) || !isfinite(cx) || !isfinite(cy)) return rec;
+    if (fabs(cx) > 1e6 || fabs(cy) > 1e6) return rec;   // float32 pixel offsets would lose the sub-pixel part
+    rec.cx = float(cx); rec.cy = float(cy);
+    rec.a = float(a); rec.b2 = float(b2); rec.c = float(c);
+    return rec;
+}
+
+template <int MODE, bool TRAIN>
+__global__ void __launch_bounds__(kPreprocessBlock) preprocess_kernel(
+    const float* __restrict__ positions, const float* __restrict__ scales, const float* __restrict__ rotations,
+    const float* __restrict__ opacities, const float* __restrict__ sh_0, const float* __restrict__ sh_rest,
+    const float* __restrict__ M, const float* __restrict__ VPM, const float* __restrict__ cam_position_ptr,
+    PrimBuffers out, FrameStatus* status, uint32_t n_primitives, uint32_t grid_w, uint32_t grid_h,
+    int active_sh_bases, int total_sh_bases, float near_plane, float far_plane, float scale_modifier_arg)
+{
+    using MT = ModeTraits<MODE>;
+    const uint32_t idx = blockIdx.x * kPreprocessBlock + threadIdx.x;
+    uint32_t n_touched = 0;
+
+    if (idx < n_primitives) {
+        const float4 M3 = ldg4(M + 8);
+        const float3 position = make_float3(__ldg(positions + 3 * size_t(idx)), __ldg(positions + 3 * size_t(idx) + 1), __ldg(positions + 3 * size_t(idx) + 2));
+        const float opacity = __ldg(opacities + idx);
+        // near/far culling of the centre (kernel_utils.cuh:88-90)
+        const float z = __fadd_rn(dot3_pinned(f3(M3), position), M3.w);
+        if (!(z < near_plane || z > far_plane)) {
+            const float scale_modifier = TRAIN ? 1.0f : scale_modifier_arg;
+            const float3 scale = make_float3(__ldg(scales + 3 * size_t(idx)), __ldg(scales + 3 * size_t(idx) + 1), __ldg(scales + 3 * size_t(idx) + 2));
+            const float4 q = ldg4(rotations + 4 * size_t(idx));
+            const Mat3 R = quat_to_mat(q);
+            const float3 u = make_float3(R.r11 * scale.x, R.r21 * scale.x, R.r31 * scale.x) * scale_modifier;
+            const float3 v = make_float3(R.r12 * scale.y, R.r22 * scale.y, R.r32 * scale.y) * scale_modifier;
+            const float3 w = make_float3(R.r13 * scale.z, R.r23 * scale.z, R.r33 * scale.z) * scale_modifier;
+            const float4 VPM4 = ldg4(VPM + 12);
+            const float4 T4 = row_times_T<true>(VPM4, u, v, w, position);
+            // tight cutoff for the opacity threshold of the mode (kernel_utils.cuh:104-108)
+            const float rho_cutoff = 2.0f * logf(opacity * MT::min_alpha_rcp);
+            const float4 d = make_float4(rho_cutoff, rho_cutoff, rho_cutoff, -1.0f);
+            const float s = dot(d, T4 * T4);
+            if (s != 0.0f) {
+                const float4 f = (1.0f / s) * d;
+                // exact near/far culling by the screen-space z extent (kernel_utils.cuh:110-116)
+                const float4 VPM3 = ldg4(VPM + 8);
+                const float4 T3 = row_times_T<false>(VPM3, u, v, w, position);
+                const float center_z = dot(f, T3 * T4);
+                const float extent_z = sqrtf(fmaxf(center_z * center_z - dot(f, T3 * T3), 0.0f));
+                const float z_min = center_z - extent_z;
+                const float z_max = center_z + extent_z;
+                if (!(z_min < -1.0f || z_max > 1.0f)) {
+                    const float4 VPM1 = ldg4(VPM);
+                    const float4 T1 = row_times_T<false>(VPM1, u, v, w, position);
+                    const float center_x = dot(f, T1 * T4);
+                    const float extent_x = sqrtf(fmaxf(center_x * center_x - dot(f, T1 * T1), 0.0f));
+                    const float4 VPM2 = ldg4(VPM + 4);
+                    const float4 T2 = row_times_T<false>(VPM2, u, v, w, position);
+                    const float center_y = dot(f, T2 * T4);
+                    const float extent_y = sqrtf(fmaxf(center_y * center_y - dot(f, T2 * T2), 0.0f));
+                    // tile box (+0.5: pixel centres sit at integer coordinates; kernel_utils.cuh:126-137)
+                    const float tw = float(MT::tile_w), th = float(MT::tile_h);
+                    const uint32_t x_min = min(grid_w, static_cast<uint32_t>(max(0, __float2int_rd((center_x - extent_x + 0.5f) / tw))));
+                    const uint32_t x_max = min(grid_w, static_cast<uint32_t>(max(0, __float2int_ru((center_x + extent_x + 0.5f) / tw))));
+                    const uint32_t y_min = min(grid_h, static_cast<uint32_t>(max(0, __float2int_rd((center_y - extent_y + 0.5f) / th))));
+                    const uint32_t y_max = min(grid_h, static_cast<uint32_t>(max(0, __float2int_ru((center_y + extent_y + 0.5f) / th))));
+                    n_touched = (x_max - x_min) * (y_max - y_min);
+                    if (n_touched != 0) {
+                        out.bounds[idx] = make_ushort4((unsigned short)x_min, (unsigned short)x_max, (unsigned short)y_min, (unsigned short)y_max);
+                        EvalRecord rec;
+                        rec.vpmt1 = T1; rec.vpmt2 = T2; rec.vpmt4 = T4;
+                        if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) rec.mt3 = make_float4(0.0f, 0.0f, 0.0f, z);
+                        else rec.mt3 = make_float4(dot3_pinned_alt(f3(M3), u), dot3_pinned(f3(M3), v), dot3_pinned(f3(M3), w), z);
+                        const float3 cam_position = make_float3(__ldg(cam_position_ptr), __ldg(cam_position_ptr + 1), __ldg(cam_position_ptr + 2));
+                        uint8_t clamp_bits = 0;
+                        const float3 rgb = sh_to_rgb<TRAIN>(sh_0, sh_rest, position, cam_position, idx, active_sh_bases, total_sh_bases, &clamp_bits);
+                        rec.rgba = make_float4(rgb.x, rgb.y, rgb.z, opacity);
+                        float4* dst = reinterpret_cast<float4*>(out.eval + idx);
+                        dst[0] = rec.vpmt1; dst[1] = rec.vpmt2; dst[2] = rec.vpmt4; dst[3] = rec.mt3; dst[4] = rec.rgba;
+                        if constexpr (TRAIN) out.clamp[idx] = clamp_bits;
+                        const CullRecord cr = make_cull_record<MODE>(T1, T2, T4, opacity);
+                        float4* cdst = reinterpret_cast<float4*>(out.cull + idx);
+                        cdst[0] = make_float4(cr.cx, cr.cy, cr.a, cr.b2);
+                        cdst[1] = make_float4(cr.c, 0.0f, 0.0f, 0.0f);
+                    }
+                }
+            }
+        }
+        out.n_touched[idx] = n_touched;
+    }
+
+    // per-block totals: instances and visible Gaussians
+    __shared__ uint32_t warp_sum[kPreprocessBlock / 32];
+    __shared__ uint32_t warp_vis[kPreprocessBlock / 32];
+    uint32_t sum = n_touched;
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const uint32_t vis = __popc(__ballot_sync(0xffffffffu, n_touched != 0));
+    if ((threadIdx.x & 31) == 0) { warp_sum[threadIdx.x >> 5] = sum; warp_vis[threadIdx.x >> 5] = vis; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t total = 0, total_vis = 0;
+        #pragma unroll
+        for (int i = 0; i < kPreprocessBlock / 32; ++i) { total += warp_sum[i]; total_vis += warp_vis[i]; }
+        out.block_sums[blockIdx.x] = total;
+        if (total_vis) atomicAdd(&status->n_visible, total_vis);
+    }
+}
+
+template <int MODE, bool TRAIN>
+cudaError_t launch_t(const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim, FrameStatus* status, cudaStream_t stream) {
+    const uint32_t n = uint32_t(scene.n_primitives);
+    const uint32_t blocks = (n + kPreprocessBlock - 1) / kPreprocessBlock;
+    if (blocks == 0) return cudaSuccess;
+    preprocess_kernel<MODE, TRAIN><<<blocks, kPreprocessBlock, 0, stream>>>(
+        scene.positions, scene.scales, scene.rotations, scene.opacities, scene.sh_0, scene.sh_rest, view.M, view.VPM, view.cam_position,
+        prim, status, n, uint32_t(geo.grid_w), uint32_t(geo.grid_h), view.active_sh_bases, scene.total_sh_bases, view.near_plane,
+        view.far_plane, view.scale_modifier);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_preprocess(int mode, bool train, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo,
+                              const PrimBuffers& prim, FrameStatus* status, cudaStream_t stream) {
+    switch (mode) {
+#define HTGS_CASE(M) case M: return train ? launch_t<M, true>(scene, view, geo, prim, status, stream) : launch_t<M, false>(scene, view, geo, prim, status, stream);
+        HTGS_CASE(HTGS_MODE_HYBRID_BLEND)
+        HTGS_CASE(HTGS_MODE_ALPHA_BLEND_FIRST_K)
+        HTGS_CASE(HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING)
+        HTGS_CASE(HTGS_MODE_OIT_BLEND)
+#undef HTGS_CASE
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace htgs

@@ -1,0 +1,142 @@
+/*
+ * htgs_b200 - C ABI of the sm_100a (B200) rasterizer core.
+ *
+ * Drop-in boundary for the rasterizer of nerficg-project/HTGS.  The entry points
+ * below are what the reference's pybind module `HTGSCudaBackend._C` binds
+ * (torch_bindings/bindings.cpp:8-16), restated with plain pointers and sizes:
+ * no torch types cross this boundary.  All pointers are DEVICE pointers unless
+ * a comment says "host".  File:line citations are relative to
+ * HTGSCudaBackend/HTGSCudaBackend/ of the reference.
+ *
+ * Threading: a context is bound to one CUDA device and must not be used from
+ * two host threads at once.  Calls are stream-ordered on the stream passed in
+ * and re-entrant across contexts (camera matrices are read from device memory
+ * by the kernels; nothing is uploaded to __constant__ memory).
+ */
+#ifndef HTGS_B200_H
+#define HTGS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* RasterizerMode (torch_bindings/rasterization.py:9-13) */
+enum HtgsMode {
+    HTGS_MODE_HYBRID_BLEND = 0,
+    HTGS_MODE_ALPHA_BLEND_FIRST_K = 1,
+    HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING = 2,
+    HTGS_MODE_OIT_BLEND = 3
+};
+
+enum HtgsStatus {
+    HTGS_OK = 0,
+    HTGS_ERR_INVALID_ARGUMENT = 1,
+    HTGS_ERR_UNSUPPORTED_MODE = 2,   /* the reference throws "unsupported rasterizer mode" (rasterization/src/rasterization_api.cu:171-172) */
+    HTGS_ERR_WORKSPACE_TOO_SMALL = 3,
+    HTGS_ERR_CUDA = 4,
+    HTGS_ERR_DEVICE_FLAG = 5         /* a kernel reported an internal error (e.g. a bounded wait gave up) */
+};
+
+/* The six per-Gaussian input tensors of `rasterize` / `diff_rasterize`
+ * (torch_bindings/rasterization.py:140-150), contiguous float32. */
+typedef struct HtgsScene {
+    const float* positions;   /* [N,3] */
+    const float* scales;      /* [N,3] activated */
+    const float* rotations;   /* [N,4] (r,x,y,z), unit length */
+    const float* opacities;   /* [N,1] activated */
+    const float* sh_0;        /* [N,1,3] */
+    const float* sh_rest;     /* [N,B,3]; may be NULL when B == 0 */
+    int32_t n_primitives;     /* N */
+    int32_t total_sh_bases;   /* B = sh_rest.size(1) */
+} HtgsScene;
+
+/* RasterizerSettings (torch_bindings/rasterization.py:16-42).  The matrices stay device
+ * tensors, as in the reference, so that building a view never forces a host sync. */
+typedef struct HtgsView {
+    const float* M;             /* [4,4] world -> view, row-major */
+    const float* VPM;           /* [4,4] world -> screen, row-major */
+    const float* cam_position;  /* [3] */
+    int32_t mode;               /* HtgsMode */
+    int32_t K;                  /* HYBRID_BLEND / ALPHA_BLEND_FIRST_K only; rounded down to a power of two <= 32 */
+    int32_t active_sh_bases;    /* 1, 4, 9 or 16 */
+    int32_t width;
+    int32_t height;
+    float near_plane;
+    float far_plane;
+    float scale_modifier;       /* ignored (treated as 1) by the training forward, as in the reference */
+} HtgsView;
+
+/* Host-side summary of the last frame. */
+typedef struct HtgsFrameInfo {
+    uint32_t n_instances;        /* (tile, Gaussian) instances */
+    uint32_t n_visible;          /* Gaussians that passed culling */
+    uint32_t key_bytes;          /* 2, 4 or 8: width of the sort key used */
+    uint32_t end_bit;            /* number of key bits that were sorted */
+    uint32_t reruns;             /* times the frame was re-run after growing the internal workspace */
+    uint32_t device_error;       /* device-side error flags (0 = none) */
+    uint64_t workspace_bytes;    /* bytes a caller-provided workspace must have for this frame */
+} HtgsFrameInfo;
+
+/* Device pointers into the workspace of the last htgs_render call of a context; valid
+ * until the next call on that context.  For parity tests and profiling. */
+typedef struct HtgsIntermediates {
+    const uint32_t* n_touched;     /* [N] tiles touched per Gaussian (0 = culled) */
+    const uint16_t* bounds;        /* [N,4] x_min,x_max,y_min,y_max in tiles (undefined where n_touched == 0) */
+    const void* eval_records;      /* [N] 80-byte records: vpmt1, vpmt2, vpmt4, mt3, rgba (float4 each) */
+    const void* cull_records;      /* [N] 32-byte records */
+    const void* keys_unsorted;     /* [n_instances] keys in emission order (key_bytes wide) */
+    const uint32_t* prims_unsorted;/* [n_instances] */
+    const void* keys_sorted;       /* [n_instances] */
+    const uint32_t* prims_sorted;  /* [n_instances] Gaussian index per sorted instance */
+    const uint32_t* tile_ranges;   /* [n_tiles,2] begin,end into the sorted arrays; (0,0) for empty tiles */
+    uint32_t n_tiles;
+    uint32_t grid_width;
+    uint32_t grid_height;
+    uint32_t key_bytes;
+} HtgsIntermediates;
+
+typedef struct HtgsContext HtgsContext;
+
+/* Library management.  htgs_last_error() returns the message of the last failing call of
+ * the calling host thread. */
+HtgsContext* htgs_create(int device);
+void htgs_destroy(HtgsContext* ctx);
+const char* htgs_last_error(void);
+int htgs_version(void);
+
+/* Bytes of workspace htgs_render needs for `instance_capacity` instances. */
+size_t htgs_render_workspace_bytes(const HtgsScene* scene, const HtgsView* view, uint64_t instance_capacity);
+
+/*
+ * Forward render.  Replaces `_C.render` = htgs::rasterization::inference_wrapper
+ * (rasterization/include/rasterization_api.h:57-77, rasterization/src/rasterization_api.cu:365-516).
+ *   image: [3,H,W] if to_chw else [H,W,3], clamped to [0,1];  depth: [H,W];
+ *   alpha: [H,W] or NULL.  Alpha is not an output of the reference; it is the total opacity the
+ *          reference uses internally to normalise the mean depth.
+ * workspace == NULL selects the context's own grow-only workspace (the frame is re-run once
+ * after growing when the instance count exceeds its capacity).  With a caller workspace that is too
+ * small the call returns HTGS_ERR_WORKSPACE_TOO_SMALL and info->workspace_bytes says what is needed.
+ * The call synchronises `stream` once, at its end, to read the frame status.
+ */
+int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
+                int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream, HtgsFrameInfo* info);
+
+/* As htgs_render with HOST buffers: inputs are copied to the device and the image/depth back inside the
+ * call (used for end-to-end measurement and by callers without device memory of their own). */
+int htgs_render_host(HtgsContext* ctx, const HtgsScene* host_scene, const HtgsView* host_view, float* host_image, float* host_depth,
+                     int to_chw, int use_median_depth, HtgsFrameInfo* info);
+
+int htgs_get_intermediates(HtgsContext* ctx, HtgsIntermediates* out);
+
+/* Plain device<->host copies for callers that have no CUDA runtime binding of their own (tests). */
+int htgs_memcpy_d2h(void* host_dst, const void* device_src, size_t bytes);
+int htgs_memcpy_h2d(void* device_dst, const void* host_src, size_t bytes);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HTGS_B200_H */
