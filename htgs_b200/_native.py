@@ -42,7 +42,8 @@ class HtgsFrameInfo(ctypes.Structure):
     _fields_ = [
         ("n_instances", ctypes.c_uint32), ("n_visible", ctypes.c_uint32), ("key_bytes", ctypes.c_uint32),
         ("end_bit", ctypes.c_uint32), ("reruns", ctypes.c_uint32), ("device_error", ctypes.c_uint32),
-        ("workspace_bytes", ctypes.c_uint64),
+        ("kernel_launches", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
+        ("workspace_bytes", ctypes.c_uint64), ("candidate_pairs", ctypes.c_uint64), ("accepted_fragments", ctypes.c_uint64),
     ]
 
 
@@ -110,6 +111,9 @@ def lib():
                                                ctypes.c_int, ctypes.c_int, ctypes.POINTER(HtgsFrameInfo)]
                 l.htgs_get_intermediates.restype = ctypes.c_int
                 l.htgs_get_intermediates.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsIntermediates)]
+                l.htgs_set_profiling.argtypes = [ctypes.c_void_p, ctypes.c_int]
+                l.htgs_set_collect_stats.argtypes = [ctypes.c_void_p, ctypes.c_int]
+                l.htgs_get_stage_ms.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]
                 l.htgs_memcpy_d2h.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
                 l.htgs_memcpy_h2d.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
                 _lib = l

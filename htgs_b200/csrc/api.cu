@@ -122,6 +122,12 @@ struct HtgsContext {
     FrameGeometry last_geo{};
     uint32_t last_n_instances = 0;
     bool has_last = false;
+    // measurement aids
+    bool profiling = false;
+    bool collect_stats = false;
+    cudaEvent_t events[8] = {};
+    bool events_created = false;
+    float stage_ms[HTGS_N_STAGES] = {};
 };
 
 extern "C" {
@@ -156,6 +162,7 @@ void htgs_destroy(HtgsContext* ctx) {
     if (ctx->host_path_buf) cudaFree(ctx->host_path_buf);
     if (ctx->host_path_stream) cudaStreamDestroy(ctx->host_path_stream);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
+    if (ctx->events_created) for (auto& e : ctx->events) cudaEventDestroy(e);
     delete ctx;
 }
 
@@ -167,15 +174,34 @@ size_t htgs_render_workspace_bytes(const HtgsScene* scene, const HtgsView* view,
 }
 
 static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const SortPlan& plan,
-                     const FrameLayout& L, const BlendOutputs& out, cudaStream_t stream) {
+                     const FrameLayout& L, BlendOutputs out, cudaStream_t stream, uint32_t* launches) {
     cudaError_t err;
+    const bool prof = ctx->profiling;
+    if (prof && !ctx->events_created) {
+        for (auto& e : ctx->events) if ((err = cudaEventCreate(&e)) != cudaSuccess) return fail_cuda(err, "cudaEventCreate");
+        ctx->events_created = true;
+    }
+    cudaEvent_t* ev = ctx->events;   // 0 start, 1 preprocess, 2 scan, 3 emit, 4 sort, 5 ranges, 6 blend
+    out.collect_stats = ctx->collect_stats;
     if ((err = cudaMemsetAsync(L.status, 0, sizeof(FrameStatus), stream)) != cudaSuccess) return fail_cuda(err, "status reset");
+    if (prof) cudaEventRecord(ev[0], stream);
     if ((err = launch_preprocess(view.mode, false, scene, view, geo, L.prim, L.status, stream)) != cudaSuccess) return fail_cuda(err, "preprocess");
-    if ((err = launch_binning(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream)) != cudaSuccess) return fail_cuda(err, "binning");
+    if (prof) cudaEventRecord(ev[1], stream);
+    if ((err = launch_scan_only(scene, L.prim, L.inst.capacity, L.status, stream)) != cudaSuccess) return fail_cuda(err, "scan");
+    if (prof) cudaEventRecord(ev[2], stream);
+    *launches += (scene.n_primitives > 0 ? 1 : 0) + 1;
+    if ((err = launch_emit_sort_ranges(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream,
+                                       prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "binning");
     const uint32_t* prims_sorted = L.inst.prims[plan.final_buffer];
     if ((err = launch_blend_inference(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, out, L.status, ctx->sm_count, stream)) != cudaSuccess) return fail_cuda(err, "blend");
+    *launches += 1;
+    if (prof) cudaEventRecord(ev[6], stream);
     if ((err = cudaMemcpyAsync(ctx->host_status, L.status, sizeof(FrameStatus), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return fail_cuda(err, "status copy");
     if ((err = cudaStreamSynchronize(stream)) != cudaSuccess) return fail_cuda(err, "frame synchronisation");
+    if (prof) {
+        for (int i = 0; i < 6; ++i) cudaEventElapsedTime(&ctx->stage_ms[i], ev[i], ev[i + 1]);
+        cudaEventElapsedTime(&ctx->stage_ms[HTGS_STAGE_TOTAL], ev[0], ev[6]);
+    }
     return HTGS_OK;
 }
 
@@ -193,9 +219,9 @@ int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, 
 
     const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
     const SortPlan plan = make_sort_plan(view->mode, geo.n_tiles);
-    const BlendOutputs out{image, depth, alpha, to_chw != 0, use_median_depth != 0};
+    const BlendOutputs out{image, depth, alpha, to_chw != 0, use_median_depth != 0, false};
     const bool internal = workspace == nullptr;
-    uint32_t reruns = 0;
+    uint32_t reruns = 0, launches = 0;
 
     uint64_t capacity;
     if (internal) {
@@ -229,7 +255,7 @@ int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, 
         } else {
             L = carve_frame(workspace, scene->n_primitives, geo.n_tiles, plan, capacity, false);
         }
-        rc = run_frame(ctx, *scene, *view, geo, plan, L, out, stream);
+        rc = run_frame(ctx, *scene, *view, geo, plan, L, out, stream, &launches);
         if (rc != HTGS_OK) return rc;
         const FrameStatus st = *ctx->host_status;
         ctx->last_layout = L; ctx->last_plan = plan; ctx->last_geo = geo; ctx->last_n_instances = st.overflow ? 0 : st.n_instances; ctx->has_last = true;
@@ -237,6 +263,8 @@ int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, 
         if (info) {
             info->n_instances = st.n_instances; info->n_visible = st.n_visible; info->key_bytes = uint32_t(plan.key_bytes);
             info->end_bit = uint32_t(plan.end_bit); info->reruns = reruns; info->device_error = st.error;
+            info->kernel_launches = launches; info->reserved = 0;
+            info->candidate_pairs = st.candidate_pairs; info->accepted_fragments = st.accepted_fragments;
             info->workspace_bytes = carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, st.overflow ? needed_capacity : capacity, false).bytes;
         }
         if (st.error) return fail(HTGS_ERR_DEVICE_FLAG, "a kernel reported an internal error (bounded wait gave up)");
@@ -268,6 +296,24 @@ int htgs_get_intermediates(HtgsContext* ctx, HtgsIntermediates* out) {
     out->grid_width = uint32_t(ctx->last_geo.grid_w);
     out->grid_height = uint32_t(ctx->last_geo.grid_h);
     out->key_bytes = uint32_t(p.key_bytes);
+    return HTGS_OK;
+}
+
+int htgs_set_profiling(HtgsContext* ctx, int enable) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    ctx->profiling = enable != 0;
+    return HTGS_OK;
+}
+
+int htgs_get_stage_ms(HtgsContext* ctx, float* out_ms) {
+    if (!ctx || !out_ms) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    for (int i = 0; i < HTGS_N_STAGES; ++i) out_ms[i] = ctx->stage_ms[i];
+    return HTGS_OK;
+}
+
+int htgs_set_collect_stats(HtgsContext* ctx, int enable) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    ctx->collect_stats = enable != 0;
     return HTGS_OK;
 }
 

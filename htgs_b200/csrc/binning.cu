@@ -359,22 +359,29 @@ __global__ void __launch_bounds__(256) tile_ranges_kernel(const KeyT* __restrict
 
 template <typename KeyT>
 cudaError_t emit_sort_ranges_t(const HtgsScene& scene, const FrameGeometry& geo, const SortPlan& plan, const PrimBuffers& prim, const InstBuffers& inst,
-                               uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream) {
+                               uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream, cudaEvent_t* ev, uint32_t* launches) {
     const uint32_t n = uint32_t(scene.n_primitives);
     const uint32_t prim_blocks = (n + kPreprocessBlock - 1) / kPreprocessBlock;
     cudaError_t err = cudaMemsetAsync(tile_ranges, 0, sizeof(uint2) * size_t(geo.n_tiles), stream);
     if (err != cudaSuccess) return err;
-    if (prim_blocks == 0 || inst.capacity == 0) return cudaSuccess;
+    if (prim_blocks == 0 || inst.capacity == 0) {
+        if (ev) { cudaEventRecord(ev[0], stream); cudaEventRecord(ev[1], stream); cudaEventRecord(ev[2], stream); }
+        return cudaSuccess;
+    }
     emit_instances_kernel<KeyT><<<prim_blocks, kPreprocessBlock, 0, stream>>>(
         prim.n_touched, prim.bounds, prim.eval, prim.block_sums, prim.block_offsets, static_cast<KeyT*>(inst.keys[0]), inst.prims[0], n,
         uint32_t(geo.grid_w), inst.capacity);
+    if (ev) cudaEventRecord(ev[0], stream);
+    if (launches) *launches += 1;
     const uint32_t persistent = uint32_t(sm_count) * 4;
     const uint32_t sort_grid = inst.sort_blocks_cap < persistent ? (inst.sort_blocks_cap ? inst.sort_blocks_cap : 1) : persistent;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 0 && device < 64 && !configured[device]) {
         err = cudaFuncSetAttribute(radix_scatter_kernel<KeyT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(scatter_smem_bytes<KeyT>()));
         if (err != cudaSuccess) return err;
-        configured = true;
+        configured[device] = true;
     }
     int cur = 0;
     for (int p = 0; p < plan.n_passes; ++p) {
@@ -386,8 +393,12 @@ cudaError_t emit_sort_ranges_t(const HtgsScene& scene, const FrameGeometry& geo,
             kin, inst.prims[cur], kout, inst.prims[cur ^ 1], inst.radix_table, inst.sort_blocks_cap, inst.digit_totals, status, inst.capacity,
             plan.shift[p], plan.bits[p]);
         cur ^= 1;
+        if (launches) *launches += 3;
     }
+    if (ev) cudaEventRecord(ev[1], stream);
     tile_ranges_kernel<KeyT><<<persistent, 256, 0, stream>>>(static_cast<const KeyT*>(inst.keys[cur]), tile_ranges, status, inst.capacity);
+    if (ev) cudaEventRecord(ev[2], stream);
+    if (launches) *launches += 1;
     return cudaGetLastError();
 }
 
@@ -401,21 +412,15 @@ cudaError_t launch_scan_only(const HtgsScene& scene, const PrimBuffers& prim, ui
 }
 
 cudaError_t launch_emit_sort_ranges(int mode, const HtgsScene& scene, const FrameGeometry& geo, const SortPlan& plan, const PrimBuffers& prim,
-                                    const InstBuffers& inst, uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream) {
+                                    const InstBuffers& inst, uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream,
+                                    cudaEvent_t* stage_events, uint32_t* launches) {
     (void)mode;
     switch (plan.key_bytes) {
-        case 2: return emit_sort_ranges_t<uint16_t>(scene, geo, plan, prim, inst, tile_ranges, status, sm_count, stream);
-        case 4: return emit_sort_ranges_t<uint32_t>(scene, geo, plan, prim, inst, tile_ranges, status, sm_count, stream);
-        case 8: return emit_sort_ranges_t<uint64_t>(scene, geo, plan, prim, inst, tile_ranges, status, sm_count, stream);
+        case 2: return emit_sort_ranges_t<uint16_t>(scene, geo, plan, prim, inst, tile_ranges, status, sm_count, stream, stage_events, launches);
+        case 4: return emit_sort_ranges_t<uint32_t>(scene, geo, plan, prim, inst, tile_ranges, status, sm_count, stream, stage_events, launches);
+        case 8: return emit_sort_ranges_t<uint64_t>(scene, geo, plan, prim, inst, tile_ranges, status, sm_count, stream, stage_events, launches);
         default: return cudaErrorInvalidValue;
     }
-}
-
-cudaError_t launch_binning(int mode, const HtgsScene& scene, const FrameGeometry& geo, const SortPlan& plan, const PrimBuffers& prim,
-                           const InstBuffers& inst, uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream) {
-    cudaError_t err = launch_scan_only(scene, prim, inst.capacity, status, stream);
-    if (err != cudaSuccess) return err;
-    return launch_emit_sort_ranges(mode, scene, geo, plan, prim, inst, tile_ranges, status, sm_count, stream);
 }
 
 }  // namespace htgs

@@ -111,7 +111,7 @@ __device__ __forceinline__ FragmentFront fragment_front(const float4& VPMT1, con
     return f;
 }
 
-template <int MODE, int K>
+template <int MODE, int K, bool STATS>
 __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
     const CullRecord* __restrict__ cull, float* __restrict__ image, float* __restrict__ depth_out, float* __restrict__ alpha_out,
@@ -164,6 +164,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
     const uint2 range = tile_ranges[tile_y * grid_w + tile_x];
     uint32_t phase = 0;
     bool wait_failed = false;
+    [[maybe_unused]] uint32_t stat_candidates = 0, stat_accepted = 0;
     __syncthreads();
 
     for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += TS::batch) {
@@ -233,6 +234,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
             phase ^= 1;
             copies_landed = true;
         }
+        if constexpr (STATS) stat_candidates += n_cand;
         const uint32_t n_iter = __reduce_max_sync(0xffffffffu, n_cand);
         for (uint32_t it = 0; it < n_iter; ++it) {
             if (it >= n_cand || done) continue;
@@ -249,6 +251,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
                 const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
                 const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
                 if (alpha < MT::min_alpha) continue;
+                if constexpr (STATS) ++stat_accepted;
                 const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
                 const float4 MT3 = rec[3];
                 float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
@@ -277,6 +280,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
                 const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
                 const float alpha = fminf(rec[4].w * G, kMaxFragmentAlpha);
                 if (alpha < MT::min_alpha) continue;
+                if constexpr (STATS) ++stat_accepted;
                 pool2[free_slot * TS::threads + tid] = make_float2(alpha, __uint_as_float(s_prim[j]));
                 uint32_t slot = free_slot;
                 #pragma unroll
@@ -293,6 +297,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
                 const float opacity = rgba_in.w;
                 const float alpha = fminf(opacity * G, kMaxFragmentAlpha);
                 if (alpha < MT::min_alpha) continue;
+                if constexpr (STATS) ++stat_accepted;
                 const float blending_weight = transmittance * alpha;
                 acc.x += blending_weight * rgba_in.x; acc.y += blending_weight * rgba_in.y; acc.z += blending_weight * rgba_in.z;
                 const float depth = rec[3].w;
@@ -305,6 +310,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
                 const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
                 const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
                 if (alpha < MT::min_alpha) continue;
+                if constexpr (STATS) ++stat_accepted;
                 const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
                 const float4 MT3 = rec[3];
                 const float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
@@ -317,6 +323,10 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
     }
 
     if (wait_failed) atomicOr(&status->error, 1u);
+    if constexpr (STATS) {
+        const uint32_t c = __reduce_add_sync(0xffffffffu, stat_candidates), a = __reduce_add_sync(0xffffffffu, stat_accepted);
+        if (lane == 0) { atomicAdd(&status->candidate_pairs, (unsigned long long)c); atomicAdd(&status->accepted_fragments, (unsigned long long)a); }
+    }
     if (!inside) return;
 
     // ---- compositing --------------------------------------------------------------------------------
@@ -404,18 +414,31 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
     if (alpha_out) alpha_out[pixel_idx] = alpha_pixel;
 }
 
-template <int MODE, int K>
-cudaError_t launch_mode_k(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
-                          const BlendOutputs& out, FrameStatus* status, cudaStream_t stream) {
+template <int MODE, int K, bool STATS>
+cudaError_t launch_mode_k_stats(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                                const BlendOutputs& out, FrameStatus* status, cudaStream_t stream) {
     using SL = SmemLayout<MODE, K>;
-    auto kernel = blend_inference_kernel<MODE, K>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SL::total));
-    if (err != cudaSuccess) return err;
+    auto kernel = blend_inference_kernel<MODE, K, STATS>;
+    static bool configured[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 0 && device < 64 && !configured[device]) {
+        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SL::total));
+        if (err != cudaSuccess) return err;
+        configured[device] = true;
+    }
     const dim3 grid(geo.grid_w, geo.grid_h, 1);
     kernel<<<grid, TileShape<MODE>::threads, SL::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, out.image, out.depth, out.alpha,
                                                                   uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), out.to_chw,
                                                                   out.use_median_depth, status);
     return cudaGetLastError();
+}
+
+template <int MODE, int K>
+cudaError_t launch_mode_k(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                          const BlendOutputs& out, FrameStatus* status, cudaStream_t stream) {
+    return out.collect_stats ? launch_mode_k_stats<MODE, K, true>(geo, prim, prims_sorted, tile_ranges, out, status, stream)
+                             : launch_mode_k_stats<MODE, K, false>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
 }
 
 // K is rounded down to a power of two <= 32 (hybrid_blend/inference.cu:15-28)

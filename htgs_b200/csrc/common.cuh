@@ -87,7 +87,9 @@ struct FrameStatus {
     unsigned int overflow;        // 1 if n_instances exceeded the instance capacity of the workspace
     unsigned int n_visible;       // Gaussians that survived culling
     unsigned int error;           // bounded waits that gave up, bad arguments seen on the device, ...
-    unsigned int reserved[12];
+    unsigned long long candidate_pairs;     // statistics mode of the blend kernels
+    unsigned long long accepted_fragments;  // statistics mode of the blend kernels
+    unsigned int reserved[8];
 };
 
 struct CameraParams {             // read from device memory at kernel start (re-entrant, no __constant__ upload)

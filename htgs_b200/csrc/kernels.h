@@ -51,11 +51,11 @@ cudaError_t launch_preprocess(int mode, bool train, const HtgsScene& scene, cons
 
 // binning.cu: scan of block sums, instance emission, stable radix sort, tile ranges.
 // Everything after the scan reads the instance count from `status` on the device.
-cudaError_t launch_binning(int mode, const HtgsScene& scene, const FrameGeometry& geo, const SortPlan& plan, const PrimBuffers& prim,
-                           const InstBuffers& inst, uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream);
 cudaError_t launch_scan_only(const HtgsScene& scene, const PrimBuffers& prim, uint32_t capacity, FrameStatus* status, cudaStream_t stream);
+// `stage_events` (optional): events recorded after emission, after the sort and after the range kernel.
 cudaError_t launch_emit_sort_ranges(int mode, const HtgsScene& scene, const FrameGeometry& geo, const SortPlan& plan, const PrimBuffers& prim,
-                                    const InstBuffers& inst, uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream);
+                                    const InstBuffers& inst, uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream,
+                                    cudaEvent_t* stage_events = nullptr, uint32_t* launches = nullptr);
 
 // blend.cu
 struct BlendOutputs {
@@ -64,6 +64,7 @@ struct BlendOutputs {
     float* alpha;     // may be null
     bool to_chw;
     bool use_median_depth;
+    bool collect_stats;
 };
 cudaError_t launch_blend_inference(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
                                    const uint2* tile_ranges, const BlendOutputs& out, FrameStatus* status, int sm_count, cudaStream_t stream);

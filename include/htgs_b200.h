@@ -77,7 +77,11 @@ typedef struct HtgsFrameInfo {
     uint32_t end_bit;            /* number of key bits that were sorted */
     uint32_t reruns;             /* times the frame was re-run after growing the internal workspace */
     uint32_t device_error;       /* device-side error flags (0 = none) */
+    uint32_t kernel_launches;    /* kernels of this library launched for the frame (re-runs included) */
+    uint32_t reserved;
     uint64_t workspace_bytes;    /* bytes a caller-provided workspace must have for this frame */
+    uint64_t candidate_pairs;    /* statistics mode only: (pixel, Gaussian) pairs that passed the outline test */
+    uint64_t accepted_fragments; /* statistics mode only: fragments accepted by the exact test */
 } HtgsFrameInfo;
 
 /* Device pointers into the workspace of the last htgs_render call of a context; valid
@@ -130,6 +134,18 @@ int htgs_render_host(HtgsContext* ctx, const HtgsScene* host_scene, const HtgsVi
                      int to_chw, int use_median_depth, HtgsFrameInfo* info);
 
 int htgs_get_intermediates(HtgsContext* ctx, HtgsIntermediates* out);
+
+/* Measurement aids (off by default; they do not change results).
+ * Profiling: CUDA events are recorded on the frame's stream between the stages; after the call
+ * htgs_get_stage_ms fills out_ms[0..HTGS_N_STAGES) with the device time of each stage in ms.
+ * Statistics: the blend kernel also counts candidate pairs and accepted fragments (HtgsFrameInfo). */
+enum HtgsStage {
+    HTGS_STAGE_PREPROCESS = 0, HTGS_STAGE_SCAN = 1, HTGS_STAGE_EMIT = 2, HTGS_STAGE_SORT = 3,
+    HTGS_STAGE_RANGES = 4, HTGS_STAGE_BLEND = 5, HTGS_STAGE_TOTAL = 6, HTGS_N_STAGES = 7
+};
+int htgs_set_profiling(HtgsContext* ctx, int enable);
+int htgs_get_stage_ms(HtgsContext* ctx, float* out_ms);
+int htgs_set_collect_stats(HtgsContext* ctx, int enable);
 
 /* Plain device<->host copies for callers that have no CUDA runtime binding of their own (tests). */
 int htgs_memcpy_d2h(void* host_dst, const void* device_src, size_t bytes);
