@@ -11,7 +11,7 @@ import threading
 from typing import Dict, Optional
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libhtgs_b200.so")
+LIB_PATH = os.environ.get("HTGS_B200_LIB") or os.path.join(_HERE, "libhtgs_b200.so")
 
 HTGS_OK = 0
 HTGS_ERR_INVALID_ARGUMENT = 1

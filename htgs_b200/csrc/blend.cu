@@ -7,26 +7,31 @@
 //   OIT_BLEND                  rasterization/include/oit_blend/kernels/inference.cuh:78-177
 // The per-fragment arithmetic (planes through the pixel ray, rho^2, G, alpha, depth of the point
 // of maximum contribution) and every threshold decision are kept operation for operation, and each
-// pixel still sees its tile's instances in list order, so results match the reference.  How the
-// work is organised is different:
+// pixel still sees its tile's instances in list order, so results match the reference bit for bit.
+// How the work is organised is different:
 //
-//  1. Staging.  One thread per instance of a batch loads the Gaussian's conservative screen-space
-//     outline (32 bytes), tests it against the pixel rectangle of every warp of the tile, and - if any
-//     warp can be touched - starts ONE 80-byte bulk asynchronous copy (TMA, cp.async.bulk) of the
-//     evaluation record into shared memory, completion tracked by an mbarrier.  Warp ballots turn the
-//     per-rectangle results into one bit mask per warp.
-//  2. Candidate pass (overlaps the copies in flight).  Each pixel walks only the set bits of its warp's
-//     mask and evaluates the 7-flop outline test; pixels that may be touched push the batch slot into a
-//     per-pixel FIFO in shared memory.  No divergence: the mask is warp-uniform.
-//  3. Exact pass.  After the mbarrier completes, every lane drains its own FIFO, so (almost) every
-//     iteration of every lane is an accepted fragment: the expensive part (IEEE divide, expf, depth,
-//     K-buffer insertion) runs converged instead of once per Gaussian per warp.
+//  1. Staging.  One thread per instance of a batch starts ONE 80-byte bulk asynchronous copy (TMA,
+//     cp.async.bulk) of the Gaussian's evaluation record into shared memory, completion tracked by an
+//     mbarrier, and publishes the Gaussian's conservative screen-space outline (5 floats).  Index and
+//     outline of the NEXT batch are prefetched into registers while the current batch is processed.
+//  2. Candidate masks (overlap the copies in flight).  Inside a warp, lane l takes Gaussian l of the
+//     batch and evaluates the 3-flop outline test at each of the warp's 32 pixels; one warp ballot per
+//     pixel transposes the result, so that afterwards lane p holds the bit mask of the Gaussians that
+//     can touch pixel p.  No divergence, no shared-memory queue.
+//  3. Exact pass.  After the mbarrier completes, every lane walks the set bits of its own mask, so
+//     (almost) every iteration of every lane is an accepted fragment: the expensive part (IEEE divide,
+//     expf, depth, K-buffer insertion) runs converged instead of once per Gaussian per warp.  HYBRID_BLEND
+//     evaluates two candidates per trip for instruction-level parallelism and commits them in list order.
 //  4. K-buffer.  Registers hold only (depth, slot) pairs; the payloads live in a shared-memory pool of
 //     K+1 slots per pixel, so an insertion moves 2 registers per level instead of 5-6.  The buffer
 //     references K slots, one is free: a new fragment is written to the free slot, the insertion
 //     chain carries (depth, slot) pairs exactly like the reference's swap chain carries whole
 //     fragments, and the slot that falls out of the chain becomes the free one.
 #include "kernels.h"
+
+#ifndef HTGS_EXPERIMENT
+#define HTGS_EXPERIMENT 0   // timing experiments only (wrong images): 1 no insertion, 2 no exact pass, 3 staging only
+#endif
 
 namespace htgs {
 
@@ -38,38 +43,9 @@ template <int MODE> struct TileShape {
     static constexpr int warps = threads / 32;
     static constexpr int rows_per_warp = 32 / tw;
     static constexpr int batch = threads;            // instances staged per iteration (one per thread)
-    static constexpr int mask_words = batch / 32;
-    static constexpr int chunk_words = mask_words < 2 ? mask_words : 2;   // candidate/exact passes alternate every 64 instances
-    static constexpr int chunk = chunk_words * 32;
+    static constexpr int chunk = 64;                 // candidate masks are built and consumed 64 instances at a time
+    static constexpr int chunks = batch / chunk;
 };
-
-// minimum over the integer pixel rectangle [x0,x1]x[y0,y1] of q = a dx^2 + b2 dx dy + c dy^2 <= 1 ?
-__device__ __forceinline__ bool outline_touches_rect(const float4& c0, float cc, float x0, float x1, float y0, float y1) {
-    const float cx = c0.x, cy = c0.y, a = c0.z, b2 = c0.w;
-    if (!(fabsf(cx) <= FLT_MAX)) return false;          // "reject everything" record
-    if (a == 0.0f && cc == 0.0f) return true;           // "accept everything" record
-    const float dx0 = x0 - cx, dx1 = x1 - cx, dy0 = y0 - cy, dy1 = y1 - cy;
-    if (dx0 <= 0.0f && dx1 >= 0.0f && dy0 <= 0.0f && dy1 >= 0.0f) return true;
-    const float ky = -0.5f * b2 / cc, kx = -0.5f * b2 / a;
-    float qmin = FLT_MAX;
-    {
-        const float dy = fminf(fmaxf(ky * dx0, dy0), dy1);
-        qmin = fminf(qmin, dx0 * (a * dx0 + b2 * dy) + cc * dy * dy);
-    }
-    {
-        const float dy = fminf(fmaxf(ky * dx1, dy0), dy1);
-        qmin = fminf(qmin, dx1 * (a * dx1 + b2 * dy) + cc * dy * dy);
-    }
-    {
-        const float dx = fminf(fmaxf(kx * dy0, dx0), dx1);
-        qmin = fminf(qmin, dx * (a * dx + b2 * dy0) + cc * dy0 * dy0);
-    }
-    {
-        const float dx = fminf(fmaxf(kx * dy1, dx0), dx1);
-        qmin = fminf(qmin, dx * (a * dx + b2 * dy1) + cc * dy1 * dy1);
-    }
-    return qmin <= 1.0f;
-}
 
 template <int MODE, int K> struct SmemLayout {
     using TS = TileShape<MODE>;
@@ -82,13 +58,9 @@ template <int MODE, int K> struct SmemLayout {
     static constexpr size_t cullc_off = cull4_off + cull4_bytes;
     static constexpr size_t cullc_bytes = size_t(TS::batch) * 4;
     static constexpr size_t prim_off = cullc_off + cullc_bytes;
-    static constexpr size_t prim_bytes = size_t(TS::batch) * 4;
-    static constexpr size_t mask_off = prim_off + prim_bytes;
-    static constexpr size_t mask_bytes = size_t(TS::warps) * TS::mask_words * 4;
-    static constexpr size_t bar_off = (mask_off + mask_bytes + 15) & ~size_t(15);
-    static constexpr size_t fifo_off = bar_off + 16;
-    static constexpr size_t fifo_bytes = size_t(TS::chunk) * TS::threads;      // u8 [slot][thread]
-    static constexpr size_t pool_off = (fifo_off + fifo_bytes + 15) & ~size_t(15);
+    static constexpr size_t prim_bytes = (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) ? size_t(TS::batch) * 4 : 0;
+    static constexpr size_t bar_off = (prim_off + prim_bytes + 15) & ~size_t(15);
+    static constexpr size_t pool_off = bar_off + 16;
     static constexpr size_t pool_bytes = has_kbuffer ? size_t(K + 1) * TS::threads * pool_elem : 0;
     static constexpr size_t total = pool_off + pool_bytes;
 };
@@ -124,11 +96,8 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
     EvalRecord* s_eval = reinterpret_cast<EvalRecord*>(smem + SL::eval_off);
     float4* s_cull4 = reinterpret_cast<float4*>(smem + SL::cull4_off);
     float* s_cullc = reinterpret_cast<float*>(smem + SL::cullc_off);
-    uint32_t* s_prim = reinterpret_cast<uint32_t*>(smem + SL::prim_off);
-    uint32_t* s_mask = reinterpret_cast<uint32_t*>(smem + SL::mask_off);
+    [[maybe_unused]] uint32_t* s_prim = reinterpret_cast<uint32_t*>(smem + SL::prim_off);
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + SL::bar_off);
-    uint8_t* s_fifo = smem + SL::fifo_off;
-    (void)s_prim;
 
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = tid >> 5, lane = tid & 31;
@@ -165,6 +134,19 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
     uint32_t phase = 0;
     bool wait_failed = false;
     [[maybe_unused]] uint32_t stat_candidates = 0, stat_accepted = 0;
+    // pixel rectangle of this warp (tw x rows_per_warp pixels; lane = row * tw + column)
+    const float rect_x0 = float(tile_x * TS::tw);
+    const float rect_y0 = float(tile_y * TS::th + warp * TS::rows_per_warp);
+
+    // prefetch registers: Gaussian index and outline of the instance this thread stages next
+    uint32_t g_next = 0;
+    float4 c0_next = make_float4(__int_as_float(0x7f800000), 0.0f, 0.0f, 0.0f);   // "reject everything"
+    float cc_next = 0.0f;
+    if (range.x + tid < range.y) {
+        g_next = __ldg(prims_sorted + range.x + tid);
+        c0_next = ldg4(reinterpret_cast<const float*>(cull + g_next));
+        cc_next = __ldg(reinterpret_cast<const float*>(cull + g_next) + 4);
+    }
     __syncthreads();
 
     for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += TS::batch) {
@@ -173,60 +155,56 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
         } else {
             __syncthreads();
         }
-        // ---- 1. staging: one instance per thread ------------------------------------------------
-        {
-            const uint32_t inst = batch_begin + tid;
-            bool keep_any = false;
-            uint32_t keep_bits = 0;
-            uint32_t g = 0;
-            if (inst < range.y) {
-                g = __ldg(prims_sorted + inst);
-                const float4 c0 = ldg4(reinterpret_cast<const float*>(cull + g));
-                const float cc = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
-                const float x0 = float(tile_x * TS::tw), x1 = float(tile_x * TS::tw + TS::tw - 1);
-                #pragma unroll
-                for (int r = 0; r < TS::warps; ++r) {
-                    const float y0 = float(tile_y * TS::th + r * TS::rows_per_warp);
-                    const float y1 = y0 + float(TS::rows_per_warp - 1);
-                    if (outline_touches_rect(c0, cc, x0, x1, y0, y1)) keep_bits |= 1u << r;
-                }
-                keep_any = keep_bits != 0;
-                s_cull4[tid] = c0;
-                s_cullc[tid] = cc;
-            }
-            if (keep_any) {
-                mbar_arrive_expect_tx(s_bar, uint32_t(sizeof(EvalRecord)));
-                bulk_copy_g2s(s_eval + tid, eval + g, uint32_t(sizeof(EvalRecord)), s_bar);
-                if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) s_prim[tid] = g;
-            } else {
-                mbar_arrive(s_bar);
-            }
-            #pragma unroll
-            for (int r = 0; r < TS::warps; ++r) {
-                const uint32_t m = __ballot_sync(0xffffffffu, (keep_bits >> r) & 1u);
-                if (lane == 0) s_mask[r * TS::mask_words + warp] = m;
-            }
+        // ---- 1. staging: one instance per thread, from the prefetch registers ------------------------
+        const bool valid_inst = batch_begin + tid < range.y;
+        s_cull4[tid] = c0_next;
+        s_cullc[tid] = cc_next;
+        if (valid_inst) {
+            mbar_arrive_expect_tx(s_bar, uint32_t(sizeof(EvalRecord)));
+            bulk_copy_g2s(s_eval + tid, eval + g_next, uint32_t(sizeof(EvalRecord)), s_bar);
+            if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) s_prim[tid] = g_next;
+        } else {
+            mbar_arrive(s_bar);
         }
+        const uint32_t inst_next = batch_begin + TS::batch + tid;
+        const bool valid_next = inst_next < range.y;
+        if (valid_next) g_next = __ldg(prims_sorted + inst_next);
         __syncthreads();
         bool copies_landed = false;
         #pragma unroll 1
-        for (int chunk_word = 0; chunk_word < TS::mask_words; chunk_word += TS::chunk_words) {
-        // ---- 2. candidate pass: outline test per pixel, only over this warp's kept instances -----
-        uint32_t n_cand = 0;
-        if (!done) {
+        for (int chunk = 0; chunk < TS::chunks; ++chunk) {
+        // ---- 2. candidate masks: lane = Gaussian, one ballot per pixel of the warp ------------------
+        uint64_t cand = 0;
+        if (HTGS_EXPERIMENT < 3) {
             #pragma unroll
-            for (int wd = 0; wd < TS::chunk_words; ++wd) {
-                uint32_t m = s_mask[warp * TS::mask_words + chunk_word + wd];
-                while (m) {
-                    const uint32_t j = (chunk_word + wd) * 32 + (__ffs(m) - 1);
-                    m &= m - 1;
-                    const float4 c0 = s_cull4[j];
-                    const float cc = s_cullc[j];
-                    const float dx = pixel_x - c0.x, dy = pixel_y - c0.y;
-                    const float q = dx * (c0.z * dx + c0.w * dy) + cc * dy * dy;
-                    if (q <= 1.0f) { s_fifo[n_cand * TS::threads + tid] = uint8_t(j); ++n_cand; }
+            for (int half = 0; half < 2; ++half) {
+                const uint32_t j = chunk * TS::chunk + half * 32 + lane;
+                const float4 c0 = s_cull4[j];
+                const float cc = s_cullc[j];
+                const float dx0 = rect_x0 - c0.x, dy0 = rect_y0 - c0.y;
+                uint32_t mine = 0;
+                #pragma unroll
+                for (int r = 0; r < TS::rows_per_warp; ++r) {
+                    const float dy = dy0 + float(r);
+                    const float b2dy = c0.w * dy, cdy2 = cc * dy * dy;
+                    #pragma unroll
+                    for (int i = 0; i < TS::tw; ++i) {
+                        const float dx = dx0 + float(i);
+                        const float q = dx * (c0.z * dx + b2dy) + cdy2;
+                        const uint32_t touched = __ballot_sync(0xffffffffu, q <= 1.0f);
+                        if (int(lane) == r * TS::tw + i) mine = touched;
+                    }
                 }
+                cand |= uint64_t(mine) << (32 * half);
             }
+            if (done) cand = 0;
+        }
+        if (chunk == 0 && valid_next) {   // the index prefetched before the barrier has arrived by now
+            c0_next = ldg4(reinterpret_cast<const float*>(cull + g_next));
+            cc_next = __ldg(reinterpret_cast<const float*>(cull + g_next) + 4);
+        } else if (chunk == 0) {
+            c0_next = make_float4(__int_as_float(0x7f800000), 0.0f, 0.0f, 0.0f);
+            cc_next = 0.0f;
         }
         // ---- 3. exact pass ------------------------------------------------------------------------
         if (!copies_landed) {
@@ -234,11 +212,71 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
             phase ^= 1;
             copies_landed = true;
         }
+        const uint32_t n_cand = __popcll(cand);
         if constexpr (STATS) stat_candidates += n_cand;
         const uint32_t n_iter = __reduce_max_sync(0xffffffffu, n_cand);
+        const uint32_t chunk_base = chunk * TS::chunk;
+        auto pop_candidate = [&](bool& valid) -> uint32_t {
+            valid = cand != 0;
+            const uint32_t j = valid ? uint32_t(__ffsll((long long)cand) - 1) : 0u;
+            cand &= cand - 1;
+            return chunk_base + j;
+        };
+        if constexpr (MODE == HTGS_MODE_HYBRID_BLEND) {
+            // Two candidates per trip: their evaluations are independent instruction streams (the compiler
+            // interleaves them), which hides the latency of the divide / expf / dot chains; the buffer
+            // and tail updates then happen strictly in list order.
+            auto evaluate = [&](bool valid, uint32_t j, float& depth, float4& frag) -> bool {
+                const float4* rec = reinterpret_cast<const float4*>(s_eval + j);
+                const FragmentFront fr = fragment_front(rec[0], rec[1], rec[2], pixel_x, pixel_y);
+                const float numerator_rho2 = fr.numerator_rho2;
+                const float denominator = fr.denominator;
+                const bool inside_cutoff = !(numerator_rho2 > MT::max_cutoff_sq * denominator);
+                const float denominator_rcp = 1.0f / denominator;
+                const float4 rgba_in = rec[4];
+                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
+                const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
+                const float4 MT3 = rec[3];
+                depth = dot(f3(MT3), eval_point_diag) + MT3.w;
+                frag = make_float4(rgba_in.x * alpha, rgba_in.y * alpha, rgba_in.z * alpha, alpha);
+                return valid && inside_cutoff && !(alpha < MT::min_alpha);
+            };
+            auto commit = [&](float depth, float4 frag) {
+                if constexpr (STATS) ++stat_accepted;
+                if (HTGS_EXPERIMENT != 1 && depth < kd[K - 1] && frag.w >= MT::min_alpha_core) {
+                    pool4[free_slot * TS::threads + tid] = frag;
+                    uint32_t slot = free_slot;
+                    #pragma unroll
+                    for (int k = 0; k < K; ++k) {
+                        if (depth < kd[k]) {
+                            const float td = kd[k]; kd[k] = depth; depth = td;
+                            const uint32_t ts = ks[k]; ks[k] = slot; slot = ts;
+                        }
+                    }
+                    free_slot = slot;                                 // whatever fell out of the chain (a real fragment or an empty entry)
+                    frag = pool4[slot * TS::threads + tid];
+                }
+                acc += frag;
+                if (!use_median_depth) acc_depth += depth * frag.w;
+                transmittance *= 1.0f - frag.w;
+            };
+            for (uint32_t it = 0; it < (HTGS_EXPERIMENT >= 2 ? 0u : n_iter); it += 2) {
+                bool v0, v1;
+                const uint32_t j0 = pop_candidate(v0);
+                const uint32_t j1 = pop_candidate(v1);
+                float depth0, depth1;
+                float4 frag0, frag1;
+                const bool ok0 = evaluate(v0, j0, depth0, frag0);
+                const bool ok1 = evaluate(v1, j1, depth1, frag1);
+                if (ok0) commit(depth0, frag0);
+                if (ok1) commit(depth1, frag1);
+            }
+        } else
         for (uint32_t it = 0; it < n_iter; ++it) {
-            if (it >= n_cand || done) continue;
-            const uint32_t j = s_fifo[it * TS::threads + tid];
+            bool valid;
+            const uint32_t j = pop_candidate(valid);
+            if (!valid || done) continue;
             const float4* rec = reinterpret_cast<const float4*>(s_eval + j);
             const FragmentFront fr = fragment_front(rec[0], rec[1], rec[2], pixel_x, pixel_y);
             const float numerator_rho2 = fr.numerator_rho2;
