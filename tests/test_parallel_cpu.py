@@ -1,0 +1,80 @@
+"""CPU: the multi-rank host logic (view partitioning, gradient all-reduce, max-over-ranks timing) with two
+gloo ranks; plus a host-side failure case (a rank that never joins makes the collective time out with an error)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from htgs_b200 import parallel
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def test_view_partition_is_disjoint_and_complete():
+    for world in (1, 2, 4, 8):
+        seen = []
+        for rank in range(world):
+            seen += parallel.shard_views(200, rank, world)
+        assert sorted(seen) == list(range(200))
+        step = [v for r in range(world) for v in parallel.step_view_indices(3, 8, r, world, 200)]
+        assert len(set(step)) == 8 * world, "ranks must render different views inside a step"
+    with pytest.raises(ValueError):
+        parallel.shard_views(10, 2, 2)
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist = parallel.init_process_group("gloo")
+    n = 1000
+    grads = [torch.full((n, 3), float(rank + 1)), torch.full((n, 15, 3), float(10 * (rank + 1))), None]
+    parallel.allreduce_gradients(grads)
+    ok = bool((grads[0] == 3.0).all() and (grads[1] == 30.0).all())
+    slowest = parallel.max_over_ranks(5.0 + rank)
+    total = parallel.sum_over_ranks(float(len(parallel.step_view_indices(0, 8, rank, world, 200))))
+    out.put((rank, ok, slowest, total))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_allreduce_and_timing_reduction_two_gloo_ranks():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok, slowest, total in results:
+        assert ok and slowest == 6.0 and total == 16.0
+
+
+def _lonely_worker(port, out):
+    import datetime
+    import torch.distributed as dist
+    os.environ.update(RANK="0", WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    try:
+        dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=3))
+        out.put("joined")
+    except Exception as e:   # the peer never joins: rendezvous times out on the host, nothing hangs
+        out.put("error:" + type(e).__name__)
+
+
+def test_missing_rank_is_reported_not_hung():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    p = ctx.Process(target=_lonely_worker, args=(_free_port(), out))
+    p.start()
+    msg = out.get(timeout=120)
+    p.join(timeout=60)
+    assert msg.startswith("error:")
