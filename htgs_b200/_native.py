@@ -57,7 +57,7 @@ class HtgsIntermediates(ctypes.Structure):
     ]
 
 
-class HtgsTrainState(ctypes.Structure):
+class HtgsTrainBlobs(ctypes.Structure):
     _fields_ = [
         ("per_primitive", ctypes.c_void_p), ("per_primitive_bytes", ctypes.c_size_t),
         ("per_tile", ctypes.c_void_p), ("per_tile_bytes", ctypes.c_size_t),
@@ -71,7 +71,7 @@ class HtgsGradients(ctypes.Structure):
         ("grad_positions", ctypes.c_void_p), ("grad_scales", ctypes.c_void_p), ("grad_rotations", ctypes.c_void_p),
         ("grad_opacities", ctypes.c_void_p), ("grad_sh_0", ctypes.c_void_p), ("grad_sh_rest", ctypes.c_void_p),
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
-        ("densification_info", ctypes.c_void_p), ("densification_rows", ctypes.c_int32),
+        ("densification_info", ctypes.c_void_p), ("densification_rows", ctypes.c_int32), ("use_distance_scaling", ctypes.c_int32),
     ]
 
 
@@ -111,6 +111,18 @@ def lib():
                                                ctypes.c_int, ctypes.c_int, ctypes.POINTER(HtgsFrameInfo)]
                 l.htgs_get_intermediates.restype = ctypes.c_int
                 l.htgs_get_intermediates.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsIntermediates)]
+                l.htgs_forward_blob_sizes.argtypes = [ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(ctypes.c_size_t),
+                                                      ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
+                l.htgs_forward_instance_bytes.restype = ctypes.c_size_t
+                l.htgs_forward_instance_bytes.argtypes = [ctypes.POINTER(HtgsView), ctypes.c_uint64]
+                l.htgs_forward_begin.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_size_t,
+                                                 ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint32)]
+                l.htgs_forward_finish.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(HtgsTrainBlobs),
+                                                  ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(HtgsFrameInfo)]
+                l.htgs_backward_scratch_bytes.restype = ctypes.c_size_t
+                l.htgs_backward_scratch_bytes.argtypes = [ctypes.POINTER(HtgsScene)]
+                l.htgs_backward.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(HtgsTrainBlobs),
+                                            ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(HtgsGradients), ctypes.c_void_p]
                 l.htgs_set_profiling.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_set_collect_stats.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_get_stage_ms.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]

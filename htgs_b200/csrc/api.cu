@@ -193,7 +193,7 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
     if ((err = launch_emit_sort_ranges(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream,
                                        prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "binning");
     const uint32_t* prims_sorted = L.inst.prims[plan.final_buffer];
-    if ((err = launch_blend_inference(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, out, L.status, ctx->sm_count, stream)) != cudaSuccess) return fail_cuda(err, "blend");
+    if ((err = launch_blend(view.mode, view.K, false, geo, L.prim, prims_sorted, L.tile_ranges, out, TrainPixelBuffers{}, L.status, stream)) != cudaSuccess) return fail_cuda(err, "blend");
     *launches += 1;
     if (prof) cudaEventRecord(ev[6], stream);
     if ((err = cudaMemcpyAsync(ctx->host_status, L.status, sizeof(FrameStatus), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return fail_cuda(err, "status copy");
@@ -373,6 +373,186 @@ int htgs_memcpy_h2d(void* device_dst, const void* host_src, size_t bytes) {
     if (bytes == 0) return HTGS_OK;
     const cudaError_t err = cudaMemcpy(device_dst, host_src, bytes, cudaMemcpyHostToDevice);
     return err == cudaSuccess ? HTGS_OK : fail_cuda(err, "cudaMemcpy H2D");
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// training forward / backward
+// ---------------------------------------------------------------------------------------------------
+namespace {
+
+struct PrimLayout { FrameStatus* status; PrimBuffers prim; size_t bytes; };
+PrimLayout carve_primitive_blob(void* blob, int n_primitives) {
+    PrimLayout L{};
+    Carver c(blob);
+    const size_t n = size_t(n_primitives);
+    const size_t prim_blocks = (n + kPreprocessBlock - 1) / kPreprocessBlock;
+    L.status = c.take<FrameStatus>(1);
+    L.prim.n_touched = c.take<uint32_t>(n);
+    L.prim.bounds = c.take<ushort4>(n);
+    L.prim.eval = c.take<EvalRecord>(n);
+    L.prim.cull = c.take<CullRecord>(n);
+    L.prim.clamp = c.take<uint8_t>(n);
+    L.prim.block_sums = c.take<uint32_t>(prim_blocks + 1);
+    L.prim.block_offsets = c.take<uint32_t>(prim_blocks + 1);
+    L.bytes = align_up(c.offset);
+    return L;
+}
+
+struct InstLayout { InstBuffers inst; size_t bytes; };
+InstLayout carve_instance_blob(void* blob, const SortPlan& plan, uint64_t capacity) {
+    InstLayout L{};
+    Carver c(blob);
+    const uint64_t cap = capacity > 0xfffffff0ull ? 0xfffffff0ull : capacity;
+    L.inst.capacity = uint32_t(cap);
+    L.inst.sort_blocks_cap = uint32_t((cap + kSortTile - 1) / kSortTile);
+    L.inst.keys[0] = c.take_bytes<void>(size_t(cap) * plan.key_bytes);
+    L.inst.keys[1] = c.take_bytes<void>(size_t(cap) * plan.key_bytes);
+    L.inst.prims[0] = c.take<uint32_t>(size_t(cap));
+    L.inst.prims[1] = c.take<uint32_t>(size_t(cap));
+    L.inst.radix_table = c.take<uint32_t>(size_t(kMaxRadixBins) * (L.inst.sort_blocks_cap + 1));
+    L.inst.digit_totals = c.take<uint32_t>(kMaxRadixBins);
+    L.bytes = align_up(c.offset);
+    return L;
+}
+
+struct PixelLayout { TrainPixelBuffers px; size_t bytes; };
+PixelLayout carve_pixel_blob(void* blob, int mode, int K, const FrameGeometry& geo) {
+    PixelLayout L{};
+    Carver c(blob);
+    const size_t PP = size_t(geo.n_tiles) * geo.tile_w * geo.tile_h;
+    const size_t k = size_t(effective_k(mode, K));
+    L.px.padded_pixels = uint32_t(PP);
+    if (mode == HTGS_MODE_HYBRID_BLEND || mode == HTGS_MODE_ALPHA_BLEND_FIRST_K) {
+        L.px.idx_core = c.take<uint32_t>(k * PP);
+        L.px.info_core = c.take<float4>(k * PP);
+    }
+    if (mode == HTGS_MODE_HYBRID_BLEND) L.px.info_tail = c.take<float>(6 * PP);
+    if (mode == HTGS_MODE_OIT_BLEND) L.px.info_tail = c.take<float>(5 * PP);
+    L.bytes = align_up(c.offset + 1);
+    return L;
+}
+
+int set_device_of(HtgsContext* ctx) {
+    int current = -1;
+    cudaGetDevice(&current);
+    if (current != ctx->device) {
+        const cudaError_t err = cudaSetDevice(ctx->device);
+        if (err != cudaSuccess) return fail_cuda(err, "cudaSetDevice");
+    }
+    return HTGS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int htgs_forward_blob_sizes(const HtgsScene* scene, const HtgsView* view, size_t* per_primitive_bytes, size_t* per_tile_bytes, size_t* per_pixel_bytes) {
+    const int rc = validate(scene, view);
+    if (rc != HTGS_OK) return rc;
+    const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
+    if (per_primitive_bytes) *per_primitive_bytes = carve_primitive_blob(nullptr, scene->n_primitives).bytes;
+    if (per_tile_bytes) *per_tile_bytes = align_up(sizeof(uint2) * size_t(geo.n_tiles) + 1);
+    if (per_pixel_bytes) *per_pixel_bytes = carve_pixel_blob(nullptr, view->mode, view->K, geo).bytes;
+    return HTGS_OK;
+}
+
+size_t htgs_forward_instance_bytes(const HtgsView* view, uint64_t n_instances) {
+    if (!view || view->mode < 0 || view->mode > 3 || view->width <= 0 || view->height <= 0) return 0;
+    const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
+    return carve_instance_blob(nullptr, make_sort_plan(view->mode, geo.n_tiles), n_instances).bytes;
+}
+
+int htgs_forward_begin(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, void* per_primitive, size_t per_primitive_bytes,
+                       void* stream_ptr, uint32_t* n_instances) {
+    if (!ctx || !n_instances) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    int rc = validate(scene, view);
+    if (rc != HTGS_OK) return rc;
+    if ((rc = set_device_of(ctx)) != HTGS_OK) return rc;
+    const PrimLayout L = carve_primitive_blob(per_primitive, scene->n_primitives);
+    if (!per_primitive || per_primitive_bytes < L.bytes) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "per-primitive blob too small");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
+    cudaError_t err;
+    if ((err = cudaMemsetAsync(L.status, 0, sizeof(FrameStatus), stream)) != cudaSuccess) return fail_cuda(err, "status reset");
+    if ((err = launch_preprocess(view->mode, true, *scene, *view, geo, L.prim, L.status, stream)) != cudaSuccess) return fail_cuda(err, "preprocess");
+    if ((err = launch_scan_only(*scene, L.prim, 0xfffffff0u, L.status, stream)) != cudaSuccess) return fail_cuda(err, "scan");
+    if ((err = cudaMemcpyAsync(ctx->host_status, L.status, sizeof(FrameStatus), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return fail_cuda(err, "status copy");
+    if ((err = cudaStreamSynchronize(stream)) != cudaSuccess) return fail_cuda(err, "synchronise");
+    if (ctx->host_status->overflow) return fail(HTGS_ERR_INVALID_ARGUMENT, "instance count does not fit 32 bits");
+    *n_instances = ctx->host_status->n_instances;
+    return HTGS_OK;
+}
+
+int htgs_forward_finish(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                        float* image, void* stream_ptr, HtgsFrameInfo* info) {
+    if (!ctx || !blobs || !image) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    int rc = validate(scene, view);
+    if (rc != HTGS_OK) return rc;
+    if ((rc = set_device_of(ctx)) != HTGS_OK) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
+    const SortPlan plan = make_sort_plan(view->mode, geo.n_tiles);
+    const PrimLayout P = carve_primitive_blob(blobs->per_primitive, scene->n_primitives);
+    const InstLayout I = carve_instance_blob(blobs->per_instance, plan, n_instances);
+    const PixelLayout X = carve_pixel_blob(blobs->per_pixel, view->mode, view->K, geo);
+    if (!blobs->per_primitive || blobs->per_primitive_bytes < P.bytes || !blobs->per_instance || blobs->per_instance_bytes < I.bytes ||
+        !blobs->per_pixel || blobs->per_pixel_bytes < X.bytes || !blobs->per_tile || blobs->per_tile_bytes < sizeof(uint2) * size_t(geo.n_tiles))
+        return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "a forward blob is missing or too small");
+    uint2* tile_ranges = static_cast<uint2*>(blobs->per_tile);
+    uint32_t launches = 0;
+    cudaError_t err;
+    if ((err = launch_emit_sort_ranges(view->mode, *scene, geo, plan, P.prim, I.inst, tile_ranges, P.status, ctx->sm_count, stream, nullptr, &launches)) != cudaSuccess)
+        return fail_cuda(err, "binning");
+    const BlendOutputs out{image, nullptr, nullptr, true, false, false};
+    if ((err = launch_blend(view->mode, view->K, true, geo, P.prim, I.inst.prims[plan.final_buffer], tile_ranges, out, X.px, P.status, stream)) != cudaSuccess)
+        return fail_cuda(err, "blend");
+    if ((err = cudaMemcpyAsync(ctx->host_status, P.status, sizeof(FrameStatus), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return fail_cuda(err, "status copy");
+    if ((err = cudaStreamSynchronize(stream)) != cudaSuccess) return fail_cuda(err, "synchronise");
+    const FrameStatus st = *ctx->host_status;
+    if (info) {
+        std::memset(info, 0, sizeof(*info));
+        info->n_instances = st.n_instances; info->n_visible = st.n_visible; info->key_bytes = uint32_t(plan.key_bytes); info->end_bit = uint32_t(plan.end_bit);
+        info->device_error = st.error; info->kernel_launches = launches + 3;
+    }
+    if (st.error) return fail(HTGS_ERR_DEVICE_FLAG, "a kernel reported an internal error (bounded wait gave up)");
+    return HTGS_OK;
+}
+
+size_t htgs_backward_scratch_bytes(const HtgsScene* scene) {
+    return scene ? align_up(size_t(scene->n_primitives > 0 ? scene->n_primitives : 0) * 5 * sizeof(float4) + 1) : 0;
+}
+
+int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                  const float* grad_image, const float* image, const HtgsGradients* grads, void* stream_ptr) {
+    if (!ctx || !blobs || !grads || !grad_image) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    int rc = validate(scene, view);
+    if (rc != HTGS_OK) return rc;
+    if ((rc = set_device_of(ctx)) != HTGS_OK) return rc;
+    if (view->mode == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING && !image) return fail(HTGS_ERR_INVALID_ARGUMENT, "ALPHA_BLEND_GLOBAL_ORDERING needs the forward image");
+    if (scene->n_primitives > 0 && (!grads->grad_positions || !grads->grad_scales || !grads->grad_rotations || !grads->grad_opacities || !grads->grad_sh_0 ||
+                                    (scene->total_sh_bases > 0 && !grads->grad_sh_rest)))
+        return fail(HTGS_ERR_INVALID_ARGUMENT, "gradient output pointers must not be null");
+    if (!grads->scratch || grads->scratch_bytes < htgs_backward_scratch_bytes(scene)) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "backward scratch too small");
+    if (grads->densification_info && grads->densification_rows != 2 && grads->densification_rows != 3)
+        return fail(HTGS_ERR_INVALID_ARGUMENT, "densification_info must have 2 or 3 rows");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
+    const SortPlan plan = make_sort_plan(view->mode, geo.n_tiles);
+    const PrimLayout P = carve_primitive_blob(blobs->per_primitive, scene->n_primitives);
+    const InstLayout I = carve_instance_blob(blobs->per_instance, plan, n_instances);
+    const PixelLayout X = carve_pixel_blob(blobs->per_pixel, view->mode, view->K, geo);
+    if (!blobs->per_primitive || blobs->per_primitive_bytes < P.bytes || !blobs->per_instance || blobs->per_instance_bytes < I.bytes ||
+        !blobs->per_pixel || blobs->per_pixel_bytes < X.bytes || !blobs->per_tile)
+        return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "a forward blob is missing or too small");
+    const GradAccumBuffers acc{static_cast<float4*>(grads->scratch)};
+    const BackwardOutputs out{grads->grad_positions, grads->grad_scales, grads->grad_rotations, grads->grad_opacities, grads->grad_sh_0, grads->grad_sh_rest,
+                              grads->densification_info, grads->densification_info ? grads->densification_rows : 0, grads->use_distance_scaling != 0};
+    const cudaError_t err = launch_backward(view->mode, view->K, *scene, *view, geo, P.prim, I.inst.prims[plan.final_buffer], static_cast<const uint2*>(blobs->per_tile),
+                                            X.px, grad_image, image, acc, out, ctx->sm_count, stream);
+    if (err != cudaSuccess) return fail_cuda(err, "backward");
+    return HTGS_OK;
 }
 
 }  // extern "C"

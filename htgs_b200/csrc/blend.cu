@@ -47,9 +47,11 @@ template <int MODE> struct TileShape {
     static constexpr int chunks = batch / chunk;
 };
 
-template <int MODE, int K> struct SmemLayout {
+template <int MODE, int K, bool TRAIN> struct SmemLayout {
     using TS = TileShape<MODE>;
     static constexpr bool has_kbuffer = (MODE == HTGS_MODE_HYBRID_BLEND || MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K);
+    static constexpr bool has_prim = (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) || (MODE == HTGS_MODE_HYBRID_BLEND && TRAIN);
+    static constexpr bool has_pool_idx = (MODE == HTGS_MODE_HYBRID_BLEND && TRAIN);
     static constexpr int pool_elem = (MODE == HTGS_MODE_HYBRID_BLEND) ? 16 : (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K ? 8 : 0);
     static constexpr size_t eval_off = 0;
     static constexpr size_t eval_bytes = size_t(TS::batch) * sizeof(EvalRecord);
@@ -58,11 +60,13 @@ template <int MODE, int K> struct SmemLayout {
     static constexpr size_t cullc_off = cull4_off + cull4_bytes;
     static constexpr size_t cullc_bytes = size_t(TS::batch) * 4;
     static constexpr size_t prim_off = cullc_off + cullc_bytes;
-    static constexpr size_t prim_bytes = (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) ? size_t(TS::batch) * 4 : 0;
+    static constexpr size_t prim_bytes = has_prim ? size_t(TS::batch) * 4 : 0;
     static constexpr size_t bar_off = (prim_off + prim_bytes + 15) & ~size_t(15);
     static constexpr size_t pool_off = bar_off + 16;
     static constexpr size_t pool_bytes = has_kbuffer ? size_t(K + 1) * TS::threads * pool_elem : 0;
-    static constexpr size_t total = pool_off + pool_bytes;
+    static constexpr size_t pool_idx_off = pool_off + pool_bytes;
+    static constexpr size_t pool_idx_bytes = has_pool_idx ? size_t(K + 1) * TS::threads * 4 : 0;
+    static constexpr size_t total = pool_idx_off + pool_idx_bytes;
 };
 
 // The shared per-fragment front end (hybrid_blend/kernels/inference.cuh:137-148).
@@ -83,15 +87,32 @@ __device__ __forceinline__ FragmentFront fragment_front(const float4& VPMT1, con
     return f;
 }
 
-template <int MODE, int K, bool STATS>
-__global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kernel(
+// The reference's insertion chain (hybrid_blend/kernels/inference.cuh:159-167) on (depth, slot) pairs.
+// On return `depth` is the depth of the entry that fell out of the buffer and the result its slot.
+template <int K>
+__device__ __forceinline__ uint32_t kbuffer_insert(float (&kd)[K], uint32_t (&ks)[K], float& depth, uint32_t slot) {
+    #pragma unroll
+    for (int k = 0; k < K; ++k) {
+        if (depth < kd[k]) {
+            const float td = kd[k]; kd[k] = depth; depth = td;
+            const uint32_t ts = ks[k]; ks[k] = slot; slot = ts;
+        }
+    }
+    return slot;
+}
+
+template <int MODE, int K, bool TRAIN, bool STATS>
+__global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
     const CullRecord* __restrict__ cull, float* __restrict__ image, float* __restrict__ depth_out, float* __restrict__ alpha_out,
-    uint32_t width, uint32_t height, uint32_t grid_w, bool to_chw, bool use_median_depth, FrameStatus* status)
+    TrainPixelBuffers tout, uint32_t width, uint32_t height, uint32_t grid_w, bool to_chw, bool use_median_depth, FrameStatus* status)
 {
     using MT = ModeTraits<MODE>;
     using TS = TileShape<MODE>;
-    using SL = SmemLayout<MODE, K>;
+    using SL = SmemLayout<MODE, K, TRAIN>;
+    constexpr bool kHybrid = MODE == HTGS_MODE_HYBRID_BLEND;
+    constexpr bool kFirstK = MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K;
+    constexpr bool kGlobal = MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING;
     extern __shared__ __align__(128) unsigned char smem[];
     EvalRecord* s_eval = reinterpret_cast<EvalRecord*>(smem + SL::eval_off);
     float4* s_cull4 = reinterpret_cast<float4*>(smem + SL::cull4_off);
@@ -115,13 +136,15 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
     [[maybe_unused]] uint32_t ks[SL::has_kbuffer ? K : 1];
     [[maybe_unused]] float4* pool4 = reinterpret_cast<float4*>(smem + SL::pool_off);
     [[maybe_unused]] float2* pool2 = reinterpret_cast<float2*>(smem + SL::pool_off);
+    [[maybe_unused]] uint32_t* pool_idx = reinterpret_cast<uint32_t*>(smem + SL::pool_idx_off);
     [[maybe_unused]] uint32_t free_slot = K;
     if constexpr (SL::has_kbuffer) {
         #pragma unroll
         for (int k = 0; k < K; ++k) {
             kd[k] = FLT_MAX; ks[k] = k;
-            if constexpr (MODE == HTGS_MODE_HYBRID_BLEND) pool4[k * TS::threads + tid] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if constexpr (kHybrid) pool4[k * TS::threads + tid] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             else pool2[k * TS::threads + tid] = make_float2(0.0f, __uint_as_float(0xffffffffu));
+            if constexpr (SL::has_pool_idx) pool_idx[k * TS::threads + tid] = 0xffffffffu;
         }
     }
     // HYBRID tail / OIT accumulators / GLOBAL_ORDERING running blend
@@ -150,7 +173,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
     __syncthreads();
 
     for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += TS::batch) {
-        if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) {
+        if constexpr (kGlobal) {
             if (__syncthreads_count(done) == TS::threads) break;
         } else {
             __syncthreads();
@@ -162,7 +185,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
         if (valid_inst) {
             mbar_arrive_expect_tx(s_bar, uint32_t(sizeof(EvalRecord)));
             bulk_copy_g2s(s_eval + tid, eval + g_next, uint32_t(sizeof(EvalRecord)), s_bar);
-            if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) s_prim[tid] = g_next;
+            if constexpr (SL::has_prim) s_prim[tid] = g_next;
         } else {
             mbar_arrive(s_bar);
         }
@@ -173,190 +196,165 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
         bool copies_landed = false;
         #pragma unroll 1
         for (int chunk = 0; chunk < TS::chunks; ++chunk) {
-        // ---- 2. candidate masks: lane = Gaussian, one ballot per pixel of the warp ------------------
-        uint64_t cand = 0;
-        if (HTGS_EXPERIMENT < 3) {
-            #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const uint32_t j = chunk * TS::chunk + half * 32 + lane;
-                const float4 c0 = s_cull4[j];
-                const float cc = s_cullc[j];
-                const float dx0 = rect_x0 - c0.x, dy0 = rect_y0 - c0.y;
-                uint32_t mine = 0;
+            // ---- 2. candidate masks: lane = Gaussian, one ballot per pixel of the warp --------------
+            uint64_t cand = 0;
+            if (HTGS_EXPERIMENT < 3) {
                 #pragma unroll
-                for (int r = 0; r < TS::rows_per_warp; ++r) {
-                    const float dy = dy0 + float(r);
-                    const float b2dy = c0.w * dy, cdy2 = cc * dy * dy;
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t j = chunk * TS::chunk + half * 32 + lane;
+                    const float4 c0 = s_cull4[j];
+                    const float cc = s_cullc[j];
+                    const float dx0 = rect_x0 - c0.x, dy0 = rect_y0 - c0.y;
+                    uint32_t mine = 0;
                     #pragma unroll
-                    for (int i = 0; i < TS::tw; ++i) {
-                        const float dx = dx0 + float(i);
-                        const float q = dx * (c0.z * dx + b2dy) + cdy2;
-                        const uint32_t touched = __ballot_sync(0xffffffffu, q <= 1.0f);
-                        if (int(lane) == r * TS::tw + i) mine = touched;
-                    }
-                }
-                cand |= uint64_t(mine) << (32 * half);
-            }
-            if (done) cand = 0;
-        }
-        if (chunk == 0 && valid_next) {   // the index prefetched before the barrier has arrived by now
-            c0_next = ldg4(reinterpret_cast<const float*>(cull + g_next));
-            cc_next = __ldg(reinterpret_cast<const float*>(cull + g_next) + 4);
-        } else if (chunk == 0) {
-            c0_next = make_float4(__int_as_float(0x7f800000), 0.0f, 0.0f, 0.0f);
-            cc_next = 0.0f;
-        }
-        // ---- 3. exact pass ------------------------------------------------------------------------
-        if (!copies_landed) {
-            if (!mbar_wait_bounded(s_bar, phase)) wait_failed = true;
-            phase ^= 1;
-            copies_landed = true;
-        }
-        const uint32_t n_cand = __popcll(cand);
-        if constexpr (STATS) stat_candidates += n_cand;
-        const uint32_t n_iter = __reduce_max_sync(0xffffffffu, n_cand);
-        const uint32_t chunk_base = chunk * TS::chunk;
-        auto pop_candidate = [&](bool& valid) -> uint32_t {
-            valid = cand != 0;
-            const uint32_t j = valid ? uint32_t(__ffsll((long long)cand) - 1) : 0u;
-            cand &= cand - 1;
-            return chunk_base + j;
-        };
-        if constexpr (MODE == HTGS_MODE_HYBRID_BLEND) {
-            // Two candidates per trip: their evaluations are independent instruction streams (the compiler
-            // interleaves them), which hides the latency of the divide / expf / dot chains; the buffer
-            // and tail updates then happen strictly in list order.
-            auto evaluate = [&](bool valid, uint32_t j, float& depth, float4& frag) -> bool {
-                const float4* rec = reinterpret_cast<const float4*>(s_eval + j);
-                const FragmentFront fr = fragment_front(rec[0], rec[1], rec[2], pixel_x, pixel_y);
-                const float numerator_rho2 = fr.numerator_rho2;
-                const float denominator = fr.denominator;
-                const bool inside_cutoff = !(numerator_rho2 > MT::max_cutoff_sq * denominator);
-                const float denominator_rcp = 1.0f / denominator;
-                const float4 rgba_in = rec[4];
-                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
-                const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
-                const float4 MT3 = rec[3];
-                depth = dot(f3(MT3), eval_point_diag) + MT3.w;
-                frag = make_float4(rgba_in.x * alpha, rgba_in.y * alpha, rgba_in.z * alpha, alpha);
-                return valid && inside_cutoff && !(alpha < MT::min_alpha);
-            };
-            auto commit = [&](float depth, float4 frag) {
-                if constexpr (STATS) ++stat_accepted;
-                if (HTGS_EXPERIMENT != 1 && depth < kd[K - 1] && frag.w >= MT::min_alpha_core) {
-                    pool4[free_slot * TS::threads + tid] = frag;
-                    uint32_t slot = free_slot;
-                    #pragma unroll
-                    for (int k = 0; k < K; ++k) {
-                        if (depth < kd[k]) {
-                            const float td = kd[k]; kd[k] = depth; depth = td;
-                            const uint32_t ts = ks[k]; ks[k] = slot; slot = ts;
+                    for (int r = 0; r < TS::rows_per_warp; ++r) {
+                        const float dy = dy0 + float(r);
+                        const float b2dy = c0.w * dy, cdy2 = cc * dy * dy;
+                        #pragma unroll
+                        for (int i = 0; i < TS::tw; ++i) {
+                            const float dx = dx0 + float(i);
+                            const float q = dx * (c0.z * dx + b2dy) + cdy2;
+                            const uint32_t touched = __ballot_sync(0xffffffffu, q <= 1.0f);
+                            if (int(lane) == r * TS::tw + i) mine = touched;
                         }
                     }
-                    free_slot = slot;                                 // whatever fell out of the chain (a real fragment or an empty entry)
-                    frag = pool4[slot * TS::threads + tid];
+                    cand |= uint64_t(mine) << (32 * half);
                 }
-                acc += frag;
-                if (!use_median_depth) acc_depth += depth * frag.w;
-                transmittance *= 1.0f - frag.w;
+                if (done) cand = 0;
+            }
+            if (chunk == 0) {   // the index prefetched before the barrier has arrived by now
+                if (valid_next) {
+                    c0_next = ldg4(reinterpret_cast<const float*>(cull + g_next));
+                    cc_next = __ldg(reinterpret_cast<const float*>(cull + g_next) + 4);
+                } else {
+                    c0_next = make_float4(__int_as_float(0x7f800000), 0.0f, 0.0f, 0.0f);
+                    cc_next = 0.0f;
+                }
+            }
+            // ---- 3. exact pass ------------------------------------------------------------------------
+            if (!copies_landed) {
+                if (!mbar_wait_bounded(s_bar, phase)) wait_failed = true;
+                phase ^= 1;
+                copies_landed = true;
+            }
+            const uint32_t n_cand = __popcll(cand);
+            if constexpr (STATS) stat_candidates += n_cand;
+            const uint32_t n_iter = __reduce_max_sync(0xffffffffu, n_cand);
+            const uint32_t chunk_base = chunk * TS::chunk;
+            auto pop_candidate = [&](bool& valid) -> uint32_t {
+                valid = cand != 0;
+                const uint32_t j = valid ? uint32_t(__ffsll((long long)cand) - 1) : 0u;
+                cand &= cand - 1;
+                return chunk_base + j;
             };
-            for (uint32_t it = 0; it < (HTGS_EXPERIMENT >= 2 ? 0u : n_iter); it += 2) {
-                bool v0, v1;
-                const uint32_t j0 = pop_candidate(v0);
-                const uint32_t j1 = pop_candidate(v1);
-                float depth0, depth1;
-                float4 frag0, frag1;
-                const bool ok0 = evaluate(v0, j0, depth0, frag0);
-                const bool ok1 = evaluate(v1, j1, depth1, frag1);
-                if (ok0) commit(depth0, frag0);
-                if (ok1) commit(depth1, frag1);
-            }
-        } else
-        for (uint32_t it = 0; it < n_iter; ++it) {
-            bool valid;
-            const uint32_t j = pop_candidate(valid);
-            if (!valid || done) continue;
-            const float4* rec = reinterpret_cast<const float4*>(s_eval + j);
-            const FragmentFront fr = fragment_front(rec[0], rec[1], rec[2], pixel_x, pixel_y);
-            const float numerator_rho2 = fr.numerator_rho2;
-            const float denominator = fr.denominator;
-            if (numerator_rho2 > MT::max_cutoff_sq * denominator) continue;
-            const float denominator_rcp = 1.0f / denominator;
-
-            if constexpr (MODE == HTGS_MODE_HYBRID_BLEND) {
-                const float4 rgba_in = rec[4];
-                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
-                if (alpha < MT::min_alpha) continue;
-                if constexpr (STATS) ++stat_accepted;
-                const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
-                const float4 MT3 = rec[3];
-                float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
-                float4 frag = make_float4(rgba_in.x * alpha, rgba_in.y * alpha, rgba_in.z * alpha, alpha);
-                if (depth < kd[K - 1] && alpha >= MT::min_alpha_core) {
-                    pool4[free_slot * TS::threads + tid] = frag;
-                    uint32_t slot = free_slot;
-                    #pragma unroll
-                    for (int k = 0; k < K; ++k) {
-                        if (depth < kd[k]) {
-                            const float td = kd[k]; kd[k] = depth; depth = td;
-                            const uint32_t ts = ks[k]; ks[k] = slot; slot = ts;
+            if constexpr (kHybrid) {
+                // Two candidates per trip: their evaluations are independent instruction streams (the compiler
+                // interleaves them), which hides the latency of the divide / expf / dot chains; the buffer
+                // and tail updates then happen strictly in list order.
+                // Inference keeps premultiplied colours in the buffer (inference.cuh:158), the training forward
+                // keeps (rgb, alpha) and the Gaussian index (forward.cuh:159-171).
+                auto evaluate = [&](bool valid, uint32_t j, float& depth, float4& frag) -> bool {
+                    const float4* rec = reinterpret_cast<const float4*>(s_eval + j);
+                    const FragmentFront fr = fragment_front(rec[0], rec[1], rec[2], pixel_x, pixel_y);
+                    const float numerator_rho2 = fr.numerator_rho2;
+                    const float denominator = fr.denominator;
+                    const bool inside_cutoff = !(numerator_rho2 > MT::max_cutoff_sq * denominator);
+                    const float denominator_rcp = 1.0f / denominator;
+                    const float4 rgba_in = rec[4];
+                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                    const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
+                    const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
+                    const float4 MT3 = rec[3];
+                    depth = dot(f3(MT3), eval_point_diag) + MT3.w;
+                    if constexpr (TRAIN) frag = make_float4(rgba_in.x, rgba_in.y, rgba_in.z, alpha);
+                    else frag = make_float4(rgba_in.x * alpha, rgba_in.y * alpha, rgba_in.z * alpha, alpha);
+                    return valid && inside_cutoff && !(alpha < MT::min_alpha);
+                };
+                auto commit = [&](float depth, float4 frag, uint32_t j) {
+                    if constexpr (STATS) ++stat_accepted;
+                    if (HTGS_EXPERIMENT != 1 && depth < kd[K - 1] && frag.w >= MT::min_alpha_core) {
+                        pool4[free_slot * TS::threads + tid] = frag;
+                        if constexpr (TRAIN) pool_idx[free_slot * TS::threads + tid] = s_prim[j];
+                        free_slot = kbuffer_insert<K>(kd, ks, depth, free_slot);   // the entry that fell out: a real fragment or an empty one
+                        frag = pool4[free_slot * TS::threads + tid];
+                    }
+                    if constexpr (TRAIN) {
+                        acc += make_float4(frag.x * frag.w, frag.y * frag.w, frag.z * frag.w, frag.w);
+                    } else {
+                        acc += frag;
+                        if (!use_median_depth) acc_depth += depth * frag.w;
+                    }
+                    transmittance *= 1.0f - frag.w;
+                };
+                for (uint32_t it = 0; it < (HTGS_EXPERIMENT >= 2 ? 0u : n_iter); it += 2) {
+                    bool v0, v1;
+                    const uint32_t j0 = pop_candidate(v0);
+                    const uint32_t j1 = pop_candidate(v1);
+                    float depth0, depth1;
+                    float4 frag0, frag1;
+                    const bool ok0 = evaluate(v0, j0, depth0, frag0);
+                    const bool ok1 = evaluate(v1, j1, depth1, frag1);
+                    if (ok0) commit(depth0, frag0, j0);
+                    if (ok1) commit(depth1, frag1, j1);
+                }
+            } else {
+                for (uint32_t it = 0; it < n_iter; ++it) {
+                    bool valid;
+                    const uint32_t j = pop_candidate(valid);
+                    if (!valid || done) continue;
+                    const float4* rec = reinterpret_cast<const float4*>(s_eval + j);
+                    const FragmentFront fr = fragment_front(rec[0], rec[1], rec[2], pixel_x, pixel_y);
+                    const float numerator_rho2 = fr.numerator_rho2;
+                    const float denominator = fr.denominator;
+                    if (numerator_rho2 > MT::max_cutoff_sq * denominator) continue;
+                    const float denominator_rcp = 1.0f / denominator;
+                    if constexpr (kFirstK) {
+                        // depth test before expf (alpha_blend_first_k/kernels/inference.cuh:147-153)
+                        const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
+                        const float4 MT3 = rec[3];
+                        float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
+                        if (depth >= kd[K - 1]) continue;
+                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                        const float alpha = fminf(rec[4].w * G, kMaxFragmentAlpha);
+                        if (alpha < MT::min_alpha) continue;
+                        if constexpr (STATS) ++stat_accepted;
+                        pool2[free_slot * TS::threads + tid] = make_float2(alpha, __uint_as_float(s_prim[j]));
+                        free_slot = kbuffer_insert<K>(kd, ks, depth, free_slot);
+                    } else if constexpr (kGlobal) {
+                        const float4 rgba_in = rec[4];
+                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                        const float opacity = rgba_in.w;
+                        const float alpha = fminf(opacity * G, kMaxFragmentAlpha);
+                        if (alpha < MT::min_alpha) continue;
+                        if constexpr (STATS) ++stat_accepted;
+                        const float blending_weight = transmittance * alpha;
+                        acc.x += blending_weight * rgba_in.x; acc.y += blending_weight * rgba_in.y; acc.z += blending_weight * rgba_in.z;
+                        if constexpr (!TRAIN) {
+                            const float depth = rec[3].w;
+                            if (use_median_depth) acc.w = (transmittance > 0.5f) ? depth : acc.w;
+                            else acc.w += blending_weight * depth;
                         }
-                    }
-                    free_slot = slot;                                 // whatever fell out of the chain (a real fragment or an empty entry)
-                    frag = pool4[slot * TS::threads + tid];
-                }
-                acc += frag;
-                if (!use_median_depth) acc_depth += depth * frag.w;
-                transmittance *= 1.0f - frag.w;
-            } else if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) {
-                const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
-                const float4 MT3 = rec[3];
-                float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
-                if (depth >= kd[K - 1]) continue;
-                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                const float alpha = fminf(rec[4].w * G, kMaxFragmentAlpha);
-                if (alpha < MT::min_alpha) continue;
-                if constexpr (STATS) ++stat_accepted;
-                pool2[free_slot * TS::threads + tid] = make_float2(alpha, __uint_as_float(s_prim[j]));
-                uint32_t slot = free_slot;
-                #pragma unroll
-                for (int k = 0; k < K; ++k) {
-                    if (depth < kd[k]) {
-                        const float td = kd[k]; kd[k] = depth; depth = td;
-                        const uint32_t ts = ks[k]; ks[k] = slot; slot = ts;
+                        transmittance *= 1.0f - alpha;
+                        if (transmittance < kTransmittanceThreshold) done = true;
+                    } else {   // OIT_BLEND
+                        const float4 rgba_in = rec[4];
+                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                        const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
+                        if (alpha < MT::min_alpha) continue;
+                        if constexpr (STATS) ++stat_accepted;
+                        if constexpr (TRAIN) {
+                            acc.x += alpha * rgba_in.x; acc.y += alpha * rgba_in.y; acc.z += alpha * rgba_in.z;
+                        } else {
+                            const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
+                            const float4 MT3 = rec[3];
+                            const float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
+                            acc += alpha * make_float4(rgba_in.x, rgba_in.y, rgba_in.z, depth);
+                        }
+                        acc_depth += alpha;
+                        transmittance *= 1.0f - alpha;
                     }
                 }
-                free_slot = slot;
-            } else if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) {
-                const float4 rgba_in = rec[4];
-                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                const float opacity = rgba_in.w;
-                const float alpha = fminf(opacity * G, kMaxFragmentAlpha);
-                if (alpha < MT::min_alpha) continue;
-                if constexpr (STATS) ++stat_accepted;
-                const float blending_weight = transmittance * alpha;
-                acc.x += blending_weight * rgba_in.x; acc.y += blending_weight * rgba_in.y; acc.z += blending_weight * rgba_in.z;
-                const float depth = rec[3].w;
-                if (use_median_depth) acc.w = (transmittance > 0.5f) ? depth : acc.w;
-                else acc.w += blending_weight * depth;
-                transmittance *= 1.0f - alpha;
-                if (transmittance < kTransmittanceThreshold) done = true;
-            } else {   // OIT_BLEND
-                const float4 rgba_in = rec[4];
-                const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
-                if (alpha < MT::min_alpha) continue;
-                if constexpr (STATS) ++stat_accepted;
-                const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
-                const float4 MT3 = rec[3];
-                const float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
-                acc += alpha * make_float4(rgba_in.x, rgba_in.y, rgba_in.z, depth);
-                acc_depth += alpha;
-                transmittance *= 1.0f - alpha;
             }
-        }
         }   // chunk loop
     }
 
@@ -367,11 +365,128 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
     }
     if (!inside) return;
 
-    // ---- compositing --------------------------------------------------------------------------------
+    const uint32_t pixel_idx = width * py_i + px_i;
+    const uint32_t n_pixels = width * height;
+
+    if constexpr (TRAIN) {
+        // ---- training forward: unclamped CHW image + what the backward pass needs per pixel ------------
+        const uint32_t slot_base = (tile_y * grid_w + tile_x) * TS::threads + tid;   // tile-major pixel slot
+        const uint32_t PP = tout.padded_pixels;
+        float3 rgb_pixel = make_float3(0.0f, 0.0f, 0.0f);
+        if constexpr (kHybrid) {
+            // hybrid_blend/kernels/forward.cuh:176-233
+            float transmittance_core = 1.0f;
+            #pragma unroll
+            for (int k = 0; k < K; ++k) {
+                if (transmittance_core >= kTransmittanceThreshold) {
+                    const float4 rgba = pool4[ks[k] * TS::threads + tid];
+                    const float blending_weight = transmittance_core * rgba.w;
+                    rgb_pixel += blending_weight * f3(rgba);
+                    transmittance_core *= 1.0f - rgba.w;
+                    if (transmittance_core < kTransmittanceThreshold) transmittance_core = 0.0f;
+                }
+            }
+            float3 weighted_rgb_tail = make_float3(0.0f, 0.0f, 0.0f);
+            float tail_info[6] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};   // the reference leaves these unwritten without tail mass; zeros make the backward terms vanish
+            if (acc.w >= MT::min_alpha) {
+                const float alpha_sum_tail_rcp = 1.0f / acc.w;
+                const float3 rgb_tail = f3(acc);
+                weighted_rgb_tail = transmittance_core * (1.0f - transmittance) * alpha_sum_tail_rcp * rgb_tail;
+                tail_info[0] = rgb_tail.x; tail_info[1] = rgb_tail.y; tail_info[2] = rgb_tail.z;
+                tail_info[3] = alpha_sum_tail_rcp; tail_info[4] = transmittance; tail_info[5] = transmittance_core;
+            }
+            #pragma unroll
+            for (int c = 0; c < 6; ++c) tout.info_tail[c * PP + slot_base] = tail_info[c];
+            float3 rgb_pixel_new = make_float3(0.0f, 0.0f, 0.0f);
+            transmittance_core = 1.0f;
+            #pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const uint32_t primitive_idx = pool_idx[ks[k] * TS::threads + tid];
+                const bool skip = primitive_idx == 0xffffffffu || transmittance_core < kTransmittanceThreshold;
+                tout.idx_core[k * PP + slot_base] = skip ? 0xffffffffu : primitive_idx;
+                if (!skip) {
+                    const float4 rgba = pool4[ks[k] * TS::threads + tid];
+                    const float blending_weight = transmittance_core * rgba.w;
+                    rgb_pixel_new += blending_weight * f3(rgba);
+                    const float one_minus_alpha = 1.0f - rgba.w;
+                    const float one_minus_alpha_rcp = 1.0f / fmaxf(one_minus_alpha, kOneMinusAlphaEps);
+                    tout.info_core[k * PP + slot_base] = make_float4(
+                        rgba.x * transmittance_core - (rgb_pixel.x - rgb_pixel_new.x + weighted_rgb_tail.x) * one_minus_alpha_rcp,
+                        rgba.y * transmittance_core - (rgb_pixel.y - rgb_pixel_new.y + weighted_rgb_tail.y) * one_minus_alpha_rcp,
+                        rgba.z * transmittance_core - (rgb_pixel.z - rgb_pixel_new.z + weighted_rgb_tail.z) * one_minus_alpha_rcp,
+                        blending_weight);
+                    transmittance_core *= one_minus_alpha;
+                }
+            }
+            rgb_pixel += weighted_rgb_tail;
+        } else if constexpr (kFirstK) {
+            // alpha_blend_first_k/kernels/forward.cuh:167-213
+            float t = 1.0f;
+            bool stop = false;
+            float3 rgbs_core[K];
+            #pragma unroll
+            for (int k = 0; k < K; ++k) {
+                rgbs_core[k] = make_float3(0.0f, 0.0f, 0.0f);
+                if (!stop && t >= kTransmittanceThreshold) {
+                    const float2 cell = pool2[ks[k] * TS::threads + tid];
+                    const uint32_t primitive_idx = __float_as_uint(cell.y);
+                    if (primitive_idx == 0xffffffffu) stop = true;
+                    else {
+                        const float alpha = cell.x;
+                        const float3 rgb = f3(ldg4(reinterpret_cast<const float*>(eval + primitive_idx) + 16));
+                        rgbs_core[k] = rgb;
+                        const float blending_weight = t * alpha;
+                        rgb_pixel += blending_weight * rgb;
+                        t *= 1.0f - alpha;
+                    }
+                }
+            }
+            float3 rgb_pixel_new = make_float3(0.0f, 0.0f, 0.0f);
+            t = 1.0f;
+            #pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const float2 cell = pool2[ks[k] * TS::threads + tid];
+                const uint32_t primitive_idx = __float_as_uint(cell.y);
+                const bool skip = primitive_idx == 0xffffffffu || t < kTransmittanceThreshold;
+                tout.idx_core[k * PP + slot_base] = skip ? 0xffffffffu : primitive_idx;
+                if (!skip) {
+                    const float alpha = cell.x;
+                    const float3 rgb = rgbs_core[k];
+                    const float blending_weight = t * alpha;
+                    rgb_pixel_new += blending_weight * rgb;
+                    const float one_minus_alpha = 1.0f - alpha;
+                    const float one_minus_alpha_rcp = 1.0f / fmaxf(one_minus_alpha, kOneMinusAlphaEps);
+                    tout.info_core[k * PP + slot_base] = make_float4(
+                        rgb.x * t - (rgb_pixel.x - rgb_pixel_new.x) * one_minus_alpha_rcp,
+                        rgb.y * t - (rgb_pixel.y - rgb_pixel_new.y) * one_minus_alpha_rcp,
+                        rgb.z * t - (rgb_pixel.z - rgb_pixel_new.z) * one_minus_alpha_rcp,
+                        blending_weight);
+                    t *= one_minus_alpha;
+                }
+            }
+        } else if constexpr (kGlobal) {
+            rgb_pixel = f3(acc);
+        } else {
+            // oit_blend/kernels/forward.cuh:143-163
+            float info[5] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            if (acc_depth >= MT::min_alpha) {
+                const float alpha_sum_rcp = 1.0f / acc_depth;
+                rgb_pixel = (1.0f - transmittance) * alpha_sum_rcp * f3(acc);
+                info[0] = acc.x; info[1] = acc.y; info[2] = acc.z; info[3] = alpha_sum_rcp; info[4] = transmittance;
+            }
+            #pragma unroll
+            for (int c = 0; c < 5; ++c) tout.info_tail[c * PP + slot_base] = info[c];
+        }
+        image[pixel_idx] = rgb_pixel.x;
+        image[n_pixels + pixel_idx] = rgb_pixel.y;
+        image[2 * n_pixels + pixel_idx] = rgb_pixel.z;
+        return;
+    } else {
+    // ---- inference compositing ----------------------------------------------------------------------
     float3 rgb_pixel = make_float3(0.0f, 0.0f, 0.0f);
     float depth_pixel = 0.0f;
     float alpha_pixel = 0.0f;
-    if constexpr (MODE == HTGS_MODE_HYBRID_BLEND) {
+    if constexpr (kHybrid) {
         // hybrid_blend/kernels/inference.cuh:174-199
         float transmittance_core = 1.0f;
         #pragma unroll
@@ -394,7 +509,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
         }
         if (!use_median_depth) depth_pixel = (total_alpha > 0.0f) ? depth_pixel / total_alpha : 0.0f;
         alpha_pixel = total_alpha;
-    } else if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K) {
+    } else if constexpr (kFirstK) {
         // alpha_blend_first_k/kernels/inference.cuh:172-191
         float t = 1.0f;
         bool stop = false;
@@ -418,7 +533,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
         }
         if (!use_median_depth) depth_pixel = (t < 1.0f) ? depth_pixel / (1.0f - t) : 0.0f;
         alpha_pixel = 1.0f - t;
-    } else if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) {
+    } else if constexpr (kGlobal) {
         rgb_pixel = f3(acc);
         depth_pixel = acc.w;
         if (!use_median_depth) depth_pixel = (transmittance < 1.0f) ? depth_pixel / (1.0f - transmittance) : 0.0f;
@@ -435,10 +550,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
         rgb_pixel = f3(rgbd_pixel);
         depth_pixel = rgbd_pixel.w;
     }
-
-    const uint32_t pixel_idx = width * py_i + px_i;
     if (to_chw) {
-        const uint32_t n_pixels = width * height;
         image[pixel_idx] = __saturatef(rgb_pixel.x);
         image[n_pixels + pixel_idx] = __saturatef(rgb_pixel.y);
         image[2 * n_pixels + pixel_idx] = __saturatef(rgb_pixel.z);
@@ -450,13 +562,14 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_inference_kern
     }
     depth_out[pixel_idx] = depth_pixel;
     if (alpha_out) alpha_out[pixel_idx] = alpha_pixel;
+    }
 }
 
-template <int MODE, int K, bool STATS>
-cudaError_t launch_mode_k_stats(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
-                                const BlendOutputs& out, FrameStatus* status, cudaStream_t stream) {
-    using SL = SmemLayout<MODE, K>;
-    auto kernel = blend_inference_kernel<MODE, K, STATS>;
+template <int MODE, int K, bool TRAIN, bool STATS>
+cudaError_t launch_blend_t(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                           const BlendOutputs& out, const TrainPixelBuffers& tout, FrameStatus* status, cudaStream_t stream) {
+    using SL = SmemLayout<MODE, K, TRAIN>;
+    auto kernel = blend_kernel<MODE, K, TRAIN, STATS>;
     static bool configured[64] = {};
     int device = 0;
     cudaGetDevice(&device);
@@ -466,41 +579,46 @@ cudaError_t launch_mode_k_stats(const FrameGeometry& geo, const PrimBuffers& pri
         configured[device] = true;
     }
     const dim3 grid(geo.grid_w, geo.grid_h, 1);
-    kernel<<<grid, TileShape<MODE>::threads, SL::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, out.image, out.depth, out.alpha,
+    kernel<<<grid, TileShape<MODE>::threads, SL::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, out.image, out.depth, out.alpha, tout,
                                                                   uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), out.to_chw,
                                                                   out.use_median_depth, status);
     return cudaGetLastError();
 }
 
 template <int MODE, int K>
-cudaError_t launch_mode_k(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
-                          const BlendOutputs& out, FrameStatus* status, cudaStream_t stream) {
-    return out.collect_stats ? launch_mode_k_stats<MODE, K, true>(geo, prim, prims_sorted, tile_ranges, out, status, stream)
-                             : launch_mode_k_stats<MODE, K, false>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+cudaError_t launch_mode_k(bool train, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                          const BlendOutputs& out, const TrainPixelBuffers& tout, FrameStatus* status, cudaStream_t stream) {
+    if (train) return launch_blend_t<MODE, K, true, false>(geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
+    return out.collect_stats ? launch_blend_t<MODE, K, false, true>(geo, prim, prims_sorted, tile_ranges, out, tout, status, stream)
+                             : launch_blend_t<MODE, K, false, false>(geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
 }
 
 // K is rounded down to a power of two <= 32 (hybrid_blend/inference.cu:15-28)
 template <int MODE>
-cudaError_t launch_mode(int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
-                        const BlendOutputs& out, FrameStatus* status, cudaStream_t stream) {
-    if (K >= 32) return launch_mode_k<MODE, 32>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
-    if (K >= 16) return launch_mode_k<MODE, 16>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
-    if (K >= 8) return launch_mode_k<MODE, 8>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
-    if (K >= 4) return launch_mode_k<MODE, 4>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
-    if (K >= 2) return launch_mode_k<MODE, 2>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
-    return launch_mode_k<MODE, 1>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+cudaError_t launch_mode(bool train, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                        const BlendOutputs& out, const TrainPixelBuffers& tout, FrameStatus* status, cudaStream_t stream) {
+    if (K >= 32) return launch_mode_k<MODE, 32>(train, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
+    if (K >= 16) return launch_mode_k<MODE, 16>(train, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
+    if (K >= 8) return launch_mode_k<MODE, 8>(train, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
+    if (K >= 4) return launch_mode_k<MODE, 4>(train, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
+    if (K >= 2) return launch_mode_k<MODE, 2>(train, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
+    return launch_mode_k<MODE, 1>(train, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
 }
 
 }  // namespace
 
-cudaError_t launch_blend_inference(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
-                                   const uint2* tile_ranges, const BlendOutputs& out, FrameStatus* status, int sm_count, cudaStream_t stream) {
-    (void)sm_count;
+int effective_k(int mode, int K) {
+    if (mode != HTGS_MODE_HYBRID_BLEND && mode != HTGS_MODE_ALPHA_BLEND_FIRST_K) return 1;
+    return K >= 32 ? 32 : K >= 16 ? 16 : K >= 8 ? 8 : K >= 4 ? 4 : K >= 2 ? 2 : 1;
+}
+
+cudaError_t launch_blend(int mode, int K, bool train, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
+                         const uint2* tile_ranges, const BlendOutputs& out, const TrainPixelBuffers& tout, FrameStatus* status, cudaStream_t stream) {
     switch (mode) {
-        case HTGS_MODE_HYBRID_BLEND: return launch_mode<HTGS_MODE_HYBRID_BLEND>(K, geo, prim, prims_sorted, tile_ranges, out, status, stream);
-        case HTGS_MODE_ALPHA_BLEND_FIRST_K: return launch_mode<HTGS_MODE_ALPHA_BLEND_FIRST_K>(K, geo, prim, prims_sorted, tile_ranges, out, status, stream);
-        case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: return launch_mode_k<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING, 1>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
-        case HTGS_MODE_OIT_BLEND: return launch_mode_k<HTGS_MODE_OIT_BLEND, 1>(geo, prim, prims_sorted, tile_ranges, out, status, stream);
+        case HTGS_MODE_HYBRID_BLEND: return launch_mode<HTGS_MODE_HYBRID_BLEND>(train, K, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
+        case HTGS_MODE_ALPHA_BLEND_FIRST_K: return launch_mode<HTGS_MODE_ALPHA_BLEND_FIRST_K>(train, K, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
+        case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: return launch_mode_k<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING, 1>(train, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
+        case HTGS_MODE_OIT_BLEND: return launch_mode_k<HTGS_MODE_OIT_BLEND, 1>(train, geo, prim, prims_sorted, tile_ranges, out, tout, status, stream);
         default: return cudaErrorInvalidValue;
     }
 }

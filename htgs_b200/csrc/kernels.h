@@ -66,8 +66,31 @@ struct BlendOutputs {
     bool use_median_depth;
     bool collect_stats;
 };
-cudaError_t launch_blend_inference(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
-                                   const uint2* tile_ranges, const BlendOutputs& out, FrameStatus* status, int sm_count, cudaStream_t stream);
-cudaError_t configure_blend_kernels();
+// per-pixel buffers the training forward leaves for the backward pass; pixel slots are tile-major
+// (slot = tile * pixels_per_tile + pixel_in_tile) and every array is plane-major over `padded_pixels` slots
+struct TrainPixelBuffers {
+    uint32_t* idx_core;      // [K][padded_pixels] Gaussian index per core entry, 0xffffffff = none (HYBRID, FIRST_K)
+    float4* info_core;       // [K][padded_pixels] (dC/dalpha factors, blending weight)                 (HYBRID, FIRST_K)
+    float* info_tail;        // [6][padded_pixels] HYBRID tail terms / [5][padded_pixels] OIT terms
+    uint32_t padded_pixels;  // n_tiles * pixels_per_tile
+};
+
+int effective_k(int mode, int K);
+cudaError_t launch_blend(int mode, int K, bool train, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
+                         const uint2* tile_ranges, const BlendOutputs& out, const TrainPixelBuffers& tout, FrameStatus* status, cudaStream_t stream);
+
+// train.cu: backward pass
+struct GradAccumBuffers {
+    float4* accum;           // [N][5] float4: dL/dVPMT1, dL/dVPMT2, dL/dVPMT4, (dL/drgb, dL/dopacity), (sum |dL/dposition|, 0, 0, 0)
+};
+struct BackwardOutputs {
+    float* grad_positions; float* grad_scales; float* grad_rotations; float* grad_opacities; float* grad_sh_0; float* grad_sh_rest;
+    float* densification_info;   // [rows][N] or null
+    int densification_rows;      // 0, 2 or 3
+    bool use_distance_scaling;
+};
+cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
+                            const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
+                            const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, int sm_count, cudaStream_t stream);
 
 }  // namespace htgs

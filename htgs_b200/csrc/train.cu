@@ -1,0 +1,579 @@
+// Backward pass of the rasterizer.
+//
+// Replaces the backward blend_cu / preprocess_cu pairs of the reference
+//   HYBRID_BLEND                rasterization/include/hybrid_blend/kernels/backward.cuh:10-331
+//   ALPHA_BLEND_FIRST_K         rasterization/include/alpha_blend_first_k/kernels/backward.cuh:10-206
+//   ALPHA_BLEND_GLOBAL_ORDERING rasterization/include/alpha_blend_global_ordering/kernels/backward.cuh:10-251
+//   OIT_BLEND                   rasterization/include/oit_blend/kernels/backward.cuh:10-290
+// and the helpers convert_quaternion_to_rotation_matrix_backward / convert_sh_to_rgb_backward
+// (rasterization/include/kernel_utils.cuh:44-61, 190-281).
+//
+// The chain rule is the reference's: gradients flow through alpha = opacity * G and the colour only
+// (not through depth, thresholds, the min(.,1) clamp or the bounds).  The organisation is new:
+//  * every mode accumulates the same per-Gaussian record of five float4 (dL/dVPMT1, dL/dVPMT2, dL/dVPMT4,
+//    (dL/drgb, dL/dopacity), (sum |dL/dposition|, -, -, -)) with 16-byte vector reductions
+//    (red.global.add.v4.f32): 4-5 per (Gaussian, tile) instead of 15-17 scalar atomics, and one
+//    per-Gaussian kernel turns the record into the six output gradients (the reference repeats the
+//    scale / rotation chain rule per fragment in two of its modes);
+//  * HYBRID / FIRST_K / OIT: one thread per Gaussian of a tile batch first builds the 64-bit mask of
+//    tile pixels its conservative outline can touch (3 flops per pixel), then only walks those pixels;
+//  * GLOBAL_ORDERING needs the running transmittance per pixel, so it stays pixel-parallel; the 32
+//    pixel contributions of a warp to one Gaussian are reduced with shuffles into a shared-memory
+//    record per staged Gaussian and flushed with vector reductions once per batch.
+#include "kernels.h"
+
+namespace htgs {
+
+namespace {
+
+__device__ __forceinline__ void red_add_v4(float4* addr, const float4& v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+struct PairGrad {      // what one (pixel, Gaussian) pair adds to the Gaussian's record
+    float4 dT1, dT2, dT4;
+};
+
+// Gradient of rho^2 = |m|^2 / |d|^2 w.r.t. the two planes through the pixel ray, then w.r.t. the rows
+// VPMT1, VPMT2, VPMT4 (hybrid_blend/kernels/backward.cuh:258-285).
+__device__ __forceinline__ PairGrad pair_gradient(const float4& plane_x_diag, const float4& plane_y_diag, const float3& m, const float3& d,
+                                                  float numerator_rho2, float denominator_rcp, float dL_drho2, float pixel_x, float pixel_y) {
+    const float dL_dnum = dL_drho2 * denominator_rcp;
+    const float dL_ddenom = dL_drho2 * -numerator_rho2 * denominator_rcp * denominator_rcp;
+    const float3 dL_dm = dL_dnum * 2.0f * m;
+    const float3 dL_dd = dL_ddenom * 2.0f * d;
+    const float3 nx = f3(plane_x_diag), ny = f3(plane_y_diag);
+    const float4 dpx = make_float4(
+        -plane_y_diag.w * dL_dm.x - plane_y_diag.z * dL_dd.y + plane_y_diag.y * dL_dd.z,
+        -plane_y_diag.w * dL_dm.y + plane_y_diag.z * dL_dd.x - plane_y_diag.x * dL_dd.z,
+        -plane_y_diag.w * dL_dm.z - plane_y_diag.y * dL_dd.x + plane_y_diag.x * dL_dd.y,
+        dot(ny, dL_dm));
+    const float4 dpy = make_float4(
+        plane_x_diag.w * dL_dm.x + plane_x_diag.z * dL_dd.y - plane_x_diag.y * dL_dd.z,
+        plane_x_diag.w * dL_dm.y - plane_x_diag.z * dL_dd.x + plane_x_diag.x * dL_dd.z,
+        plane_x_diag.w * dL_dm.z + plane_x_diag.y * dL_dd.x - plane_x_diag.x * dL_dd.y,
+        -dot(nx, dL_dm));
+    PairGrad g;
+    g.dT1 = dpx;
+    g.dT2 = dpy;
+    g.dT4 = (-pixel_x) * dpx - pixel_y * dpy;
+    return g;
+}
+
+struct CameraCols { float3 c1, c2, c3; };   // columns 1..3 of rows (1,2,4) of VPM
+__device__ __forceinline__ CameraCols load_camera_cols(const float* __restrict__ VPM) {
+    const float4 r1 = ldg4(VPM), r2 = ldg4(VPM + 4), r4 = ldg4(VPM + 12);
+    return {make_float3(r1.x, r2.x, r4.x), make_float3(r1.y, r2.y, r4.y), make_float3(r1.z, r2.z, r4.z)};
+}
+
+template <int MODE, int K> struct BwdSmem {
+    static constexpr bool has_core = (MODE == HTGS_MODE_HYBRID_BLEND || MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K);
+    static constexpr bool has_tail = (MODE == HTGS_MODE_HYBRID_BLEND || MODE == HTGS_MODE_OIT_BLEND);
+    static constexpr size_t idx_off = 0;
+    static constexpr size_t idx_bytes = has_core ? size_t(K) * 64 * 4 : 0;
+    static constexpr size_t cg_off = idx_off + idx_bytes;
+    static constexpr size_t cg_bytes = has_core ? size_t(K) * 64 * 16 : 0;
+    static constexpr size_t tc_off = cg_off + cg_bytes;
+    static constexpr size_t tc_bytes = has_tail ? 64 * 16 : 0;
+    static constexpr size_t ta_off = tc_off + tc_bytes;
+    static constexpr size_t ta_bytes = has_tail ? 64 * 4 : 0;
+    static constexpr size_t total = ta_off + ta_bytes;
+};
+
+// HYBRID_BLEND / ALPHA_BLEND_FIRST_K / OIT_BLEND: one CTA per 8x8 tile, one thread per Gaussian of a batch.
+template <int MODE, int K, bool ABS_GRAD>
+__global__ void __launch_bounds__(64) backward_tile_kernel(
+    const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
+    const CullRecord* __restrict__ cull, TrainPixelBuffers tin, const float* __restrict__ grad_image, const float* __restrict__ VPM,
+    float4* __restrict__ accum, uint32_t width, uint32_t height, uint32_t grid_w)
+{
+    using MT = ModeTraits<MODE>;
+    using SM = BwdSmem<MODE, K>;
+    constexpr bool kHybrid = MODE == HTGS_MODE_HYBRID_BLEND;
+    constexpr bool kFirstK = MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K;
+    extern __shared__ __align__(16) unsigned char smem[];
+    [[maybe_unused]] uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem + SM::idx_off);   // [K][64]
+    [[maybe_unused]] float4* s_cg = reinterpret_cast<float4*>(smem + SM::cg_off);          // [K][64] (W * grad_pixel, A . grad_pixel)
+    [[maybe_unused]] float4* s_tc = reinterpret_cast<float4*>(smem + SM::tc_off);          // [64] (full_weight * grad_pixel, common term)
+    [[maybe_unused]] float* s_ta = reinterpret_cast<float*>(smem + SM::ta_off);            // [64] term divided by (1 - alpha)
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t tile_x = blockIdx.x, tile_y = blockIdx.y;
+    const uint2 range = tile_ranges[tile_y * grid_w + tile_x];
+    if (range.x >= range.y) return;
+    const uint32_t n_pixels = width * height;
+    const uint32_t PP = tin.padded_pixels;
+    const uint32_t slot = (tile_y * grid_w + tile_x) * 64 + tid;
+
+    // ---- per-pixel terms of this tile (hybrid_blend/kernels/backward.cuh:137-176, oit_blend/kernels/backward.cuh:131-156)
+    {
+        const uint32_t px_i = tile_x * 8 + (tid & 7), py_i = tile_y * 8 + (tid >> 3);
+        const bool inside = px_i < width && py_i < height;
+        float3 grad_pixel = make_float3(0.0f, 0.0f, 0.0f);
+        if (inside) {
+            const uint32_t pixel_idx = width * py_i + px_i;
+            grad_pixel = make_float3(__ldg(grad_image + pixel_idx), __ldg(grad_image + n_pixels + pixel_idx), __ldg(grad_image + 2 * n_pixels + pixel_idx));
+        }
+        if constexpr (SM::has_core) {
+            #pragma unroll
+            for (int k = 0; k < K; ++k) {
+                uint32_t idx = 0xffffffffu;
+                float4 cg = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (inside) {
+                    idx = tin.idx_core[k * PP + slot];
+                    if (idx != 0xffffffffu) {
+                        const float4 info = tin.info_core[k * PP + slot];
+                        const float3 drgb = info.w * grad_pixel;
+                        cg = make_float4(drgb.x, drgb.y, drgb.z, dot(f3(info), grad_pixel));
+                    }
+                }
+                s_idx[k * 64 + tid] = idx;
+                s_cg[k * 64 + tid] = cg;
+            }
+        }
+        if constexpr (SM::has_tail) {
+            float4 tc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            float ta = 0.0f;
+            if (inside) {
+                const float3 rgb_tail = make_float3(tin.info_tail[slot], tin.info_tail[PP + slot], tin.info_tail[2 * PP + slot]);
+                const float alpha_sum_rcp = tin.info_tail[3 * PP + slot];
+                const float transmittance_tail = tin.info_tail[4 * PP + slot];
+                const float transmittance_core = kHybrid ? tin.info_tail[5 * PP + slot] : 1.0f;
+                const float weight_tail = transmittance_core * alpha_sum_rcp;
+                const float full_weight_tail = weight_tail * (1.0f - transmittance_tail);
+                const float rgb_dot_grad = dot(rgb_tail, grad_pixel);
+                const float3 part = full_weight_tail * grad_pixel;
+                tc = make_float4(part.x, part.y, part.z, -full_weight_tail * alpha_sum_rcp * rgb_dot_grad);
+                ta = weight_tail * transmittance_tail * rgb_dot_grad;
+            }
+            s_tc[tid] = tc;
+            s_ta[tid] = ta;
+        }
+    }
+    // pixels of the tile that exist in the image, as a 64-bit mask (bit = row * 8 + column)
+    uint64_t inside_mask = 0;
+    {
+        const uint32_t cols = min(8u, width - tile_x * 8), rows = min(8u, height - tile_y * 8);
+        const uint64_t row_bits = (1ull << cols) - 1ull;
+        for (uint32_t r = 0; r < rows; ++r) inside_mask |= row_bits << (8 * r);
+    }
+    [[maybe_unused]] CameraCols cam;
+    if constexpr (ABS_GRAD) cam = load_camera_cols(VPM);
+    __syncthreads();
+
+    const float x0 = float(tile_x * 8), y0 = float(tile_y * 8);
+    for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += 64) {
+        const uint32_t inst = batch_begin + tid;
+        const bool valid = inst < range.y;
+        uint32_t g = 0;
+        uint64_t mask = 0;
+        float4 T1 = make_float4(0, 0, 0, 0), T2 = T1, T4 = T1, rgba = T1;
+        if (valid) {
+            g = __ldg(prims_sorted + inst);
+            const float4 c0 = ldg4(reinterpret_cast<const float*>(cull + g));
+            const float cc = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
+            const float* rec = reinterpret_cast<const float*>(eval + g);
+            T1 = ldg4(rec); T2 = ldg4(rec + 4); T4 = ldg4(rec + 8); rgba = ldg4(rec + 16);
+            const float dx0 = x0 - c0.x, dy0 = y0 - c0.y;
+            #pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const float dy = dy0 + float(r);
+                const float b2dy = c0.w * dy, cdy2 = cc * dy * dy;
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float dx = dx0 + float(i);
+                    const float q = dx * (c0.z * dx + b2dy) + cdy2;
+                    if (q <= 1.0f) mask |= 1ull << (r * 8 + i);
+                }
+            }
+            mask &= inside_mask;
+        }
+        float4 aT1 = make_float4(0, 0, 0, 0), aT2 = aT1, aT4 = aT1, aC = aT1;   // aC = (dL/drgb, dL/dopacity)
+        [[maybe_unused]] float abs_grad = 0.0f;
+        bool touched = false;
+        while (__any_sync(0xffffffffu, mask != 0)) {
+            if (mask == 0) continue;
+            const uint32_t p = uint32_t(__ffsll((long long)mask) - 1);
+            mask &= mask - 1;
+            const float pixel_x = x0 + float(p & 7), pixel_y = y0 + float(p >> 3);
+            const float4 plane_x_diag = T1 - T4 * pixel_x;
+            const float4 plane_y_diag = T2 - T4 * pixel_y;
+            const float3 nx = f3(plane_x_diag), ny = f3(plane_y_diag);
+            const float3 m = plane_x_diag.w * ny - nx * plane_y_diag.w;
+            const float3 d = cross(nx, ny);
+            const float numerator_rho2 = dot(m, m);
+            const float denominator = dot(d, d);
+            int core_idx = -1;
+            if constexpr (SM::has_core) {
+                #pragma unroll
+                for (int k = 0; k < K; ++k) if (s_idx[k * 64 + p] == g) core_idx = k;
+            }
+            if constexpr (kFirstK) {
+                if (core_idx < 0) continue;                    // only stored fragments carry gradient (first_k backward.cuh:84-87)
+            } else {
+                if (numerator_rho2 > MT::max_cutoff_sq * denominator) continue;
+            }
+            const float denominator_rcp = 1.0f / denominator;
+            const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+            const float alpha = fminf(rgba.w * G, kMaxFragmentAlpha);
+            if constexpr (!kFirstK) { if (alpha < MT::min_alpha) continue; }
+            float3 dL_drgb;
+            float dL_dalpha;
+            if (core_idx >= 0) {
+                const float4 cg = s_cg[core_idx * 64 + p];
+                dL_drgb = f3(cg);
+                dL_dalpha = cg.w;
+            } else {
+                if constexpr (SM::has_tail) {
+                    const float4 tc = s_tc[p];
+                    dL_drgb = f3(tc) * alpha;
+                    dL_dalpha = tc.w + dot(f3(rgba), f3(tc)) + s_ta[p] / fmaxf(1.0f - alpha, kOneMinusAlphaEps);
+                } else {
+                    continue;
+                }
+            }
+            aC.x += dL_drgb.x; aC.y += dL_drgb.y; aC.z += dL_drgb.z;
+            touched = true;
+            if (dL_dalpha == 0.0f) continue;
+            aC.w += dL_dalpha * G;
+            const float dL_dG = dL_dalpha * rgba.w;
+            const float dL_drho2 = dL_dG * -0.5f * G;
+            const PairGrad pg = pair_gradient(plane_x_diag, plane_y_diag, m, d, numerator_rho2, denominator_rcp, dL_drho2, pixel_x, pixel_y);
+            aT1 += pg.dT1; aT2 += pg.dT2; aT4 += pg.dT4;
+            if constexpr (ABS_GRAD) {
+                const float3 c4 = make_float3(pg.dT1.w, pg.dT2.w, pg.dT4.w);
+                abs_grad += fabsf(dot(cam.c1, c4)) + fabsf(dot(cam.c2, c4)) + fabsf(dot(cam.c3, c4));
+            }
+        }
+        if (valid && touched) {
+            float4* rec = accum + size_t(g) * 5;
+            red_add_v4(rec, aT1); red_add_v4(rec + 1, aT2); red_add_v4(rec + 2, aT4); red_add_v4(rec + 3, aC);
+            if constexpr (ABS_GRAD) red_add_v4(rec + 4, make_float4(abs_grad, 0.0f, 0.0f, 0.0f));
+        }
+    }
+}
+
+// ALPHA_BLEND_GLOBAL_ORDERING: pixel-parallel, front to back in key order, using the final pixel colour so that
+// "colour behind" = rgb_pixel - rgb_pixel_new (alpha_blend_global_ordering/kernels/backward.cuh:104-161).
+constexpr int kGoBatch = 128;   // Gaussians staged per iteration (two per 256-thread CTA would waste threads; 128 keeps shared memory at 28 KB)
+__global__ void __launch_bounds__(256) backward_global_kernel(
+    const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
+    const float* __restrict__ grad_image, const float* __restrict__ image, const float* __restrict__ VPM, float4* __restrict__ accum,
+    uint32_t width, uint32_t height, uint32_t grid_w, bool abs_grad_on)
+{
+    using MT = ModeTraits<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING>;
+    __shared__ float4 s_T1[kGoBatch], s_T2[kGoBatch], s_T4[kGoBatch], s_rgba[kGoBatch];
+    __shared__ uint32_t s_g[kGoBatch];
+    __shared__ float s_acc[kGoBatch][20];
+    const uint32_t tid = threadIdx.x, lane = tid & 31;
+    const uint32_t tile_x = blockIdx.x, tile_y = blockIdx.y;
+    const uint32_t px_i = tile_x * 16 + (tid & 15), py_i = tile_y * 16 + (tid >> 4);
+    const bool inside = px_i < width && py_i < height;
+    const float pixel_x = __uint2float_rn(px_i), pixel_y = __uint2float_rn(py_i);
+    const uint32_t n_pixels = width * height;
+    float3 grad_pixel = make_float3(0, 0, 0), rgb_pixel = make_float3(0, 0, 0);
+    if (inside) {
+        const uint32_t pixel_idx = width * py_i + px_i;
+        grad_pixel = make_float3(__ldg(grad_image + pixel_idx), __ldg(grad_image + n_pixels + pixel_idx), __ldg(grad_image + 2 * n_pixels + pixel_idx));
+        rgb_pixel = make_float3(__ldg(image + pixel_idx), __ldg(image + n_pixels + pixel_idx), __ldg(image + 2 * n_pixels + pixel_idx));
+    }
+    const CameraCols cam = load_camera_cols(VPM);
+    float3 rgb_pixel_new = make_float3(0, 0, 0);
+    float transmittance = 1.0f;
+    bool done = !inside;
+    const uint2 range = tile_ranges[tile_y * grid_w + tile_x];
+    for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += kGoBatch) {
+        if (__syncthreads_count(done) == 256) break;
+        const uint32_t batch = min(uint32_t(kGoBatch), range.y - batch_begin);
+        if (tid < batch) {
+            const uint32_t g = __ldg(prims_sorted + batch_begin + tid);
+            const float* rec = reinterpret_cast<const float*>(eval + g);
+            s_g[tid] = g;
+            s_T1[tid] = ldg4(rec); s_T2[tid] = ldg4(rec + 4); s_T4[tid] = ldg4(rec + 8); s_rgba[tid] = ldg4(rec + 16);
+        }
+        for (uint32_t i = tid; i < kGoBatch * 20; i += 256) (&s_acc[0][0])[i] = 0.0f;
+        __syncthreads();
+        for (uint32_t j = 0; j < batch; ++j) {
+            if (__all_sync(0xffffffffu, done)) break;
+            float v[17];
+            #pragma unroll
+            for (int c = 0; c < 17; ++c) v[c] = 0.0f;
+            bool contributes = false;
+            if (!done) {
+                const float4 T1 = s_T1[j], T2 = s_T2[j], T4 = s_T4[j];
+                const float4 plane_x_diag = T1 - T4 * pixel_x;
+                const float4 plane_y_diag = T2 - T4 * pixel_y;
+                const float3 nx = f3(plane_x_diag), ny = f3(plane_y_diag);
+                const float3 m = plane_x_diag.w * ny - nx * plane_y_diag.w;
+                const float3 d = cross(nx, ny);
+                const float numerator_rho2 = dot(m, m);
+                const float denominator = dot(d, d);
+                if (!(numerator_rho2 > MT::max_cutoff_sq * denominator)) {
+                    const float denominator_rcp = 1.0f / denominator;
+                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                    const float4 rgba = s_rgba[j];
+                    const float opacity = rgba.w;
+                    const float alpha = fminf(opacity * G, kMaxFragmentAlpha);
+                    if (!(alpha < MT::min_alpha)) {
+                        const float blending_weight = transmittance * alpha;
+                        const float3 dL_drgb = blending_weight * grad_pixel;
+                        v[12] = dL_drgb.x; v[13] = dL_drgb.y; v[14] = dL_drgb.z;
+                        contributes = true;
+                        const float3 rgb = f3(rgba);
+                        rgb_pixel_new += blending_weight * rgb;
+                        const float one_minus_alpha = 1.0f - alpha;
+                        const float one_minus_alpha_rcp = 1.0f / fmaxf(one_minus_alpha, kOneMinusAlphaEps);
+                        const float dL_dalpha = dot(transmittance * rgb - (rgb_pixel - rgb_pixel_new) * one_minus_alpha_rcp, grad_pixel);
+                        if (dL_dalpha != 0.0f) {
+                            v[15] = dL_dalpha * G;
+                            const float dL_dG = dL_dalpha * opacity;
+                            const float dL_drho2 = dL_dG * -0.5f * G;
+                            const PairGrad pg = pair_gradient(plane_x_diag, plane_y_diag, m, d, numerator_rho2, denominator_rcp, dL_drho2, pixel_x, pixel_y);
+                            v[0] = pg.dT1.x; v[1] = pg.dT1.y; v[2] = pg.dT1.z; v[3] = pg.dT1.w;
+                            v[4] = pg.dT2.x; v[5] = pg.dT2.y; v[6] = pg.dT2.z; v[7] = pg.dT2.w;
+                            v[8] = pg.dT4.x; v[9] = pg.dT4.y; v[10] = pg.dT4.z; v[11] = pg.dT4.w;
+                            if (abs_grad_on) {
+                                const float3 c4 = make_float3(pg.dT1.w, pg.dT2.w, pg.dT4.w);
+                                v[16] = fabsf(dot(cam.c1, c4)) + fabsf(dot(cam.c2, c4)) + fabsf(dot(cam.c3, c4));
+                            }
+                        }
+                        transmittance *= one_minus_alpha;
+                        if (transmittance < kTransmittanceThreshold) done = true;
+                    }
+                }
+            }
+            if (__any_sync(0xffffffffu, contributes)) {      // warp-aggregated: one shared-memory add per value and warp
+                #pragma unroll
+                for (int c = 0; c < 17; ++c) {
+                    float x = v[c];
+                    #pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+                    if (lane == 0 && x != 0.0f) atomicAdd(&s_acc[j][c], x);
+                }
+            }
+        }
+        __syncthreads();
+        if (tid < batch) {
+            const float* a = s_acc[tid];
+            bool any = false;
+            #pragma unroll
+            for (int c = 0; c < 17; ++c) any |= a[c] != 0.0f;
+            if (any) {
+                float4* rec = accum + size_t(s_g[tid]) * 5;
+                red_add_v4(rec, make_float4(a[0], a[1], a[2], a[3]));
+                red_add_v4(rec + 1, make_float4(a[4], a[5], a[6], a[7]));
+                red_add_v4(rec + 2, make_float4(a[8], a[9], a[10], a[11]));
+                red_add_v4(rec + 3, make_float4(a[12], a[13], a[14], a[15]));
+                if (abs_grad_on) red_add_v4(rec + 4, make_float4(a[16], 0.0f, 0.0f, 0.0f));
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// kernel_utils.cuh:44-61
+__device__ __forceinline__ float4 quat_backward(const float4& q, const float (&dR)[9]) {
+    const float r = q.x, x = q.y, y = q.z, z = q.w;
+    const float r21_sub_r12 = dR[3] - dR[1], r21_add_r12 = dR[3] + dR[1];
+    const float r13_sub_r31 = dR[2] - dR[6], r13_add_r31 = dR[2] + dR[6];
+    const float r32_sub_r23 = dR[7] - dR[5], r32_add_r23 = dR[7] + dR[5];
+    return make_float4(
+        2.0f * (x * r32_sub_r23 + y * r13_sub_r31 + z * r21_sub_r12),
+        2.0f * (r * r32_sub_r23 - 2.0f * x * (dR[4] + dR[8]) + y * r21_add_r12 + z * r13_add_r31),
+        2.0f * (r * r13_sub_r31 + x * r21_add_r12 - 2.0f * y * (dR[0] + dR[8]) + z * r32_add_r23),
+        2.0f * (r * r21_sub_r12 + x * r13_add_r31 + y * r32_add_r23 - 2.0f * z * (dR[0] + dR[4])));
+}
+
+// Per-Gaussian chain rule: accumulated record -> the six output gradients
+// (hybrid_blend/kernels/backward.cuh:10-102; SH part kernel_utils.cuh:190-281).  Every output element is
+// written (zeros for Gaussians that were culled), so the caller need not clear the output tensors.
+__global__ void __launch_bounds__(256) preprocess_backward_kernel(
+    const float* __restrict__ positions, const float* __restrict__ scales, const float* __restrict__ rotations, const float* __restrict__ sh_rest,
+    const float* __restrict__ M, const float* __restrict__ VPM, const float* __restrict__ cam_position_ptr,
+    const uint32_t* __restrict__ n_touched, const uint8_t* __restrict__ clamp, const float4* __restrict__ accum, BackwardOutputs out,
+    uint32_t n_primitives, int active_sh_bases, int total_sh_bases)
+{
+    const uint32_t idx = blockIdx.x * 256 + threadIdx.x;
+    if (idx >= n_primitives) return;
+    float3* grad_sh_rest = reinterpret_cast<float3*>(out.grad_sh_rest) + size_t(idx) * total_sh_bases;
+    if (n_touched[idx] == 0) {
+        reinterpret_cast<float3*>(out.grad_positions)[idx] = make_float3(0, 0, 0);
+        reinterpret_cast<float3*>(out.grad_scales)[idx] = make_float3(0, 0, 0);
+        reinterpret_cast<float4*>(out.grad_rotations)[idx] = make_float4(0, 0, 0, 0);
+        out.grad_opacities[idx] = 0.0f;
+        reinterpret_cast<float3*>(out.grad_sh_0)[idx] = make_float3(0, 0, 0);
+        for (int i = 0; i < total_sh_bases; ++i) grad_sh_rest[i] = make_float3(0, 0, 0);
+        return;
+    }
+    const float4 dT1 = accum[size_t(idx) * 5], dT2 = accum[size_t(idx) * 5 + 1], dT4 = accum[size_t(idx) * 5 + 2], dC = accum[size_t(idx) * 5 + 3];
+    const float3 c1 = make_float3(dT1.x, dT2.x, dT4.x), c2 = make_float3(dT1.y, dT2.y, dT4.y), c3 = make_float3(dT1.z, dT2.z, dT4.z);
+    const float3 c4 = make_float3(dT1.w, dT2.w, dT4.w);
+    const float4 r1 = ldg4(VPM), r2 = ldg4(VPM + 4), r4 = ldg4(VPM + 12);
+    const float3 VPM1 = f3(r1), VPM2 = f3(r2), VPM4 = f3(r4);
+    const float3 VPM_c1 = make_float3(r1.x, r2.x, r4.x), VPM_c2 = make_float3(r1.y, r2.y, r4.y), VPM_c3 = make_float3(r1.z, r2.z, r4.z);
+
+    const float3 scale = make_float3(scales[3 * size_t(idx)], scales[3 * size_t(idx) + 1], scales[3 * size_t(idx) + 2]);
+    const float4 q = ldg4(rotations + 4 * size_t(idx));
+    const float r = q.x, x = q.y, y = q.z, z = q.w;
+    const float xx = x * x, yy = y * y, zz = z * z, xy = x * y, xz = x * z, yz = y * z, rx = r * x, ry = r * y, rz = r * z;
+    const float3 R_c1 = make_float3(1.0f - 2.0f * (yy + zz), 2.0f * (xy + rz), 2.0f * (xz - ry));
+    const float3 R_c2 = make_float3(2.0f * (xy - rz), 1.0f - 2.0f * (xx + zz), 2.0f * (yz + rx));
+    const float3 R_c3 = make_float3(2.0f * (xz + ry), 2.0f * (yz - rx), 1.0f - 2.0f * (xx + yy));
+    reinterpret_cast<float3*>(out.grad_scales)[idx] = make_float3(
+        dot(make_float3(dot(VPM1, R_c1), dot(VPM2, R_c1), dot(VPM4, R_c1)), c1),
+        dot(make_float3(dot(VPM1, R_c2), dot(VPM2, R_c2), dot(VPM4, R_c2)), c2),
+        dot(make_float3(dot(VPM1, R_c3), dot(VPM2, R_c3), dot(VPM4, R_c3)), c3));
+    const float dR[9] = {
+        dot(VPM_c1, c1) * scale.x, dot(VPM_c1, c2) * scale.y, dot(VPM_c1, c3) * scale.z,
+        dot(VPM_c2, c1) * scale.x, dot(VPM_c2, c2) * scale.y, dot(VPM_c2, c3) * scale.z,
+        dot(VPM_c3, c1) * scale.x, dot(VPM_c3, c2) * scale.y, dot(VPM_c3, c3) * scale.z};
+    reinterpret_cast<float4*>(out.grad_rotations)[idx] = quat_backward(q, dR);
+    out.grad_opacities[idx] = dC.w;
+
+    // colour: undo the clamp at 0, then SH backward
+    const uint8_t cl = clamp[idx];
+    const float3 grad_rgb = make_float3((cl & 1) ? 0.0f : dC.x, (cl & 2) ? 0.0f : dC.y, (cl & 4) ? 0.0f : dC.z);
+    reinterpret_cast<float3*>(out.grad_sh_0)[idx] = 0.28209479177387814f * grad_rgb;
+    const float3 position = make_float3(positions[3 * size_t(idx)], positions[3 * size_t(idx) + 1], positions[3 * size_t(idx) + 2]);
+    float3 drgb_dposition = make_float3(0, 0, 0);
+    int written = 0;
+    if (active_sh_bases > 1) {
+        const float3* co = reinterpret_cast<const float3*>(sh_rest) + size_t(idx) * total_sh_bases;
+        const float3 cam_position = make_float3(__ldg(cam_position_ptr), __ldg(cam_position_ptr + 1), __ldg(cam_position_ptr + 2));
+        const float3 raw = position - cam_position;
+        const float3 dir = normalize(raw);
+        const float dx = dir.x, dy = dir.y, dz = dir.z;
+        grad_sh_rest[0] = (-0.48860251190291987f * dy) * grad_rgb;
+        grad_sh_rest[1] = (0.48860251190291987f * dz) * grad_rgb;
+        grad_sh_rest[2] = (-0.48860251190291987f * dx) * grad_rgb;
+        float3 gdx = -0.48860251190291987f * co[2];
+        float3 gdy = -0.48860251190291987f * co[0];
+        float3 gdz = 0.48860251190291987f * co[1];
+        written = 3;
+        if (active_sh_bases > 4) {
+            const float sxx = dx * dx, syy = dy * dy, szz = dz * dz, sxy = dx * dy, sxz = dx * dz, syz = dy * dz;
+            grad_sh_rest[3] = (1.0925484305920792f * sxy) * grad_rgb;
+            grad_sh_rest[4] = (-1.0925484305920792f * syz) * grad_rgb;
+            grad_sh_rest[5] = (0.94617469575755997f * szz - 0.31539156525251999f) * grad_rgb;
+            grad_sh_rest[6] = (-1.0925484305920792f * sxz) * grad_rgb;
+            grad_sh_rest[7] = (0.54627421529603959f * sxx - 0.54627421529603959f * syy) * grad_rgb;
+            gdx = gdx + (1.0925484305920792f * dy) * co[3] + (-1.0925484305920792f * dz) * co[6] + (1.0925484305920792f * dx) * co[7];
+            gdy = gdy + (1.0925484305920792f * dx) * co[3] + (-1.0925484305920792f * dz) * co[4] + (-1.0925484305920792f * dy) * co[7];
+            gdz = gdz + (-1.0925484305920792f * dy) * co[4] + (1.8923493915151202f * dz) * co[5] + (-1.0925484305920792f * dx) * co[6];
+            written = 8;
+            if (active_sh_bases > 9) {
+                grad_sh_rest[8] = (0.59004358992664352f * dy * (-3.0f * sxx + syy)) * grad_rgb;
+                grad_sh_rest[9] = (2.8906114426405538f * sxy * dz) * grad_rgb;
+                grad_sh_rest[10] = (0.45704579946446572f * dy * (1.0f - 5.0f * szz)) * grad_rgb;
+                grad_sh_rest[11] = (0.3731763325901154f * dz * (5.0f * szz - 3.0f)) * grad_rgb;
+                grad_sh_rest[12] = (0.45704579946446572f * dx * (1.0f - 5.0f * szz)) * grad_rgb;
+                grad_sh_rest[13] = (1.4453057213202769f * dz * (sxx - syy)) * grad_rgb;
+                grad_sh_rest[14] = (0.59004358992664352f * dx * (-sxx + 3.0f * syy)) * grad_rgb;
+                gdx = gdx + (-3.5402615395598609f * sxy) * co[8] + (2.8906114426405538f * syz) * co[9]
+                          + (0.45704579946446572f - 2.2852289973223288f * szz) * co[12] + (2.8906114426405538f * sxz) * co[13]
+                          + (-1.7701307697799304f * sxx + 1.7701307697799304f * syy) * co[14];
+                gdy = gdy + (-1.7701307697799304f * sxx + 1.7701307697799304f * syy) * co[8] + (2.8906114426405538f * sxz) * co[9]
+                          + (0.45704579946446572f - 2.2852289973223288f * szz) * co[10] + (-2.8906114426405538f * syz) * co[13]
+                          + (3.5402615395598609f * sxy) * co[14];
+                gdz = gdz + (2.8906114426405538f * sxy) * co[9] + (-4.5704579946446566f * syz) * co[10]
+                          + (5.597644988851731f * szz - 1.1195289977703462f) * co[11] + (-4.5704579946446566f * sxz) * co[12]
+                          + (1.4453057213202769f * sxx - 1.4453057213202769f * syy) * co[13];
+                written = 15;
+            }
+        }
+        const float3 gdir = make_float3(dot(gdx, grad_rgb), dot(gdy, grad_rgb), dot(gdz, grad_rgb));
+        const float xr = raw.x, yr = raw.y, zr = raw.z;
+        const float xxr = xr * xr, yyr = yr * yr, zzr = zr * zr, xyr = xr * yr, xzr = xr * zr, yzr = yr * zr;
+        const float norm_sq = xxr + yyr + zzr;
+        drgb_dposition = make_float3(
+            (yyr + zzr) * gdir.x - xyr * gdir.y - xzr * gdir.z,
+            -xyr * gdir.x + (xxr + zzr) * gdir.y - yzr * gdir.z,
+            -xzr * gdir.x - yzr * gdir.y + (xxr + yyr) * gdir.z) * rsqrtf(norm_sq * norm_sq * norm_sq);
+    }
+    for (int i = written; i < total_sh_bases; ++i) grad_sh_rest[i] = make_float3(0, 0, 0);
+    const float3 dL_dposition = make_float3(dot(VPM_c1, c4), dot(VPM_c2, c4), dot(VPM_c3, c4)) + drgb_dposition;
+    reinterpret_cast<float3*>(out.grad_positions)[idx] = dL_dposition;
+    if (out.densification_info != nullptr) {     // hybrid_blend/kernels/backward.cuh:85-98
+        float z_scale = 1.0f;
+        if (out.use_distance_scaling) {
+            const float4 M3 = ldg4(M + 8);
+            z_scale = (dot(f3(M3), position) + M3.w) * 0.5f;
+        }
+        float* info = out.densification_info;
+        info[idx] += 1.0f;
+        info[size_t(n_primitives) + idx] += length(dL_dposition * z_scale);
+        if (out.densification_rows == 3) info[2 * size_t(n_primitives) + idx] += z_scale * accum[size_t(idx) * 5 + 4].x;
+    }
+}
+
+template <int MODE, int K>
+cudaError_t launch_tile_backward(bool abs_grad, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                                 const TrainPixelBuffers& tin, const float* grad_image, const float* VPM, float4* accum, cudaStream_t stream) {
+    using SM = BwdSmem<MODE, K>;
+    const dim3 grid(geo.grid_w, geo.grid_h, 1);
+    auto launch = [&](auto kernel) -> cudaError_t {
+        static bool configured[64] = {};
+        int device = 0;
+        cudaGetDevice(&device);
+        if (SM::total > 48 * 1024 && device >= 0 && device < 64 && !configured[device]) {
+            const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SM::total));
+            if (err != cudaSuccess) return err;
+            configured[device] = true;
+        }
+        kernel<<<grid, 64, SM::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, tin, grad_image, VPM, accum,
+                                                uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w));
+        return cudaGetLastError();
+    };
+    return abs_grad ? launch(backward_tile_kernel<MODE, K, true>) : launch(backward_tile_kernel<MODE, K, false>);
+}
+
+template <int MODE>
+cudaError_t launch_tile_backward_k(int K, bool abs_grad, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
+                                   const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image, const float* VPM, float4* accum,
+                                   cudaStream_t stream) {
+    switch (K) {
+        case 32: return launch_tile_backward<MODE, 32>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
+        case 16: return launch_tile_backward<MODE, 16>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
+        case 8: return launch_tile_backward<MODE, 8>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
+        case 4: return launch_tile_backward<MODE, 4>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
+        case 2: return launch_tile_backward<MODE, 2>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
+        default: return launch_tile_backward<MODE, 1>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
+                            const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
+                            const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, int sm_count, cudaStream_t stream) {
+    (void)sm_count;
+    const uint32_t n = uint32_t(scene.n_primitives);
+    if (n == 0) return cudaSuccess;
+    cudaError_t err = cudaMemsetAsync(acc.accum, 0, size_t(n) * 5 * sizeof(float4), stream);
+    if (err != cudaSuccess) return err;
+    const bool abs_grad = out.densification_info != nullptr && out.densification_rows == 3;
+    const int k = effective_k(mode, K);
+    switch (mode) {
+        case HTGS_MODE_HYBRID_BLEND:
+            err = launch_tile_backward_k<HTGS_MODE_HYBRID_BLEND>(k, abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, stream); break;
+        case HTGS_MODE_ALPHA_BLEND_FIRST_K:
+            err = launch_tile_backward_k<HTGS_MODE_ALPHA_BLEND_FIRST_K>(k, abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, stream); break;
+        case HTGS_MODE_OIT_BLEND:
+            err = launch_tile_backward<HTGS_MODE_OIT_BLEND, 1>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, stream); break;
+        case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: {
+            const dim3 grid(geo.grid_w, geo.grid_h, 1);
+            backward_global_kernel<<<grid, 256, 0, stream>>>(tile_ranges, prims_sorted, prim.eval, grad_image, image, view.VPM, acc.accum,
+                                                             uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), abs_grad);
+            err = cudaGetLastError();
+            break;
+        }
+        default: return cudaErrorInvalidValue;
+    }
+    if (err != cudaSuccess) return err;
+    preprocess_backward_kernel<<<(n + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
+                                                                    view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
+                                                                    view.active_sh_bases, scene.total_sh_bases);
+    return cudaGetLastError();
+}
+
+}  // namespace htgs

@@ -73,12 +73,97 @@ def render(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_p
     return image, depth
 
 
-def forward(*args):
-    raise NotImplementedError("htgs_b200: the training forward is provided by htgs_b200.torch_bindings._train once built")
+def _device_index(device):
+    return device.index if device.index is not None else torch.cuda.current_device()
 
 
-def backward(*args):
-    raise NotImplementedError("htgs_b200: the backward pass is provided by htgs_b200.torch_bindings._train once built")
+def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases,
+            width, height, near_plane, far_plane, scale_modifier):
+    """`_C.forward` (rasterization/include/rasterization_api.h:8-26): returns
+    (image, per_primitive_buffers, per_tile_buffers, per_instance_buffers, per_pixel_buffers, n_instances, selector).
+    The four byte tensors are opaque to the caller and only meaningful to `backward` of this module."""
+    global last_frame_info
+    n, device = _check_inputs(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_position)
+    tensors = [t.contiguous() for t in (positions, scales, rotations, opacities, sh_0, sh_rest)]
+    M, VPM, cam_position = M.contiguous(), VPM.contiguous(), cam_position.contiguous()
+    lib = _native.lib()
+    with torch.cuda.device(device):
+        ctx = _native.context(_device_index(device))
+        scene, view = _scene_view(tensors, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases, width, height, near_plane, far_plane, 1.0)
+        sz = [ctypes.c_size_t() for _ in range(3)]
+        _native.check(lib.htgs_forward_blob_sizes(ctypes.byref(scene), ctypes.byref(view), *(ctypes.byref(x) for x in sz)))
+        byte = dict(dtype=torch.uint8, device=device)
+        per_primitive = torch.empty(sz[0].value, **byte)
+        per_tile = torch.empty(sz[1].value, **byte)
+        per_pixel = torch.empty(sz[2].value, **byte)
+        image = torch.empty((3, height, width), dtype=torch.float32, device=device)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        n_inst = ctypes.c_uint32()
+        _native.check(lib.htgs_forward_begin(ctx, ctypes.byref(scene), ctypes.byref(view), per_primitive.data_ptr(), per_primitive.numel(), stream,
+                                             ctypes.byref(n_inst)))
+        per_instance = torch.empty(lib.htgs_forward_instance_bytes(ctypes.byref(view), n_inst.value), **byte)
+        blobs = _native.HtgsTrainBlobs(per_primitive.data_ptr(), per_primitive.numel(), per_tile.data_ptr(), per_tile.numel(),
+                                       per_instance.data_ptr(), per_instance.numel(), per_pixel.data_ptr(), per_pixel.numel())
+        info = HtgsFrameInfo()
+        _native.check(lib.htgs_forward_finish(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), n_inst.value, image.data_ptr(), stream,
+                                              ctypes.byref(info)))
+    last_frame_info = info
+    return image, per_primitive, per_tile, per_instance, per_pixel, int(n_inst.value), 0
+
+
+def backward(densification_info, grad_image, image, positions, scales, rotations, opacities, sh_rest, per_primitive_buffers, per_tile_buffers,
+             per_instance_buffers, per_pixel_buffers, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases, width, height, near_plane,
+             far_plane, scale_modifier, n_instances, instance_primitive_indices_selector, use_distance_scaling):
+    """`_C.backward` (rasterization/include/rasterization_api.h:28-55): returns the six gradients; `densification_info`
+    ([2|3, N, 1] or empty) is updated in place.  `image` / `opacities` may be empty tensors, as the reference's autograd
+    function passes them (torch_bindings/rasterization.py:72-76)."""
+    device = positions.device
+    if device.type != "cuda":
+        raise ValueError("htgs_b200 rasterizer: tensors must live on a CUDA device")
+    n = positions.shape[0]
+    total_sh = sh_rest.shape[1]
+    for name, t in (("grad_image", grad_image), ("positions", positions), ("scales", scales), ("rotations", rotations), ("sh_rest", sh_rest)):
+        if t.dtype != torch.float32 or t.device != device:
+            raise TypeError(f"{name} must be a float32 tensor on {device}")
+    if tuple(grad_image.shape) != (3, height, width):
+        raise ValueError(f"grad_image must have shape (3, {height}, {width}), got {tuple(grad_image.shape)}")
+    grad_image = grad_image.contiguous()
+    positions, scales, rotations, sh_rest = positions.contiguous(), scales.contiguous(), rotations.contiguous(), sh_rest.contiguous()
+    M, VPM, cam_position = M.contiguous(), VPM.contiguous(), cam_position.contiguous()
+    lib = _native.lib()
+    with torch.cuda.device(device):
+        ctx = _native.context(_device_index(device))
+        f32 = dict(dtype=torch.float32, device=device)
+        grad_positions = torch.empty((n, 3), **f32)
+        grad_scales = torch.empty((n, 3), **f32)
+        grad_rotations = torch.empty((n, 4), **f32)
+        grad_opacities = torch.empty((n, 1), **f32)
+        grad_sh_0 = torch.empty((n, 1, 3), **f32)
+        grad_sh_rest = torch.empty((n, total_sh, 3), **f32)
+        # opacities / sh_0 are not read by the backward kernels (the forward's records hold what is needed)
+        scene = HtgsScene(positions.data_ptr(), scales.data_ptr(), rotations.data_ptr(), positions.data_ptr(), positions.data_ptr(),
+                          sh_rest.data_ptr() if sh_rest.numel() else None, n, total_sh)
+        view = HtgsView(M.data_ptr(), VPM.data_ptr(), cam_position.data_ptr(), int(rasterizer_mode), int(K), int(active_sh_bases), int(width), int(height),
+                        float(near_plane), float(far_plane), 1.0)
+        scratch = torch.empty(lib.htgs_backward_scratch_bytes(ctypes.byref(scene)), dtype=torch.uint8, device=device)
+        rows = int(densification_info.shape[0]) if densification_info.numel() > 0 else 0
+        if rows not in (0, 2, 3):
+            raise ValueError("densification_info must be empty or have 2 or 3 rows")
+        if rows and (densification_info.dtype != torch.float32 or densification_info.device != device or not densification_info.is_contiguous()
+                     or densification_info.numel() != rows * n):
+            raise ValueError("densification_info must be a contiguous float32 tensor of shape [rows, N, 1] on the same device")
+        grads = _native.HtgsGradients(grad_positions.data_ptr(), grad_scales.data_ptr(), grad_rotations.data_ptr(), grad_opacities.data_ptr(),
+                                      grad_sh_0.data_ptr(), grad_sh_rest.data_ptr() if grad_sh_rest.numel() else None, scratch.data_ptr(), scratch.numel(),
+                                      densification_info.data_ptr() if rows else None, rows, int(bool(use_distance_scaling)))
+        blobs = _native.HtgsTrainBlobs(per_primitive_buffers.data_ptr(), per_primitive_buffers.numel(), per_tile_buffers.data_ptr(),
+                                       per_tile_buffers.numel(), per_instance_buffers.data_ptr(), per_instance_buffers.numel(),
+                                       per_pixel_buffers.data_ptr(), per_pixel_buffers.numel())
+        image_ptr = image.contiguous().data_ptr() if image.numel() else None
+        stream = torch.cuda.current_stream(device).cuda_stream
+        _native.check(lib.htgs_backward(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), int(n_instances), grad_image.data_ptr(),
+                                        image_ptr, ctypes.byref(grads), stream))
+        scratch.record_stream(torch.cuda.current_stream(device))
+    return grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest
 
 
 def update_max_weights(*args):

@@ -135,6 +135,55 @@ int htgs_render_host(HtgsContext* ctx, const HtgsScene* host_scene, const HtgsVi
 
 int htgs_get_intermediates(HtgsContext* ctx, HtgsIntermediates* out);
 
+/*
+ * Training forward and backward.  Replace `_C.forward` / `_C.backward` = forward_wrapper / backward_wrapper
+ * (rasterization/include/rasterization_api.h:8-55, rasterization/src/rasterization_api.cu:37-363).
+ *
+ * As in the reference, the forward leaves four opaque byte blobs for the backward (per Gaussian, per tile,
+ * per instance, per pixel); the caller owns them (the Python layer allocates them with torch, exactly like
+ * the reference's resizable byte tensors).  Three sizes are known up front, the per-instance one only after
+ * the instance count is: htgs_forward_begin runs preprocess + prefix sum and returns the count (one host
+ * synchronisation, as in the reference), htgs_forward_finish runs the rest.
+ *   image: [3,H,W], NOT clamped; scale_modifier is ignored (1), as in the reference's training forward.
+ */
+typedef struct HtgsTrainBlobs {
+    void* per_primitive; size_t per_primitive_bytes;
+    void* per_tile;      size_t per_tile_bytes;
+    void* per_instance;  size_t per_instance_bytes;
+    void* per_pixel;     size_t per_pixel_bytes;
+} HtgsTrainBlobs;
+
+int htgs_forward_blob_sizes(const HtgsScene* scene, const HtgsView* view, size_t* per_primitive_bytes, size_t* per_tile_bytes, size_t* per_pixel_bytes);
+size_t htgs_forward_instance_bytes(const HtgsView* view, uint64_t n_instances);
+int htgs_forward_begin(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, void* per_primitive, size_t per_primitive_bytes,
+                       void* stream, uint32_t* n_instances);
+int htgs_forward_finish(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                        float* image, void* stream, HtgsFrameInfo* info);
+
+/* Outputs of the backward pass.  Every element of the six gradient tensors is written (zeros for culled
+ * Gaussians), so they need not be cleared.  `scratch` (htgs_backward_scratch_bytes) holds the per-Gaussian
+ * accumulation records and is cleared by the call.  `densification_info` ([rows,N], rows 2 or 3) is
+ * updated in place as in the reference (rasterization/src/rasterization_api.cu:219-223), or NULL. */
+typedef struct HtgsGradients {
+    float* grad_positions;   /* [N,3] */
+    float* grad_scales;      /* [N,3] */
+    float* grad_rotations;   /* [N,4] */
+    float* grad_opacities;   /* [N,1] */
+    float* grad_sh_0;        /* [N,1,3] */
+    float* grad_sh_rest;     /* [N,B,3] */
+    void* scratch;
+    size_t scratch_bytes;
+    float* densification_info;
+    int32_t densification_rows;
+    int32_t use_distance_scaling;
+} HtgsGradients;
+
+size_t htgs_backward_scratch_bytes(const HtgsScene* scene);
+/* grad_image: [3,H,W]; image: the forward's output, read only by ALPHA_BLEND_GLOBAL_ORDERING (may be NULL otherwise).
+ * Stream-ordered, no host synchronisation. */
+int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                  const float* grad_image, const float* image, const HtgsGradients* grads, void* stream);
+
 /* Measurement aids (off by default; they do not change results).
  * Profiling: CUDA events are recorded on the frame's stream between the stages; after the call
  * htgs_get_stage_ms fills out_ms[0..HTGS_N_STAGES) with the device time of each stage in ms.

@@ -1,0 +1,100 @@
+"""GPU: training forward + backward (`diff_rasterize`) against the golden gradients produced by the reference
+extension, against the live reference when it is built beside the repo, and basic autograd plumbing."""
+import os
+
+import numpy as np
+import pytest
+
+import harness
+from htgs_b200 import scenes
+from golden.make_golden import CASES, target_image
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+GRAD_NAMES = ("positions", "scales", "rotations", "opacities", "sh_0", "sh_rest")
+GRAD_RTOL = 1e-3    # gradients: relative to the largest magnitude of the tensor
+
+
+def run_training_step(mod, scene, view, mode, K, densification_rows=0, use_distance_scaling=False):
+    import torch
+    tensors = harness.scene_tensors(scene)
+    leaves = [t.clone().requires_grad_(True) for t in tensors]
+    st = harness.settings_for(mod, scene, view, mode, K)
+    dens = torch.zeros((densification_rows, scene.n, 1), device="cuda") if densification_rows else torch.empty(0, device="cuda")
+    image = mod.diff_rasterize(*leaves, dens, st, use_distance_scaling)
+    target = torch.from_numpy(target_image(view.height, view.width, 1000 + mode)).cuda()
+    loss = (image - target).abs().mean()
+    loss.backward()
+    torch.cuda.synchronize()
+    return image.detach(), [l.grad for l in leaves], dens
+
+
+def assert_grads_close(ours, ref, what):
+    for name, a, b in zip(GRAD_NAMES, ours, ref):
+        a = a.detach().cpu().numpy() if hasattr(a, "detach") else np.asarray(a)
+        b = b.detach().cpu().numpy() if hasattr(b, "detach") else np.asarray(b)
+        assert a.shape == b.shape, f"{what} grad_{name}: shape {a.shape} vs {b.shape}"
+        scale = np.abs(b).max()
+        if scale == 0:
+            assert np.abs(a).max() == 0, f"{what} grad_{name}: reference is all zero"
+            continue
+        err = np.abs(a - b).max() / scale
+        assert err <= GRAD_RTOL, f"{what} grad_{name}: max error {err:.2e} of the tensor's scale"
+
+
+def golden_cases():
+    for name, case in CASES.items():
+        for mode, K in case["modes"]:
+            yield name, mode, K
+
+
+@pytest.mark.parametrize("name,mode,K", list(golden_cases()))
+def test_training_against_reference_golden(name, mode, K):
+    scene = scenes.tiny_scene(**CASES[name]["kwargs"])
+    view = scene.views[0]
+    gold = np.load(os.path.join(GOLDEN, f"{name}.npz"))
+    tag = f"m{mode}_k{K}"
+    image, grads, _ = run_training_step(harness.ours(), scene, view, mode, K)
+    assert np.abs(image.cpu().numpy() - gold[f"{tag}_train_image"]).max() <= 1e-5
+    assert_grads_close(grads, [gold[f"{tag}_grad_{n}"] for n in GRAD_NAMES], f"{name} {tag}")
+
+
+@pytest.mark.parametrize("mode,K", [(0, 16), (0, 4), (1, 8), (2, 1), (3, 1)])
+def test_training_against_reference_extension(mode, K):
+    import torch
+    ref = harness.reference()
+    if ref is None:
+        pytest.skip("reference extension not built under baseline/_ref")
+    scene = scenes.outdoor_scene(n=200_000, n_views=2, seed=31, width=640, height=360, focal=500.0)
+    view = scene.views[1]
+    img_o, g_o, _ = run_training_step(harness.ours(), scene, view, mode, K)
+    img_r, g_r, _ = run_training_step(ref, scene, view, mode, K)
+    assert (img_o - img_r).abs().max().item() <= 1e-5
+    assert_grads_close(g_o, g_r, f"mode {mode} K {K}")
+
+
+@pytest.mark.parametrize("rows", [2, 3])
+def test_densification_info_matches_reference(rows):
+    ref = harness.reference()
+    if ref is None:
+        pytest.skip("reference extension not built under baseline/_ref")
+    scene = scenes.tiny_scene(n=5000, size=128, seed=17, sh_degree=2)
+    view = scene.views[0]
+    _, _, d_o = run_training_step(harness.ours(), scene, view, 0, 8, rows, True)
+    _, _, d_r = run_training_step(ref, scene, view, 0, 8, rows, True)
+    a, b = d_o.cpu().numpy(), d_r.cpu().numpy()
+    assert np.array_equal(a[0], b[0])
+    for r in range(1, rows):
+        assert np.abs(a[r] - b[r]).max() <= 2e-3 * max(np.abs(b[r]).max(), 1e-12)
+
+
+def test_backward_twice_is_deterministic_enough_and_culled_gradients_are_zero():
+    scene = scenes.tiny_scene(n=3000, size=96, seed=23, sh_degree=1)
+    scene.positions[:100, 2] = -5.0            # behind the camera: culled
+    view = scene.views[0]
+    _, g1, _ = run_training_step(harness.ours(), scene, view, 0, 8)
+    _, g2, _ = run_training_step(harness.ours(), scene, view, 0, 8)
+    for a, b in zip(g1, g2):
+        assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-12)   # float atomics reorder sums
+        assert not a[:100].any(), "culled Gaussians must get exactly zero gradient"
