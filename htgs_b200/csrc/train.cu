@@ -69,15 +69,18 @@ __device__ __forceinline__ CameraCols load_camera_cols(const float* __restrict__
 template <int MODE, int K> struct BwdSmem {
     static constexpr bool has_core = (MODE == HTGS_MODE_HYBRID_BLEND || MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K);
     static constexpr bool has_tail = (MODE == HTGS_MODE_HYBRID_BLEND || MODE == HTGS_MODE_OIT_BLEND);
+    static constexpr int idx_stride = ((K + 3) / 4) * 4 + 4;         // words per pixel row: 16-byte rows, odd multiple of 4 words -> conflict-free uint4 reads
     static constexpr size_t idx_off = 0;
-    static constexpr size_t idx_bytes = has_core ? size_t(K) * 64 * 4 : 0;
+    static constexpr size_t idx_bytes = has_core ? size_t(idx_stride) * 64 * 4 : 0;
     static constexpr size_t cg_off = idx_off + idx_bytes;
     static constexpr size_t cg_bytes = has_core ? size_t(K) * 64 * 16 : 0;
     static constexpr size_t tc_off = cg_off + cg_bytes;
     static constexpr size_t tc_bytes = has_tail ? 64 * 16 : 0;
     static constexpr size_t ta_off = tc_off + tc_bytes;
     static constexpr size_t ta_bytes = has_tail ? 64 * 4 : 0;
-    static constexpr size_t total = ta_off + ta_bytes;
+    static constexpr size_t stage_off = (ta_off + ta_bytes + 15) & ~size_t(15);
+    static constexpr size_t stage_bytes = 64 * (4 * 16 + 8 + 4) + 65 * 4 + 12;
+    static constexpr size_t total = stage_off + stage_bytes;
 };
 
 // HYBRID_BLEND / ALPHA_BLEND_FIRST_K / OIT_BLEND: one CTA per 8x8 tile, one thread per Gaussian of a batch.
@@ -92,7 +95,7 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
     constexpr bool kHybrid = MODE == HTGS_MODE_HYBRID_BLEND;
     constexpr bool kFirstK = MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K;
     extern __shared__ __align__(16) unsigned char smem[];
-    [[maybe_unused]] uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem + SM::idx_off);   // [K][64]
+    [[maybe_unused]] uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem + SM::idx_off);   // [64 pixels][idx_stride]
     [[maybe_unused]] float4* s_cg = reinterpret_cast<float4*>(smem + SM::cg_off);          // [K][64] (W * grad_pixel, A . grad_pixel)
     [[maybe_unused]] float4* s_tc = reinterpret_cast<float4*>(smem + SM::tc_off);          // [64] (full_weight * grad_pixel, common term)
     [[maybe_unused]] float* s_ta = reinterpret_cast<float*>(smem + SM::ta_off);            // [64] term divided by (1 - alpha)
@@ -127,7 +130,7 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
                         cg = make_float4(drgb.x, drgb.y, drgb.z, dot(f3(info), grad_pixel));
                     }
                 }
-                s_idx[k * 64 + tid] = idx;
+                s_idx[tid * SM::idx_stride + k] = idx;
                 s_cg[k * 64 + tid] = cg;
             }
         }
@@ -161,19 +164,29 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
     if constexpr (ABS_GRAD) cam = load_camera_cols(VPM);
     __syncthreads();
 
+    // ---- batches of 64 instances; the (Gaussian, pixel) candidate pairs of a batch are split EVENLY over the
+    //      64 threads (pairs of one Gaussian are contiguous, so a thread walks a few Gaussians back to back)
+    float4* s_T1 = reinterpret_cast<float4*>(smem + SM::stage_off);
+    float4* s_T2 = s_T1 + 64;
+    float4* s_T4 = s_T2 + 64;
+    float4* s_rgba = s_T4 + 64;
+    unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(s_rgba + 64);
+    uint32_t* s_g = reinterpret_cast<uint32_t*>(s_mask + 64);
+    uint32_t* s_off = s_g + 64;          // [65] exclusive prefix of the per-Gaussian pair counts
+    __shared__ uint32_t s_warp_total[2];
     const float x0 = float(tile_x * 8), y0 = float(tile_y * 8);
+    const uint32_t lane = tid & 31, warp = tid >> 5;
     for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += 64) {
+        __syncthreads();                  // previous batch fully consumed
         const uint32_t inst = batch_begin + tid;
-        const bool valid = inst < range.y;
-        uint32_t g = 0;
-        uint64_t mask = 0;
-        float4 T1 = make_float4(0, 0, 0, 0), T2 = T1, T4 = T1, rgba = T1;
-        if (valid) {
-            g = __ldg(prims_sorted + inst);
+        uint64_t my_mask = 0;
+        if (inst < range.y) {
+            const uint32_t g = __ldg(prims_sorted + inst);
             const float4 c0 = ldg4(reinterpret_cast<const float*>(cull + g));
             const float cc = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
             const float* rec = reinterpret_cast<const float*>(eval + g);
-            T1 = ldg4(rec); T2 = ldg4(rec + 4); T4 = ldg4(rec + 8); rgba = ldg4(rec + 16);
+            s_T1[tid] = ldg4(rec); s_T2[tid] = ldg4(rec + 4); s_T4[tid] = ldg4(rec + 8); s_rgba[tid] = ldg4(rec + 16);
+            s_g[tid] = g;
             const float dx0 = x0 - c0.x, dy0 = y0 - c0.y;
             #pragma unroll
             for (int r = 0; r < 8; ++r) {
@@ -183,16 +196,57 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
                 for (int i = 0; i < 8; ++i) {
                     const float dx = dx0 + float(i);
                     const float q = dx * (c0.z * dx + b2dy) + cdy2;
-                    if (q <= 1.0f) mask |= 1ull << (r * 8 + i);
+                    if (q <= 1.0f) my_mask |= 1ull << (r * 8 + i);
                 }
             }
-            mask &= inside_mask;
+            my_mask &= inside_mask;
         }
+        s_mask[tid] = my_mask;
+        const uint32_t cnt = __popcll(my_mask);
+        uint32_t inc = cnt;
+        #pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= uint32_t(o)) inc += t; }
+        if (lane == 31) s_warp_total[warp] = inc;
+        __syncthreads();
+        const uint32_t excl = inc - cnt + (warp ? s_warp_total[0] : 0u);
+        s_off[tid] = excl;
+        const uint32_t total_pairs = s_warp_total[0] + s_warp_total[1];
+        if (tid == 0) s_off[64] = total_pairs;
+        __syncthreads();
+        if (total_pairs == 0) continue;
+        // my share of the pairs
+        const uint32_t lo = uint32_t((uint64_t(tid) * total_pairs) >> 6), hi = uint32_t((uint64_t(tid + 1) * total_pairs) >> 6);
+        uint32_t remaining = hi - lo;
+        if (remaining == 0) continue;
+        uint32_t j = 0;
+        {
+            uint32_t a = 0, b = 64;      // last j with s_off[j] <= lo
+            #pragma unroll
+            for (int it = 0; it < 6; ++it) { const uint32_t mid = (a + b) >> 1; if (s_off[mid] <= lo) a = mid; else b = mid; }
+            j = a;
+        }
+        uint64_t mask = s_mask[j];
+        for (uint32_t skip = lo - s_off[j]; skip > 0; --skip) mask &= mask - 1;     // drop the pairs that belong to the previous thread
+        float4 T1 = s_T1[j], T2 = s_T2[j], T4 = s_T4[j], rgba = s_rgba[j];
+        uint32_t g = s_g[j];
         float4 aT1 = make_float4(0, 0, 0, 0), aT2 = aT1, aT4 = aT1, aC = aT1;   // aC = (dL/drgb, dL/dopacity)
         [[maybe_unused]] float abs_grad = 0.0f;
         bool touched = false;
-        while (__any_sync(0xffffffffu, mask != 0)) {
-            if (mask == 0) continue;
+        auto flush = [&]() {
+            if (touched) {
+                float4* rec = accum + size_t(g) * 5;
+                red_add_v4(rec, aT1); red_add_v4(rec + 1, aT2); red_add_v4(rec + 2, aT4); red_add_v4(rec + 3, aC);
+                if constexpr (ABS_GRAD) red_add_v4(rec + 4, make_float4(abs_grad, 0.0f, 0.0f, 0.0f));
+            }
+            aT1 = make_float4(0, 0, 0, 0); aT2 = aT1; aT4 = aT1; aC = aT1; abs_grad = 0.0f; touched = false;
+        };
+        for (; remaining > 0; --remaining) {
+            while (mask == 0) {           // next Gaussian of my share (its mask is non-empty somewhere before `hi`)
+                flush();
+                ++j;
+                mask = s_mask[j];
+                T1 = s_T1[j]; T2 = s_T2[j]; T4 = s_T4[j]; rgba = s_rgba[j]; g = s_g[j];
+            }
             const uint32_t p = uint32_t(__ffsll((long long)mask) - 1);
             mask &= mask - 1;
             const float pixel_x = x0 + float(p & 7), pixel_y = y0 + float(p >> 3);
@@ -205,8 +259,15 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
             const float denominator = dot(d, d);
             int core_idx = -1;
             if constexpr (SM::has_core) {
+                const uint4* row = reinterpret_cast<const uint4*>(s_idx + p * SM::idx_stride);
                 #pragma unroll
-                for (int k = 0; k < K; ++k) if (s_idx[k * 64 + p] == g) core_idx = k;
+                for (int k4 = 0; k4 < (K + 3) / 4; ++k4) {
+                    const uint4 v = row[k4];
+                    if (v.x == g) core_idx = 4 * k4;
+                    if (4 * k4 + 1 < K && v.y == g) core_idx = 4 * k4 + 1;
+                    if (4 * k4 + 2 < K && v.z == g) core_idx = 4 * k4 + 2;
+                    if (4 * k4 + 3 < K && v.w == g) core_idx = 4 * k4 + 3;
+                }
             }
             if constexpr (kFirstK) {
                 if (core_idx < 0) continue;                    // only stored fragments carry gradient (first_k backward.cuh:84-87)
@@ -245,11 +306,7 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
                 abs_grad += fabsf(dot(cam.c1, c4)) + fabsf(dot(cam.c2, c4)) + fabsf(dot(cam.c3, c4));
             }
         }
-        if (valid && touched) {
-            float4* rec = accum + size_t(g) * 5;
-            red_add_v4(rec, aT1); red_add_v4(rec + 1, aT2); red_add_v4(rec + 2, aT4); red_add_v4(rec + 3, aC);
-            if constexpr (ABS_GRAD) red_add_v4(rec + 4, make_float4(abs_grad, 0.0f, 0.0f, 0.0f));
-        }
+        flush();
     }
 }
 
@@ -386,7 +443,7 @@ __device__ __forceinline__ float4 quat_backward(const float4& q, const float (&d
 
 // Per-Gaussian chain rule: accumulated record -> the six output gradients
 // (hybrid_blend/kernels/backward.cuh:10-102; SH part kernel_utils.cuh:190-281).  Every output element is
-// written (zeros for Gaussians that were culled), so the caller need not clear the output tensors.
+// defined after the call (the launcher clears the tensors first), so the caller need not clear them.
 __global__ void __launch_bounds__(256) preprocess_backward_kernel(
     const float* __restrict__ positions, const float* __restrict__ scales, const float* __restrict__ rotations, const float* __restrict__ sh_rest,
     const float* __restrict__ M, const float* __restrict__ VPM, const float* __restrict__ cam_position_ptr,
@@ -396,15 +453,7 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
     const uint32_t idx = blockIdx.x * 256 + threadIdx.x;
     if (idx >= n_primitives) return;
     float3* grad_sh_rest = reinterpret_cast<float3*>(out.grad_sh_rest) + size_t(idx) * total_sh_bases;
-    if (n_touched[idx] == 0) {
-        reinterpret_cast<float3*>(out.grad_positions)[idx] = make_float3(0, 0, 0);
-        reinterpret_cast<float3*>(out.grad_scales)[idx] = make_float3(0, 0, 0);
-        reinterpret_cast<float4*>(out.grad_rotations)[idx] = make_float4(0, 0, 0, 0);
-        out.grad_opacities[idx] = 0.0f;
-        reinterpret_cast<float3*>(out.grad_sh_0)[idx] = make_float3(0, 0, 0);
-        for (int i = 0; i < total_sh_bases; ++i) grad_sh_rest[i] = make_float3(0, 0, 0);
-        return;
-    }
+    if (n_touched[idx] == 0) return;          // outputs were cleared by the launcher
     const float4 dT1 = accum[size_t(idx) * 5], dT2 = accum[size_t(idx) * 5 + 1], dT4 = accum[size_t(idx) * 5 + 2], dC = accum[size_t(idx) * 5 + 3];
     const float3 c1 = make_float3(dT1.x, dT2.x, dT4.x), c2 = make_float3(dT1.y, dT2.y, dT4.y), c3 = make_float3(dT1.z, dT2.z, dT4.z);
     const float3 c4 = make_float3(dT1.w, dT2.w, dT4.w);
@@ -490,7 +539,7 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
             -xyr * gdir.x + (xxr + zzr) * gdir.y - yzr * gdir.z,
             -xzr * gdir.x - yzr * gdir.y + (xxr + yyr) * gdir.z) * rsqrtf(norm_sq * norm_sq * norm_sq);
     }
-    for (int i = written; i < total_sh_bases; ++i) grad_sh_rest[i] = make_float3(0, 0, 0);
+    (void)written;
     const float3 dL_dposition = make_float3(dot(VPM_c1, c4), dot(VPM_c2, c4), dot(VPM_c3, c4)) + drgb_dposition;
     reinterpret_cast<float3*>(out.grad_positions)[idx] = dL_dposition;
     if (out.densification_info != nullptr) {     // hybrid_blend/kernels/backward.cuh:85-98
@@ -551,6 +600,13 @@ cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsV
     if (n == 0) return cudaSuccess;
     cudaError_t err = cudaMemsetAsync(acc.accum, 0, size_t(n) * 5 * sizeof(float4), stream);
     if (err != cudaSuccess) return err;
+    const size_t B = size_t(scene.total_sh_bases);
+    if ((err = cudaMemsetAsync(out.grad_positions, 0, size_t(n) * 3 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_scales, 0, size_t(n) * 3 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_rotations, 0, size_t(n) * 4 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_opacities, 0, size_t(n) * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_sh_0, 0, size_t(n) * 3 * 4, stream)) != cudaSuccess) return err;
+    if (B && (err = cudaMemsetAsync(out.grad_sh_rest, 0, size_t(n) * B * 3 * 4, stream)) != cudaSuccess) return err;
     const bool abs_grad = out.densification_info != nullptr && out.densification_rows == 3;
     const int k = effective_k(mode, K);
     switch (mode) {
