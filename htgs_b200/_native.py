@@ -123,6 +123,7 @@ def lib():
                 l.htgs_backward_scratch_bytes.argtypes = [ctypes.POINTER(HtgsScene)]
                 l.htgs_backward.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(HtgsTrainBlobs),
                                             ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(HtgsGradients), ctypes.c_void_p]
+                l.htgs_backward_static.argtypes = l.htgs_backward.argtypes
                 l.htgs_set_profiling.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_set_collect_stats.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_get_stage_ms.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]

@@ -448,6 +448,9 @@ int set_device_of(HtgsContext* ctx) {
 
 extern "C" {
 
+int htgs_backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                             const float* grad_image, const float* image, const HtgsGradients* grads, void* accum_ptr, void* stream_ptr);
+
 int htgs_forward_blob_sizes(const HtgsScene* scene, const HtgsView* view, size_t* per_primitive_bytes, size_t* per_tile_bytes, size_t* per_pixel_bytes) {
     const int rc = validate(scene, view);
     if (rc != HTGS_OK) return rc;
@@ -524,9 +527,20 @@ size_t htgs_backward_scratch_bytes(const HtgsScene* scene) {
     return scene ? align_up(size_t(scene->n_primitives > 0 ? scene->n_primitives : 0) * 5 * sizeof(float4) + 1) : 0;
 }
 
+int htgs_context_device(const HtgsContext* ctx) { return ctx ? ctx->device : -1; }
+
+void htgs_set_last_error(const char* message) { g_last_error = message ? message : ""; }
+
 int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                   const float* grad_image, const float* image, const HtgsGradients* grads, void* stream_ptr) {
-    if (!ctx || !blobs || !grads || !grad_image) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    if (!grads) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    if (!grads->scratch || grads->scratch_bytes < htgs_backward_scratch_bytes(scene)) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "backward scratch too small");
+    return htgs_backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, grads->scratch, stream_ptr);
+}
+
+int htgs_backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                             const float* grad_image, const float* image, const HtgsGradients* grads, void* accum_ptr, void* stream_ptr) {
+    if (!ctx || !blobs || !grads || !grad_image || !accum_ptr) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     int rc = validate(scene, view);
     if (rc != HTGS_OK) return rc;
     if ((rc = set_device_of(ctx)) != HTGS_OK) return rc;
@@ -534,7 +548,6 @@ int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view
     if (scene->n_primitives > 0 && (!grads->grad_positions || !grads->grad_scales || !grads->grad_rotations || !grads->grad_opacities || !grads->grad_sh_0 ||
                                     (scene->total_sh_bases > 0 && !grads->grad_sh_rest)))
         return fail(HTGS_ERR_INVALID_ARGUMENT, "gradient output pointers must not be null");
-    if (!grads->scratch || grads->scratch_bytes < htgs_backward_scratch_bytes(scene)) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "backward scratch too small");
     if (grads->densification_info && grads->densification_rows != 2 && grads->densification_rows != 3)
         return fail(HTGS_ERR_INVALID_ARGUMENT, "densification_info must have 2 or 3 rows");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
@@ -546,7 +559,7 @@ int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view
     if (!blobs->per_primitive || blobs->per_primitive_bytes < P.bytes || !blobs->per_instance || blobs->per_instance_bytes < I.bytes ||
         !blobs->per_pixel || blobs->per_pixel_bytes < X.bytes || !blobs->per_tile)
         return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "a forward blob is missing or too small");
-    const GradAccumBuffers acc{static_cast<float4*>(grads->scratch)};
+    const GradAccumBuffers acc{static_cast<float4*>(accum_ptr)};
     const BackwardOutputs out{grads->grad_positions, grads->grad_scales, grads->grad_rotations, grads->grad_opacities, grads->grad_sh_0, grads->grad_sh_rest,
                               grads->densification_info, grads->densification_info ? grads->densification_rows : 0, grads->use_distance_scaling != 0};
     const cudaError_t err = launch_backward(view->mode, view->K, *scene, *view, geo, P.prim, I.inst.prims[plan.final_buffer], static_cast<const uint2*>(blobs->per_tile),

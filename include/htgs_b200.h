@@ -184,6 +184,26 @@ size_t htgs_backward_scratch_bytes(const HtgsScene* scene);
 int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                   const float* grad_image, const float* image, const HtgsGradients* grads, void* stream);
 
+/*
+ * Backward pass that allocates nothing.  No counterpart in the reference.
+ *
+ * Same inputs, outputs and results as htgs_backward, but `grads->scratch` is ignored: the per-Gaussian
+ * accumulation records live in a fixed array inside the library (10 MiB of device memory per GPU that loads
+ * the library, held until the process exits).  It exists for hosts that cannot hand over a scratch buffer
+ * because they may not allocate device memory at the point of the call: a plug-in inside an application that
+ * owns all allocations, or a process that has given every free byte to another allocator.  The call performs
+ * no cudaMalloc / cudaFree and calls no allocating library routine.
+ *   - Scenes with more than htgs_backward_static_max_gaussians() (131072) Gaussians are rejected with
+ *     HTGS_ERR_INVALID_ARGUMENT; use htgs_backward for those.
+ *   - The first call on a device looks up the device address of the array (cudaGetSymbolAddress); make that
+ *     first call before any stream capture.
+ *   - All calls on a device share the one array.  Each call clears it before use, but two calls whose kernels
+ *     overlap on the GPU (different streams, different host threads) race on it: run them one after the other.
+ */
+int htgs_backward_static_max_gaussians(void);
+int htgs_backward_static(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                         const float* grad_image, const float* image, const HtgsGradients* grads, void* stream);
+
 /* Measurement aids (off by default; they do not change results).
  * Profiling: CUDA events are recorded on the frame's stream between the stages; after the call
  * htgs_get_stage_ms fills out_ms[0..HTGS_N_STAGES) with the device time of each stage in ms.
