@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--views-per-step", type=int, default=8)
     ap.add_argument("--n-gaussians", type=int, default=3_000_000, help="scale the workload down for quick checks (invalid as a benchmark)")
+    ap.add_argument("--workload", default="render", choices=["render", "train"],
+                    help="render: configuration 1 (default, the headline metric); train: configuration 2 (fwd+bwd, L1 loss, one view per GPU, gradient all-reduce)")
     ap.add_argument("--reference-kind", default="auto", choices=["auto", "cuda", "cpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-views", type=int, default=3)
@@ -148,6 +150,65 @@ def run_reference_cpu(args, scene, workload_name, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, device, dist, rank, world, workload_name):
+    """Configuration 2: one view per GPU per step, forward + backward through `diff_rasterize` with an L1 loss against a
+    seeded uniform target, gradients of the six rasterizer inputs all-reduced over the ranks (NCCL)."""
+    import torch
+    n_views = len(scene.views)
+    v0 = scene.views[0]
+    gen = torch.Generator(device="cpu").manual_seed(1234)
+    target = torch.rand((3, v0.height, v0.width), generator=gen).to(device)
+    leaves = [t.clone().requires_grad_(True) for t in tensors]
+    empty = torch.empty(0, device=device)
+
+    def step(s):
+        vi = parallel.step_view_indices(s, 1, rank, world, n_views)[0]
+        for l in leaves:
+            l.grad = None
+        image = mod.diff_rasterize(*leaves, empty, settings(cams_dev[vi]), False)
+        loss = (image - target).abs().mean()
+        loss.backward()
+        if dist is not None:
+            parallel.allreduce_gradients([l.grad for l in leaves])
+        return loss
+
+    for s in range(args.warmup):
+        step(s)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(device.index)
+    sampler.start()
+    time.sleep(0.25)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for s in range(args.warmup, args.warmup + args.steps):
+        loss = step(s)
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    if dist is not None:
+        dist.barrier()
+    clocks = sampler.stop(t0, t1)
+    ms = parallel.max_over_ranks(e0.elapsed_time(e1), device)
+    n = scene.n
+    grad_bytes = n * (3 + 3 + 4 + 1 + 3 + 3 * scene.sh_rest.shape[1]) * 4
+    line = {"metric": "train-steps/s", "value": args.steps / (ms / 1000.0), "unit": "steps/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name.replace("config1", "config2 (fwd+bwd, L1, one view per GPU)"), "views_per_step": world,
+                       "allreduce_bytes_per_rank": grad_bytes if world > 1 else 0, "parallelism": f"view-partitioned x{world} + gradient all-reduce"},
+            "clocks": clocks, "final_loss": float(loss.item())}
+    if is_reference:
+        line["impl"] = "reference"
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     rank, world, local_rank = parallel.rank_world()
@@ -197,6 +258,10 @@ def main():
         return mod.RasterizerSettings(M=cam[0], VPM=cam[1], cam_position=cam[2], mode=mode_enum, K=scene.K, active_sh_bases=scene.active_sh_bases,
                                       width=v0.width, height=v0.height, near_plane=v0.near_plane, far_plane=v0.far_plane, scale_modifier=1.0)
 
+    if args.workload == "train":
+        run_training(args, mod, ref_mod is not None, scene, tensors, cams_dev, settings, device, dist, rank, world, workload_name)
+        return
+
     launches = [0]
 
     def render_resident(view_idx):
@@ -206,16 +271,27 @@ def main():
         return out
 
     n_pix = v0.width * v0.height
-    host_image = torch.empty((3, v0.height, v0.width), dtype=torch.float32).pin_memory()
-    host_depth = torch.empty((1, v0.height, v0.width), dtype=torch.float32).pin_memory()
+
+    # end-to-end frame: camera H2D from pinned memory -> rasterize -> image + depth D2H into pinned memory.  The copies back
+    # run on a second stream into two alternating pinned buffers, so that they overlap the next frame's kernels.
+    copy_stream = torch.cuda.Stream(device=device)
+    host_out = [(torch.empty((3, v0.height, v0.width), dtype=torch.float32).pin_memory(),
+                 torch.empty((1, v0.height, v0.width), dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+    e2e_count = [0]
 
     def render_e2e(view_idx):
         cam = tuple(a.to(device, non_blocking=True) for a in cams_host[view_idx])
         image, depth = mod.rasterize(*tensors, settings(cam), True, False)
-        host_image.copy_(image, non_blocking=True)
-        host_depth.copy_(depth, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return float(host_image[0, 0, 0])
+        h_img, h_depth, done = host_out[e2e_count[0] % 2]
+        e2e_count[0] += 1
+        done.synchronize()                       # the copy that used this pinned buffer two frames ago has finished
+        copy_stream.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(copy_stream):
+            h_img.copy_(image, non_blocking=True)
+            h_depth.copy_(depth, non_blocking=True)
+            done.record(copy_stream)
+        image.record_stream(copy_stream)
+        depth.record_stream(copy_stream)
 
     def timed(fn, steps, warmup, sample_clocks=False):
         for s in range(warmup):
@@ -236,6 +312,7 @@ def main():
         for s in range(warmup, warmup + steps):
             for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views):
                 fn(vi)
+        torch.cuda.current_stream(device).wait_stream(copy_stream)   # outstanding copies back belong to the timed region
         e1.record()
         torch.cuda.synchronize()
         t1 = time.time()
@@ -279,7 +356,7 @@ def main():
     ctx = _native.context(local_rank)
     lib = _native.lib()
     import ctypes
-    probe_views = parallel.step_view_indices(0, min(args.views_per_step, 8), rank, world, n_views)
+    probe_views = [parallel.step_view_indices(args.warmup + (i * args.steps) // 8, args.views_per_step, rank, world, n_views)[i % args.views_per_step] for i in range(8)]
     lib.htgs_set_profiling(ctx, 1)
     stage = np.zeros((len(probe_views), 7), np.float64)
     buf = (ctypes.c_float * 7)()
