@@ -87,17 +87,32 @@ __device__ __forceinline__ FragmentFront fragment_front(const float4& VPMT1, con
     return f;
 }
 
-// The reference's insertion chain (hybrid_blend/kernels/inference.cuh:159-167) on (depth, slot) pairs.
+// The reference's insertion chain (hybrid_blend/kernels/inference.cuh:159-167) on (depth, slot) pairs:
+//     for k: if (carried.depth < kd[k]) swap(carried, entry[k]);
+// Because kd is sorted, the DEPTH carried into level k is always max(depth, kd[k-1]) - with or without ties -
+// so every level's comparison and new depth are computed from the old buffer in parallel; only the carried
+// slot is still passed from level to level (one select per level on the critical path instead of a compare
+// and a select).  Results, including the reference's behaviour for equal depths, are bit-identical to the chain.
 // On return `depth` is the depth of the entry that fell out of the buffer and the result its slot.
 template <int K>
 __device__ __forceinline__ uint32_t kbuffer_insert(float (&kd)[K], uint32_t (&ks)[K], float& depth, uint32_t slot) {
+    bool p[K];
+    float nd[K];
     #pragma unroll
     for (int k = 0; k < K; ++k) {
-        if (depth < kd[k]) {
-            const float td = kd[k]; kd[k] = depth; depth = td;
-            const uint32_t ts = ks[k]; ks[k] = slot; slot = ts;
-        }
+        const float carried = k == 0 ? depth : fmaxf(depth, kd[k - 1]);
+        p[k] = carried < kd[k];
+        nd[k] = p[k] ? carried : kd[k];
     }
+    const float out_depth = fmaxf(depth, kd[K - 1]);
+    #pragma unroll
+    for (int k = 0; k < K; ++k) {
+        const uint32_t mine = ks[k];
+        ks[k] = p[k] ? slot : mine;
+        slot = p[k] ? mine : slot;
+        kd[k] = nd[k];
+    }
+    depth = out_depth;
     return slot;
 }
 
