@@ -130,7 +130,7 @@ __device__ __forceinline__ float length(const float3& v) { return sqrtf(dot(v, v
 __device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 
 // ---------------------------------------------------------------------------
-// PTX wrappers: mbarrier + bulk asynchronous copy (TMA, non-tensor, no multicast)
+// PTX wrappers: mbarrier + bulk asynchronous copy (TMA, non-tensor, single-CTA destination)
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
