@@ -124,6 +124,8 @@ def lib():
                 l.htgs_backward.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(HtgsTrainBlobs),
                                             ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(HtgsGradients), ctypes.c_void_p]
                 l.htgs_backward_static.argtypes = l.htgs_backward.argtypes
+                l.htgs_update_3d_filter.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
+                                                    ctypes.c_int32] + [ctypes.c_float] * 7 + [ctypes.c_void_p]
                 l.htgs_set_profiling.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_set_collect_stats.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_get_stage_ms.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]

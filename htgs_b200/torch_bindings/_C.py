@@ -170,5 +170,22 @@ def update_max_weights(*args):
     raise NotImplementedError("htgs_b200: update_max_weights is outside the rasterizer hot path of this build")
 
 
-def update_3d_filter_cuda(*args):
-    raise NotImplementedError("htgs_b200: update_3d_filter is outside the rasterizer hot path of this build")
+def update_3d_filter_cuda(positions, w2c, filter_3d, visibility_mask, width, height, focal_x, focal_y, center_x, center_y, near_plane,
+                          clipping_tolerance, distance2filter):
+    """`_C.update_3d_filter_cuda` (filter3d/include/filter3d_api.h:7-20): updates `filter_3d` and `visibility_mask` in place."""
+    device = positions.device
+    if device.type != "cuda":
+        raise ValueError("htgs_b200: tensors must live on a CUDA device")
+    n = positions.shape[0]
+    if positions.dtype != torch.float32 or w2c.dtype != torch.float32 or filter_3d.dtype != torch.float32 or visibility_mask.dtype != torch.bool:
+        raise TypeError("positions, w2c, filter_3d must be float32 and visibility_mask bool")
+    if tuple(positions.shape) != (n, 3) or w2c.numel() != 16 or filter_3d.numel() != n or visibility_mask.numel() != n:
+        raise ValueError("expected positions [N,3], w2c [4,4], filter_3d [N,1], visibility_mask [N]")
+    if not (filter_3d.is_contiguous() and visibility_mask.is_contiguous()):
+        raise ValueError("filter_3d and visibility_mask are updated in place and must be contiguous")
+    positions, w2c = positions.contiguous(), w2c.contiguous()
+    with torch.cuda.device(device):
+        rc = _native.lib().htgs_update_3d_filter(positions.data_ptr(), w2c.data_ptr(), filter_3d.data_ptr(), visibility_mask.data_ptr(), n, int(width),
+                                                 int(height), float(focal_x), float(focal_y), float(center_x), float(center_y), float(near_plane),
+                                                 float(clipping_tolerance), float(distance2filter), torch.cuda.current_stream(device).cuda_stream)
+    _native.check(rc)

@@ -204,6 +204,16 @@ int htgs_backward_static_max_gaussians(void);
 int htgs_backward_static(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                          const float* grad_image, const float* image, const HtgsGradients* grads, void* stream);
 
+/*
+ * 3D smoothing-filter update for one view.  Replaces `_C.update_3d_filter_cuda` = update_3d_filter_wrapper
+ * (filter3d/include/filter3d_api.h:7-20, filter3d/src/filter3d_api.cu:6-47).  positions [N,3], w2c [4,4] row-major,
+ * filter_3d [N] (updated in place: min with distance2filter * view depth), visibility_mask [N] bytes (set to 1 for points
+ * in view that were updated).  Stream-ordered, no host synchronisation.
+ */
+int htgs_update_3d_filter(const float* positions, const float* w2c, float* filter_3d, uint8_t* visibility_mask, int32_t n_points,
+                          int32_t width, int32_t height, float focal_x, float focal_y, float center_x, float center_y, float near_plane,
+                          float clipping_tolerance, float distance2filter, void* stream);
+
 /* Measurement aids (off by default; they do not change results).
  * Profiling: CUDA events are recorded on the frame's stream between the stages; after the call
  * htgs_get_stage_ms fills out_ms[0..HTGS_N_STAGES) with the device time of each stage in ms.

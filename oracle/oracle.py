@@ -135,3 +135,27 @@ def render(scene, view, mode: Optional[int] = None, K: Optional[int] = None, sca
                 int(use_median_depth), _p(image), _p(depth), _p(alpha), int(n_threads or hardware_threads()))
     del keep
     return image, depth, alpha, int(n_inst)
+
+
+def update_3d_filter(positions, w2c, filter_3d, visibility_mask, width, height, focal_x, focal_y, center_x, center_y, near_plane,
+                     clipping_tolerance, distance2filter):
+    """numpy restatement of the 3D-filter update (filter3d/src/filter3d_kernels.cu:6-35, filter3d/src/filter3d_api.cu:23-33).
+    Returns new (filter_3d, visibility_mask); float32 arithmetic in the reference's order."""
+    f32 = np.float32
+    p = np.asarray(positions, f32)
+    w = np.asarray(w2c, f32).reshape(4, 4)
+    bounds = f32(clipping_tolerance) + f32(0.5)
+    mx, my = bounds * f32(width), bounds * f32(height)
+    ox, oy = f32(center_x) - f32(0.5) * f32(width), f32(center_y) - f32(0.5) * f32(height)
+    left, right = (-mx - ox) / f32(focal_x), (mx - ox) / f32(focal_x)
+    top, bottom = (-my - oy) / f32(focal_y), (my - oy) / f32(focal_y)
+
+    def row(r):
+        return (w[r, 0] * p[:, 0] + w[r, 1] * p[:, 1] + w[r, 2] * p[:, 2] + w[r, 3]).astype(f32)
+    z, x, y = row(2), row(0), row(1)
+    inside = (z >= f32(near_plane)) & ~((x < left * z) | (x > right * z)) & ~((y < top * z) | (y > bottom * z))
+    new = (f32(distance2filter) * z).astype(f32)
+    old = np.asarray(filter_3d, f32).reshape(-1)
+    update = inside & ~(old < new)
+    out = np.where(update, new, old).astype(f32)
+    return out.reshape(np.asarray(filter_3d).shape), np.asarray(visibility_mask, bool).reshape(-1) | update
