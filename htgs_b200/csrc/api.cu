@@ -84,19 +84,19 @@ FrameLayout carve_frame(void* blob, int n_primitives, int n_tiles, const SortPla
     return L;
 }
 
-int validate(const HtgsScene* scene, const HtgsView* view) {
+int validate(const HtgsScene* scene, const HtgsView* view, bool needs_colour = true) {
     if (!scene || !view) return fail(HTGS_ERR_INVALID_ARGUMENT, "scene and view must not be null");
     if (view->mode < 0 || view->mode > 3) return fail(HTGS_ERR_UNSUPPORTED_MODE, "unsupported rasterizer mode");
     if (scene->n_primitives < 0) return fail(HTGS_ERR_INVALID_ARGUMENT, "n_primitives must be >= 0");
     if (view->width <= 0 || view->height <= 0) return fail(HTGS_ERR_INVALID_ARGUMENT, "width and height must be positive");
     if (view->width > 65535 * 8 || view->height > 65535 * 8) return fail(HTGS_ERR_INVALID_ARGUMENT, "image too large for 16-bit tile coordinates");
-    if (scene->n_primitives > 0 && (!scene->positions || !scene->scales || !scene->rotations || !scene->opacities || !scene->sh_0))
+    if (scene->n_primitives > 0 && (!scene->positions || !scene->scales || !scene->rotations || !scene->opacities || (needs_colour && !scene->sh_0)))
         return fail(HTGS_ERR_INVALID_ARGUMENT, "per-Gaussian input pointers must not be null");
     if (scene->total_sh_bases < 0) return fail(HTGS_ERR_INVALID_ARGUMENT, "total_sh_bases must be >= 0");
     const int a = view->active_sh_bases;
     if (a != 1 && a != 4 && a != 9 && a != 16) return fail(HTGS_ERR_INVALID_ARGUMENT, "active_sh_bases must be 1, 4, 9 or 16");
-    if (a - 1 > scene->total_sh_bases) return fail(HTGS_ERR_INVALID_ARGUMENT, "active_sh_bases needs more coefficients than sh_rest holds");
-    if (a > 1 && !scene->sh_rest) return fail(HTGS_ERR_INVALID_ARGUMENT, "sh_rest must not be null when active_sh_bases > 1");
+    if (needs_colour && a - 1 > scene->total_sh_bases) return fail(HTGS_ERR_INVALID_ARGUMENT, "active_sh_bases needs more coefficients than sh_rest holds");
+    if (needs_colour && a > 1 && !scene->sh_rest) return fail(HTGS_ERR_INVALID_ARGUMENT, "sh_rest must not be null when active_sh_bases > 1");
     if (!view->M || !view->VPM || !view->cam_position) return fail(HTGS_ERR_INVALID_ARGUMENT, "camera pointers must not be null");
     if ((view->mode == HTGS_MODE_HYBRID_BLEND || view->mode == HTGS_MODE_ALPHA_BLEND_FIRST_K) && view->K < 1)
         return fail(HTGS_ERR_INVALID_ARGUMENT, "K must be >= 1");
@@ -174,7 +174,8 @@ size_t htgs_render_workspace_bytes(const HtgsScene* scene, const HtgsView* view,
 }
 
 static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const SortPlan& plan,
-                     const FrameLayout& L, BlendOutputs out, cudaStream_t stream, uint32_t* launches) {
+                     const FrameLayout& L, BlendOutputs out, cudaStream_t stream, uint32_t* launches, float* max_weights = nullptr,
+                     float weight_threshold = 0.0f) {
     cudaError_t err;
     const bool prof = ctx->profiling;
     if (prof && !ctx->events_created) {
@@ -193,7 +194,9 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
     if ((err = launch_emit_sort_ranges(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream,
                                        prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "binning");
     const uint32_t* prims_sorted = L.inst.prims[plan.final_buffer];
-    if ((err = launch_blend(view.mode, view.K, false, geo, L.prim, prims_sorted, L.tile_ranges, out, TrainPixelBuffers{}, L.status, stream)) != cudaSuccess) return fail_cuda(err, "blend");
+    if (max_weights) {
+        if ((err = launch_max_weights(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, max_weights, weight_threshold, stream)) != cudaSuccess) return fail_cuda(err, "max weights");
+    } else if ((err = launch_blend(view.mode, view.K, false, geo, L.prim, prims_sorted, L.tile_ranges, out, TrainPixelBuffers{}, L.status, stream)) != cudaSuccess) return fail_cuda(err, "blend");
     *launches += 1;
     if (prof) cudaEventRecord(ev[6], stream);
     if ((err = cudaMemcpyAsync(ctx->host_status, L.status, sizeof(FrameStatus), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return fail_cuda(err, "status copy");
@@ -205,12 +208,28 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
     return HTGS_OK;
 }
 
+static int render_core(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
+                       int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info,
+                       float* max_weights, float weight_threshold);
+
 int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
                 int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info) {
-    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
-    int rc = validate(scene, view);
-    if (rc != HTGS_OK) return rc;
     if (!image || !depth) return fail(HTGS_ERR_INVALID_ARGUMENT, "image and depth must not be null");
+    return render_core(ctx, scene, view, image, depth, alpha, to_chw, use_median_depth, workspace, workspace_bytes, stream_ptr, info, nullptr, 0.0f);
+}
+
+int htgs_update_max_weights(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* max_weights, float weight_threshold,
+                            void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info) {
+    if (!max_weights) return fail(HTGS_ERR_INVALID_ARGUMENT, "max_weights must not be null");
+    return render_core(ctx, scene, view, nullptr, nullptr, nullptr, 1, 0, workspace, workspace_bytes, stream_ptr, info, max_weights, weight_threshold);
+}
+
+static int render_core(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
+                       int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info,
+                       float* max_weights, float weight_threshold) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    int rc = validate(scene, view, max_weights == nullptr);
+    if (rc != HTGS_OK) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     cudaError_t err;
     int current = -1;
@@ -255,7 +274,7 @@ int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, 
         } else {
             L = carve_frame(workspace, scene->n_primitives, geo.n_tiles, plan, capacity, false);
         }
-        rc = run_frame(ctx, *scene, *view, geo, plan, L, out, stream, &launches);
+        rc = run_frame(ctx, *scene, *view, geo, plan, L, out, stream, &launches, max_weights, weight_threshold);
         if (rc != HTGS_OK) return rc;
         const FrameStatus st = *ctx->host_status;
         ctx->last_layout = L; ctx->last_plan = plan; ctx->last_geo = geo; ctx->last_n_instances = st.overflow ? 0 : st.n_instances; ctx->has_last = true;

@@ -79,6 +79,10 @@ int effective_k(int mode, int K);
 cudaError_t launch_blend(int mode, int K, bool train, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
                          const uint2* tile_ranges, const BlendOutputs& out, const TrainPixelBuffers& tout, FrameStatus* status, cudaStream_t stream);
 
+// weights.cu
+cudaError_t launch_max_weights(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                               float* max_weights, float weight_threshold, cudaStream_t stream);
+
 // train.cu: backward pass
 struct GradAccumBuffers {
     float4* accum;           // [N][5] float4: dL/dVPMT1, dL/dVPMT2, dL/dVPMT4, (dL/drgb, dL/dopacity), (sum |dL/dposition|, 0, 0, 0)

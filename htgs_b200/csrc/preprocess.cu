@@ -193,7 +193,8 @@ __global__ void __launch_bounds__(kPreprocessBlock) preprocess_kernel(
                         else rec.mt3 = make_float4(dot3_pinned_alt(f3(M3), u), dot3_pinned(f3(M3), v), dot3_pinned(f3(M3), w), z);
                         const float3 cam_position = make_float3(__ldg(cam_position_ptr), __ldg(cam_position_ptr + 1), __ldg(cam_position_ptr + 2));
                         uint8_t clamp_bits = 0;
-                        const float3 rgb = sh_to_rgb<TRAIN>(sh_0, sh_rest, position, cam_position, idx, active_sh_bases, total_sh_bases, &clamp_bits);
+                        const float3 rgb = sh_0 ? sh_to_rgb<TRAIN>(sh_0, sh_rest, position, cam_position, idx, active_sh_bases, total_sh_bases, &clamp_bits)
+                                                : make_float3(0.0f, 0.0f, 0.0f);   // colour-less callers (update_max_weights)
                         rec.rgba = make_float4(rgb.x, rgb.y, rgb.z, opacity);
                         float4* dst = reinterpret_cast<float4*>(out.eval + idx);
                         dst[0] = rec.vpmt1; dst[1] = rec.vpmt2; dst[2] = rec.vpmt4; dst[3] = rec.mt3; dst[4] = rec.rgba;

@@ -1,0 +1,196 @@
+// update_max_weights: per-Gaussian maximum blending weight over the pixels of one view (importance for pruning).
+// Replaces update_max_weights_cu of the four modes
+//   rasterization/include/hybrid_blend/kernels/update_max_weights.cuh:59-212
+//   rasterization/include/alpha_blend_first_k/kernels/update_max_weights.cuh:60-
+//   rasterization/include/alpha_blend_global_ordering/kernels/update_max_weights.cuh:59-
+//   rasterization/include/oit_blend/kernels/update_max_weights.cuh:57-
+// The result is a maximum (atomicMax on the bit pattern of non-negative floats), so it does not depend on the
+// order of evaluation and is bit-identical to the reference's.  This helper is called a few times per training
+// run, not per frame; it uses plain staged loads and the conservative outline only as a per-pixel skip test.
+#include "kernels.h"
+
+namespace htgs {
+
+namespace {
+
+template <int MODE> struct WShape {
+    static constexpr int tw = ModeTraits<MODE>::tile_w, th = ModeTraits<MODE>::tile_h, threads = tw * th;
+};
+
+__device__ __forceinline__ void raise_weight(unsigned int* max_weights, uint32_t primitive_idx, float weight) {
+    const unsigned int bits = __float_as_uint(weight);
+    if (max_weights[primitive_idx] < bits) atomicMax(&max_weights[primitive_idx], bits);
+}
+
+template <int MODE, int K>
+__global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
+    const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
+    const CullRecord* __restrict__ cull, unsigned int* __restrict__ max_weights, uint32_t width, uint32_t height, uint32_t grid_w, float weight_threshold)
+{
+    using MT = ModeTraits<MODE>;
+    using WS = WShape<MODE>;
+    constexpr bool kHybrid = MODE == HTGS_MODE_HYBRID_BLEND, kFirstK = MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K;
+    constexpr bool kGlobal = MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING, kOit = MODE == HTGS_MODE_OIT_BLEND;
+    constexpr bool kBuffer = kHybrid || kFirstK;
+    __shared__ float4 s_T1[WS::threads], s_T2[WS::threads], s_T4[WS::threads], s_M3[WS::threads], s_c0[WS::threads];
+    __shared__ float s_cc[WS::threads], s_op[WS::threads];
+    __shared__ uint32_t s_g[WS::threads];
+    const uint32_t tid = threadIdx.x;
+    const uint32_t px_i = blockIdx.x * WS::tw + (tid % WS::tw), py_i = blockIdx.y * WS::th + (tid / WS::tw);
+    const bool inside = px_i < width && py_i < height;
+    const float pixel_x = __uint2float_rn(px_i), pixel_y = __uint2float_rn(py_i);
+    const uint2 range = tile_ranges[blockIdx.y * grid_w + blockIdx.x];
+
+    [[maybe_unused]] float kd[kBuffer ? K : 1], ka[kBuffer ? K : 1];
+    [[maybe_unused]] uint32_t ki[kBuffer ? K : 1];
+    if constexpr (kBuffer) {
+        #pragma unroll
+        for (int k = 0; k < K; ++k) { kd[k] = FLT_MAX; ka[k] = 0.0f; ki[k] = 0xffffffffu; }
+    }
+    float alpha_sum = 0.0f, transmittance = 1.0f;   // HB: tail; OIT / GO: pixel
+    bool done = !inside;
+    float second_pass_weight = 0.0f;
+
+    for (int pass = 0; pass < ((kHybrid || kOit) ? 2 : 1); ++pass) {
+        for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += WS::threads) {
+            if constexpr (kGlobal) { if (__syncthreads_count(done) == WS::threads) break; } else __syncthreads();
+            const uint32_t batch = min(uint32_t(WS::threads), range.y - batch_begin);
+            if (tid < batch) {
+                const uint32_t g = __ldg(prims_sorted + batch_begin + tid);
+                const float* rec = reinterpret_cast<const float*>(eval + g);
+                s_g[tid] = g;
+                s_T1[tid] = ldg4(rec); s_T2[tid] = ldg4(rec + 4); s_T4[tid] = ldg4(rec + 8); s_M3[tid] = ldg4(rec + 12);
+                s_op[tid] = __ldg(rec + 19);
+                s_c0[tid] = ldg4(reinterpret_cast<const float*>(cull + g));
+                s_cc[tid] = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
+            }
+            __syncthreads();
+            if (done || (pass == 1 && !(second_pass_weight >= weight_threshold))) continue;
+            for (uint32_t j = 0; j < batch; ++j) {
+                if (pass == 0) {   // fragments that can pass the alpha test lie inside the outline; the second pass has no alpha test
+                    const float4 c0 = s_c0[j];
+                    const float dx = pixel_x - c0.x, dy = pixel_y - c0.y;
+                    if (!(dx * (c0.z * dx + c0.w * dy) + s_cc[j] * dy * dy <= 1.0f)) continue;
+                }
+                const float4 plane_x_diag = s_T1[j] - s_T4[j] * pixel_x;
+                const float4 plane_y_diag = s_T2[j] - s_T4[j] * pixel_y;
+                const float3 nx = f3(plane_x_diag), ny = f3(plane_y_diag);
+                const float3 m = plane_x_diag.w * ny - nx * plane_y_diag.w;
+                const float3 d = cross(nx, ny);
+                const float numerator_rho2 = dot(m, m);
+                const float denominator = dot(d, d);
+                if (numerator_rho2 > MT::max_cutoff_sq * denominator) continue;
+                const float denominator_rcp = 1.0f / denominator;
+                if (pass == 1) {
+                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                    const float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
+                    const float blending_weight = alpha * second_pass_weight;
+                    if (blending_weight < weight_threshold) continue;
+                    raise_weight(max_weights, s_g[j], blending_weight);
+                    continue;
+                }
+                if constexpr (kFirstK) {
+                    const float3 e = cross(d, m) * denominator_rcp;
+                    const float4 MT3 = s_M3[j];
+                    float depth = dot(f3(MT3), e) + MT3.w;
+                    if (depth >= kd[K - 1]) continue;
+                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                    float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
+                    if (alpha < MT::min_alpha) continue;
+                    uint32_t primitive_idx = s_g[j];
+                    #pragma unroll
+                    for (int k = 0; k < K; ++k)
+                        if (depth < kd[k]) {
+                            const float td = kd[k]; kd[k] = depth; depth = td;
+                            const float ta = ka[k]; ka[k] = alpha; alpha = ta;
+                            const uint32_t ti = ki[k]; ki[k] = primitive_idx; primitive_idx = ti;
+                        }
+                } else {
+                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                    float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
+                    if (alpha < MT::min_alpha) continue;
+                    if constexpr (kHybrid) {
+                        const float3 e = cross(d, m) * denominator_rcp;
+                        const float4 MT3 = s_M3[j];
+                        float depth = dot(f3(MT3), e) + MT3.w;
+                        if (depth < kd[K - 1] && alpha >= MT::min_alpha_core) {
+                            uint32_t primitive_idx = s_g[j];
+                            #pragma unroll
+                            for (int k = 0; k < K; ++k)
+                                if (depth < kd[k]) {
+                                    const float td = kd[k]; kd[k] = depth; depth = td;
+                                    const float ta = ka[k]; ka[k] = alpha; alpha = ta;
+                                    const uint32_t ti = ki[k]; ki[k] = primitive_idx; primitive_idx = ti;
+                                }
+                        }
+                        alpha_sum += alpha;
+                        transmittance *= 1.0f - alpha;
+                    } else if constexpr (kGlobal) {
+                        const float blending_weight = transmittance * alpha;
+                        transmittance *= 1.0f - alpha;
+                        if (transmittance < kTransmittanceThreshold) done = true;
+                        if (!(blending_weight < weight_threshold)) raise_weight(max_weights, s_g[j], blending_weight);
+                        if (done) break;
+                    } else {
+                        alpha_sum += alpha;
+                        transmittance *= 1.0f - alpha;
+                    }
+                }
+            }
+        }
+        if (pass == 0 && inside) {
+            if constexpr (kBuffer) {
+                float t = 1.0f;
+                #pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    const float alpha = ka[k];
+                    const float blending_weight = t * alpha;
+                    t *= 1.0f - alpha;
+                    if (t < kTransmittanceThreshold) t = 0.0f;
+                    if (blending_weight < weight_threshold || ki[k] == 0xffffffffu) continue;
+                    raise_weight(max_weights, ki[k], blending_weight);
+                }
+                if constexpr (kHybrid) { if (alpha_sum >= weight_threshold) second_pass_weight = t * (1.0f - transmittance) * (1.0f / alpha_sum); }
+            }
+            if constexpr (kOit) { if (alpha_sum >= weight_threshold) second_pass_weight = (1.0f - transmittance) * (1.0f / alpha_sum); }
+        }
+    }
+}
+
+template <int MODE, int K>
+cudaError_t launch_w(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges, float* max_weights,
+                     float weight_threshold, cudaStream_t stream) {
+    const dim3 grid(geo.grid_w, geo.grid_h, 1);
+    max_weights_kernel<MODE, K><<<grid, WShape<MODE>::threads, 0, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, reinterpret_cast<unsigned int*>(max_weights),
+                                                                            uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), weight_threshold);
+    return cudaGetLastError();
+}
+
+template <int MODE>
+cudaError_t launch_w_k(int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges, float* max_weights,
+                       float weight_threshold, cudaStream_t stream) {
+    switch (K) {
+        case 32: return launch_w<MODE, 32>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        case 16: return launch_w<MODE, 16>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        case 8: return launch_w<MODE, 8>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        case 4: return launch_w<MODE, 4>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        case 2: return launch_w<MODE, 2>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        default: return launch_w<MODE, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_max_weights(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                               float* max_weights, float weight_threshold, cudaStream_t stream) {
+    const int k = effective_k(mode, K);
+    switch (mode) {
+        case HTGS_MODE_HYBRID_BLEND: return launch_w_k<HTGS_MODE_HYBRID_BLEND>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        case HTGS_MODE_ALPHA_BLEND_FIRST_K: return launch_w_k<HTGS_MODE_ALPHA_BLEND_FIRST_K>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: return launch_w<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        case HTGS_MODE_OIT_BLEND: return launch_w<HTGS_MODE_OIT_BLEND, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace htgs

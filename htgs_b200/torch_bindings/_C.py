@@ -166,8 +166,33 @@ def backward(densification_info, grad_image, image, positions, scales, rotations
     return grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest
 
 
-def update_max_weights(*args):
-    raise NotImplementedError("htgs_b200: update_max_weights is outside the rasterizer hot path of this build")
+def update_max_weights(max_weights, positions, scales, rotations, opacities, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases,
+                       width, height, near_plane, far_plane, scale_modifier, weight_threshold):
+    """`_C.update_max_weights` (rasterization/include/rasterization_api.h:79-97): raises `max_weights` [N,1] in place."""
+    global last_frame_info
+    device = positions.device
+    if device.type != "cuda":
+        raise ValueError("htgs_b200 rasterizer: tensors must live on a CUDA device")
+    n = positions.shape[0]
+    for name, t in (("max_weights", max_weights), ("positions", positions), ("scales", scales), ("rotations", rotations), ("opacities", opacities),
+                    ("M", M), ("VPM", VPM), ("cam_position", cam_position)):
+        if t.dtype != torch.float32 or t.device != device:
+            raise TypeError(f"{name} must be a float32 tensor on {device}")
+    if tuple(positions.shape) != (n, 3) or tuple(scales.shape) != (n, 3) or tuple(rotations.shape) != (n, 4) or opacities.numel() != n:
+        raise ValueError("expected positions [N,3], scales [N,3], rotations [N,4], opacities [N,1]")
+    if max_weights.numel() != n or not max_weights.is_contiguous():
+        raise ValueError("max_weights is updated in place and must be a contiguous tensor of N values")
+    tensors = [t.contiguous() for t in (positions, scales, rotations, opacities)]
+    M, VPM, cam_position = M.contiguous(), VPM.contiguous(), cam_position.contiguous()
+    with torch.cuda.device(device):
+        scene = HtgsScene(tensors[0].data_ptr(), tensors[1].data_ptr(), tensors[2].data_ptr(), tensors[3].data_ptr(), None, None, n, 0)
+        view = HtgsView(M.data_ptr(), VPM.data_ptr(), cam_position.data_ptr(), int(rasterizer_mode), int(K), int(active_sh_bases), int(width), int(height),
+                        float(near_plane), float(far_plane), float(scale_modifier))
+        info = HtgsFrameInfo()
+        rc = _native.lib().htgs_update_max_weights(_native.context(_device_index(device)), ctypes.byref(scene), ctypes.byref(view), max_weights.data_ptr(),
+                                                   float(weight_threshold), None, 0, torch.cuda.current_stream(device).cuda_stream, ctypes.byref(info))
+    _native.check(rc)
+    last_frame_info = info
 
 
 def update_3d_filter_cuda(positions, w2c, filter_3d, visibility_mask, width, height, focal_x, focal_y, center_x, center_y, near_plane,

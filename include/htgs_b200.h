@@ -205,6 +205,14 @@ int htgs_backward_static(HtgsContext* ctx, const HtgsScene* scene, const HtgsVie
                          const float* grad_image, const float* image, const HtgsGradients* grads, void* stream);
 
 /*
+ * Per-Gaussian maximum blending weight over the pixels of one view.  Replaces `_C.update_max_weights` =
+ * update_max_weights_wrapper (rasterization/include/rasterization_api.h:79-97).  `max_weights` [N] is raised in place
+ * (maximum with what it holds); scene->sh_0 / sh_rest are not read and may be NULL.  Workspace handling as htgs_render.
+ */
+int htgs_update_max_weights(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* max_weights, float weight_threshold,
+                            void* workspace, size_t workspace_bytes, void* stream, HtgsFrameInfo* info);
+
+/*
  * 3D smoothing-filter update for one view.  Replaces `_C.update_3d_filter_cuda` = update_3d_filter_wrapper
  * (filter3d/include/filter3d_api.h:7-20, filter3d/src/filter3d_api.cu:6-47).  positions [N,3], w2c [4,4] row-major,
  * filter_3d [N] (updated in place: min with distance2filter * view depth), visibility_mask [N] bytes (set to 1 for points

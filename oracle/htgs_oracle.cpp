@@ -540,6 +540,83 @@ int64_t run_render(const float* positions, const float* scales, const float* rot
     return int64_t(bin.sorted_prims.size());
 }
 
+// ----------------------------------------------------------------------------
+// update_max_weights: per-Gaussian maximum blending weight over the pixels of a view
+// R/include/hybrid_blend/kernels/update_max_weights.cuh:59-212 (core weights, then a second pass over the
+// tile's list that credits alpha * tail_weight to every fragment inside the cutoff),
+// first_k :60-, global_ordering :59-, oit :57- analogues.  Sequential over tiles (small cases only).
+// ----------------------------------------------------------------------------
+template <typename R>
+void max_weights_image(int mode, const BlendIn<R>& in, R weight_threshold, R* max_weights) {
+    const ModeConstants mc = mode_constants(mode);
+    const int K = in.K;
+    auto raise = [&](int64_t g, R w) { if (max_weights[g] < w) max_weights[g] = w; };
+    for (int tile = 0; tile < in.grid_w * in.grid_h; ++tile) {
+        const int tx = tile % in.grid_w, ty = tile / in.grid_w;
+        for (int ly = 0; ly < mc.tile_h; ++ly)
+            for (int lx = 0; lx < mc.tile_w; ++lx) {
+                const int pxi = tx * mc.tile_w + lx, pyi = ty * mc.tile_h + ly;
+                if (pxi >= in.width || pyi >= in.height) continue;
+                const R px = R(pxi), py = R(pyi);
+                std::vector<R> ka(K, R(0)), kd(K, R(FLT_MAX));
+                std::vector<uint32_t> ki(K, UINT32_MAX);
+                R alpha_sum = 0, t = 1;
+                bool done = false;
+                for (uint32_t it = in.ranges[2 * tile]; it < in.ranges[2 * tile + 1] && !done; ++it) {
+                    const int64_t g = in.prim_idx[it];
+                    Fragment<R> fr;
+                    fragment_planes(in.vpmt1 + 4 * g, in.vpmt2 + 4 * g, in.vpmt4 + 4 * g, px, py, fr);
+                    if (fr.rho2_num > R(mc.max_cutoff_sq) * fr.denom) continue;
+                    fr.denom_rcp = R(1) / fr.denom;
+                    R depth = 0;
+                    if (mode == 1) { depth = fragment_depth(in.mt3 + 4 * g, fr); if (depth >= kd[K - 1]) continue; }
+                    R alpha = std::min(in.rgba[4 * g + 3] * std::exp(R(-0.5) * fr.rho2_num * fr.denom_rcp), R(1));
+                    if (alpha < R(mc.min_alpha)) continue;
+                    if (mode == 2) {
+                        const R w = t * alpha;
+                        t *= R(1) - alpha;
+                        if (t < R(kTransmittanceThreshold)) done = true;
+                        if (!(w < weight_threshold)) raise(g, w);
+                        continue;
+                    }
+                    if (mode == 0) depth = fragment_depth(in.mt3 + 4 * g, fr);
+                    if (mode == 1 || (mode == 0 && depth < kd[K - 1] && alpha >= R(mc.min_alpha_core))) {
+                        uint32_t idx = uint32_t(g);
+                        for (int k = 0; k < K; ++k)
+                            if (depth < kd[k]) { std::swap(depth, kd[k]); std::swap(alpha, ka[k]); std::swap(idx, ki[k]); }
+                    }
+                    if (mode != 1) { alpha_sum += alpha; t *= R(1) - alpha; }
+                }
+                if (mode == 2) continue;
+                R second = 0;
+                if (mode == 0 || mode == 1) {
+                    R tc = 1;
+                    for (int k = 0; k < K; ++k) {
+                        const R w = tc * ka[k];
+                        tc *= R(1) - ka[k];
+                        if (tc < R(kTransmittanceThreshold)) tc = 0;
+                        if (w < weight_threshold || ki[k] == UINT32_MAX) continue;
+                        raise(ki[k], w);
+                    }
+                    if (mode == 0 && alpha_sum >= weight_threshold) second = tc * (R(1) - t) * (R(1) / alpha_sum);
+                } else if (alpha_sum >= weight_threshold) {
+                    second = (R(1) - t) * (R(1) / alpha_sum);
+                }
+                if (mode == 1 || !(second >= weight_threshold)) continue;
+                for (uint32_t it = in.ranges[2 * tile]; it < in.ranges[2 * tile + 1]; ++it) {
+                    const int64_t g = in.prim_idx[it];
+                    Fragment<R> fr;
+                    fragment_planes(in.vpmt1 + 4 * g, in.vpmt2 + 4 * g, in.vpmt4 + 4 * g, px, py, fr);
+                    if (fr.rho2_num > R(mc.max_cutoff_sq) * fr.denom) continue;
+                    const R alpha = std::min(in.rgba[4 * g + 3] * std::exp(R(-0.5) * fr.rho2_num * (R(1) / fr.denom)), R(1));
+                    const R w = alpha * second;
+                    if (w < weight_threshold) continue;
+                    raise(g, w);
+                }
+            }
+    }
+}
+
 }  // namespace
 
 // ----------------------------------------------------------------------------
@@ -599,6 +676,21 @@ void htgs_oracle_blend_f64(int mode, const uint32_t* ranges, const uint32_t* pri
     BlendIn<double> in{ranges, prim_idx, vpmt1, vpmt2, vpmt4, mt3, rgba, width, height, (width + mc.tile_w - 1) / mc.tile_w,
                        (height + mc.tile_h - 1) / mc.tile_h, K, use_median_depth != 0};
     blend_image<double>(mode, in, image, depth, alpha, to_chw != 0, n_threads);
+}
+
+void htgs_oracle_max_weights_f32(int mode, const uint32_t* ranges, const uint32_t* prim_idx, const float* vpmt1, const float* vpmt2, const float* vpmt4,
+                                 const float* mt3, const float* rgba, int width, int height, int K, float weight_threshold, float* max_weights) {
+    const ModeConstants mc = mode_constants(mode);
+    BlendIn<float> in{ranges, prim_idx, vpmt1, vpmt2, vpmt4, mt3, rgba, width, height, (width + mc.tile_w - 1) / mc.tile_w,
+                      (height + mc.tile_h - 1) / mc.tile_h, K, false};
+    max_weights_image<float>(mode, in, weight_threshold, max_weights);
+}
+void htgs_oracle_max_weights_f64(int mode, const uint32_t* ranges, const uint32_t* prim_idx, const double* vpmt1, const double* vpmt2, const double* vpmt4,
+                                 const double* mt3, const double* rgba, int width, int height, int K, double weight_threshold, double* max_weights) {
+    const ModeConstants mc = mode_constants(mode);
+    BlendIn<double> in{ranges, prim_idx, vpmt1, vpmt2, vpmt4, mt3, rgba, width, height, (width + mc.tile_w - 1) / mc.tile_w,
+                       (height + mc.tile_h - 1) / mc.tile_h, K, false};
+    max_weights_image<double>(mode, in, weight_threshold, max_weights);
 }
 
 // whole forward (preprocess -> bin -> blend); returns the instance count

@@ -119,6 +119,20 @@ def blend(mode: int, ranges, prim_idx, pre: dict, view, K: int, use_median_depth
     return image, depth, alpha
 
 
+def max_weights(mode: int, ranges, prim_idx, pre: dict, view, K: int, weight_threshold: float, start=None):
+    """update_max_weights from preprocess outputs and a sorted instance list (sequential; small cases only)."""
+    dtype = pre["vpmt1"].dtype
+    n = pre["vpmt1"].shape[0]
+    out = np.zeros(n, dtype) if start is None else np.ascontiguousarray(start, dtype).reshape(-1).copy()
+    ranges = np.ascontiguousarray(ranges, np.uint32)
+    prim_idx = np.ascontiguousarray(prim_idx, np.uint32)
+    thr = ctypes.c_double(weight_threshold) if dtype == np.float64 else ctypes.c_float(weight_threshold)
+    fn = lib().htgs_oracle_max_weights_f64 if dtype == np.float64 else lib().htgs_oracle_max_weights_f32
+    fn(int(mode), _p(ranges), _p(prim_idx), _p(pre["vpmt1"]), _p(pre["vpmt2"]), _p(pre["vpmt4"]), _p(pre["mt3"]), _p(pre["rgba"]),
+       int(view.width), int(view.height), int(K), thr, _p(out))
+    return out
+
+
 def render(scene, view, mode: Optional[int] = None, K: Optional[int] = None, scale_modifier: float = 1.0, to_chw: bool = True,
            use_median_depth: bool = False, dtype=np.float64, n_threads: int = 0):
     """Whole forward (the `rasterize` path).  Returns image, depth, alpha, n_instances."""

@@ -10,8 +10,8 @@ inputs is stored with every case so that a drifting generator is detected.
 
 Per case and blend mode the file holds: the `rasterize` image and depth, the tile boxes and
 tile counts of the preprocess, the sorted instance list and tile ranges (parsed from the
-scratch blobs `_C.forward` returns), the training-forward image and the six gradients of
-`diff_rasterize` for an L1 loss against a seeded target.
+scratch blobs `_C.forward` returns), the training-forward image, the six gradients of
+`diff_rasterize` for an L1 loss against a seeded target, and the `update_max_weights` result.
 """
 from __future__ import annotations
 
@@ -32,6 +32,9 @@ CASES = {
     "small_sh3": dict(kwargs=dict(n=1024, size=64, seed=12, sh_degree=3), modes=[(0, 8), (3, 8)]),
     "config0": dict(kwargs=dict(n=16384, size=256, seed=0, sh_degree=0), modes=[(0, 16)]),
 }
+
+
+MAX_WEIGHT_THRESHOLD = 0.02
 
 
 def inputs_digest(scene) -> str:
@@ -87,6 +90,10 @@ def main():
             out[f"{tag}_train_image"] = image.detach().cpu().numpy()
             for gname, leaf in zip(("positions", "scales", "rotations", "opacities", "sh_0", "sh_rest"), leaves):
                 out[f"{tag}_grad_{gname}"] = leaf.grad.cpu().numpy()
+            # importance weights (update_max_weights), threshold 0.02
+            max_weights = torch.zeros((scene.n, 1), device="cuda")
+            ref.update_max_weights(max_weights, *tensors[:4], st, MAX_WEIGHT_THRESHOLD)
+            out[f"{tag}_max_weights"] = max_weights.cpu().numpy()
         path = os.path.join(HERE, f"{name}.npz")
         np.savez_compressed(path, **out)
         print(name, "->", path, os.path.getsize(path) // 1024, "KiB")

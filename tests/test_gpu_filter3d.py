@@ -13,7 +13,7 @@ def _inputs(n=200_000, seed=5):
     positions = (rng.standard_normal((n, 3)) * 3.0).astype(np.float32)
     w2c = scenes.look_at((3.0, 1.0, 2.0)).astype(np.float32)
     filter_3d = np.full((n, 1), 1e5, np.float32)
-    filter_3d[::3] = 0.001      # already smaller than anything a view can give: must stay untouched
+    filter_3d[::3] = 0.0        # already smaller than anything a view can give: must stay untouched
     return positions, w2c, filter_3d, np.zeros(n, bool)
 
 
