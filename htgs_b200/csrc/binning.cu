@@ -240,7 +240,7 @@ __device__ __forceinline__ void block_exclusive_scan_512(uint32_t* vals, uint32_
 
 // Pass step 3: stable scatter.  Warp w of a sort block owns the 512 consecutive keys
 // [w*512, (w+1)*512) of the block's tile and visits them in 16 rounds of 32, so (warp, round, lane)
-// order is input order.  Ranks inside a round come from __match_any_sync; per-warp digit counters
+// order is input order.  Ranks inside a round come from per-bit warp ballots; per-warp digit counters
 // in shared memory chain the rounds; a scan over warps and digits turns them into positions in the
 // locally sorted tile, which is staged in shared memory and written out as runs.
 template <typename KeyT>
@@ -288,9 +288,16 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(
             const bool valid = idx < n;
             const uint32_t valid_mask = __ballot_sync(0xffffffffu, valid);
             rank[r] = 0;
+            // lanes holding the same digit: one ballot per digit bit (fixed cost; a hardware match over 32 mostly
+            // distinct tile digits is slower)
+            const uint32_t d = valid ? digit_of(key[r], shift, mask) : 0u;
+            uint32_t peers = valid_mask;
+            for (int b = 0; b < bits; ++b) {
+                const bool bit = (d >> b) & 1u;
+                const uint32_t bal = __ballot_sync(0xffffffffu, bit);
+                peers &= bit ? bal : ~bal;
+            }
             if (valid) {
-                const uint32_t d = digit_of(key[r], shift, mask);
-                const uint32_t peers = __match_any_sync(valid_mask, d);
                 const int leader = __ffs(peers) - 1;
                 uint32_t old = 0;
                 if (int(lane) == leader) { old = my_count[d]; my_count[d] = old + __popc(peers); }
