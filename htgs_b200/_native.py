@@ -126,6 +126,8 @@ def lib():
                 l.htgs_backward_static.argtypes = l.htgs_backward.argtypes
                 l.htgs_update_max_weights.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_float,
                                                       ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.POINTER(HtgsFrameInfo)]
+                l.htgs_render_fast.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_int,
+                                               ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.POINTER(HtgsFrameInfo)]
                 l.htgs_update_3d_filter.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                                     ctypes.c_int32] + [ctypes.c_float] * 7 + [ctypes.c_void_p]
                 l.htgs_set_profiling.argtypes = [ctypes.c_void_p, ctypes.c_int]

@@ -70,6 +70,7 @@ FrameLayout carve_frame(void* blob, int n_primitives, int n_tiles, const SortPla
     L.prim.clamp = training ? c.take<uint8_t>(n) : nullptr;
     L.prim.block_sums = c.take<uint32_t>(prim_blocks + 1);
     L.prim.block_offsets = c.take<uint32_t>(prim_blocks + 1);
+    L.prim.visible_list = c.take<uint32_t>(n);
     L.tile_ranges = c.take<uint2>(size_t(n_tiles));
     const uint64_t cap = instance_capacity > 0xfffffff0ull ? 0xfffffff0ull : instance_capacity;
     L.inst.capacity = uint32_t(cap);
@@ -175,7 +176,7 @@ size_t htgs_render_workspace_bytes(const HtgsScene* scene, const HtgsView* view,
 
 static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const SortPlan& plan,
                      const FrameLayout& L, BlendOutputs out, cudaStream_t stream, uint32_t* launches, float* max_weights = nullptr,
-                     float weight_threshold = 0.0f) {
+                     float weight_threshold = 0.0f, bool fast = false) {
     cudaError_t err;
     const bool prof = ctx->profiling;
     if (prof && !ctx->events_created) {
@@ -186,16 +187,18 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
     out.collect_stats = ctx->collect_stats;
     if ((err = cudaMemsetAsync(L.status, 0, sizeof(FrameStatus), stream)) != cudaSuccess) return fail_cuda(err, "status reset");
     if (prof) cudaEventRecord(ev[0], stream);
-    if ((err = launch_preprocess(view.mode, false, scene, view, geo, L.prim, L.status, stream)) != cudaSuccess) return fail_cuda(err, "preprocess");
+    if ((err = launch_preprocess(view.mode, false, scene, view, geo, L.prim, L.status, stream, fast)) != cudaSuccess) return fail_cuda(err, "preprocess");
     if (prof) cudaEventRecord(ev[1], stream);
     if ((err = launch_scan_only(scene, L.prim, L.inst.capacity, L.status, stream)) != cudaSuccess) return fail_cuda(err, "scan");
     if (prof) cudaEventRecord(ev[2], stream);
-    *launches += (scene.n_primitives > 0 ? 1 : 0) + 1;
+    *launches += (scene.n_primitives > 0 ? 2 : 0) + 1;
     if ((err = launch_emit_sort_ranges(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream,
                                        prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "binning");
     const uint32_t* prims_sorted = L.inst.prims[plan.final_buffer];
     if (max_weights) {
         if ((err = launch_max_weights(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, max_weights, weight_threshold, stream)) != cudaSuccess) return fail_cuda(err, "max weights");
+    } else if (fast) {
+        if ((err = launch_blend_fast(view.K, geo, L.prim, prims_sorted, L.tile_ranges, out.image, out.to_chw, L.status, stream)) != cudaSuccess) return fail_cuda(err, "fast blend");
     } else if ((err = launch_blend(view.mode, view.K, false, geo, L.prim, prims_sorted, L.tile_ranges, out, TrainPixelBuffers{}, L.status, stream)) != cudaSuccess) return fail_cuda(err, "blend");
     *launches += 1;
     if (prof) cudaEventRecord(ev[6], stream);
@@ -210,7 +213,7 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
 
 static int render_core(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
                        int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info,
-                       float* max_weights, float weight_threshold);
+                       float* max_weights, float weight_threshold, bool fast = false);
 
 int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
                 int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info) {
@@ -224,9 +227,15 @@ int htgs_update_max_weights(HtgsContext* ctx, const HtgsScene* scene, const Htgs
     return render_core(ctx, scene, view, nullptr, nullptr, nullptr, 1, 0, workspace, workspace_bytes, stream_ptr, info, max_weights, weight_threshold);
 }
 
+int htgs_render_fast(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, int to_chw, void* workspace,
+                     size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info) {
+    if (!image) return fail(HTGS_ERR_INVALID_ARGUMENT, "image must not be null");
+    return render_core(ctx, scene, view, image, nullptr, nullptr, to_chw, 0, workspace, workspace_bytes, stream_ptr, info, nullptr, 0.0f, true);
+}
+
 static int render_core(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
                        int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info,
-                       float* max_weights, float weight_threshold) {
+                       float* max_weights, float weight_threshold, bool fast) {
     if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
     int rc = validate(scene, view, max_weights == nullptr);
     if (rc != HTGS_OK) return rc;
@@ -237,6 +246,7 @@ static int render_core(HtgsContext* ctx, const HtgsScene* scene, const HtgsView*
     if (current != ctx->device && (err = cudaSetDevice(ctx->device)) != cudaSuccess) return fail_cuda(err, "cudaSetDevice");
 
     const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
+    fast = fast && !max_weights && blend_fast_supports(view->mode, view->K);   // other modes / K: the exact kernels serve the fast entry point
     const SortPlan plan = make_sort_plan(view->mode, geo.n_tiles);
     const BlendOutputs out{image, depth, alpha, to_chw != 0, use_median_depth != 0, false};
     const bool internal = workspace == nullptr;
@@ -274,7 +284,7 @@ static int render_core(HtgsContext* ctx, const HtgsScene* scene, const HtgsView*
         } else {
             L = carve_frame(workspace, scene->n_primitives, geo.n_tiles, plan, capacity, false);
         }
-        rc = run_frame(ctx, *scene, *view, geo, plan, L, out, stream, &launches, max_weights, weight_threshold);
+        rc = run_frame(ctx, *scene, *view, geo, plan, L, out, stream, &launches, max_weights, weight_threshold, fast);
         if (rc != HTGS_OK) return rc;
         const FrameStatus st = *ctx->host_status;
         ctx->last_layout = L; ctx->last_plan = plan; ctx->last_geo = geo; ctx->last_n_instances = st.overflow ? 0 : st.n_instances; ctx->has_last = true;
@@ -415,6 +425,7 @@ PrimLayout carve_primitive_blob(void* blob, int n_primitives) {
     L.prim.clamp = c.take<uint8_t>(n);
     L.prim.block_sums = c.take<uint32_t>(prim_blocks + 1);
     L.prim.block_offsets = c.take<uint32_t>(prim_blocks + 1);
+    L.prim.visible_list = c.take<uint32_t>(n);
     L.bytes = align_up(c.offset);
     return L;
 }
@@ -536,7 +547,7 @@ int htgs_forward_finish(HtgsContext* ctx, const HtgsScene* scene, const HtgsView
     if (info) {
         std::memset(info, 0, sizeof(*info));
         info->n_instances = st.n_instances; info->n_visible = st.n_visible; info->key_bytes = uint32_t(plan.key_bytes); info->end_bit = uint32_t(plan.end_bit);
-        info->device_error = st.error; info->kernel_launches = launches + 3;
+        info->device_error = st.error; info->kernel_launches = launches + 4;
     }
     if (st.error) return fail(HTGS_ERR_DEVICE_FLAG, "a kernel reported an internal error (bounded wait gave up)");
     return HTGS_OK;

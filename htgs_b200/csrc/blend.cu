@@ -575,7 +575,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
         image[base_idx + 1] = __saturatef(rgb_pixel.y);
         image[base_idx + 2] = __saturatef(rgb_pixel.z);
     }
-    depth_out[pixel_idx] = depth_pixel;
+    if (depth_out) depth_out[pixel_idx] = depth_pixel;
     if (alpha_out) alpha_out[pixel_idx] = alpha_pixel;
     }
 }

@@ -77,9 +77,31 @@ struct __align__(16) CullRecord {
     float cx, cy;
     float a, b2;
     float c;
-    float pad0, pad1, pad2;
+    float cx_lo, cy_lo;   // projected centre of the Gaussian minus (cx, cy); written and read by the relaxed-precision path only
+    float pad;
 };
 static_assert(sizeof(CullRecord) == 32, "CullRecord must be 32 bytes");
+
+// Relaxed-precision evaluation record (fast_rasterize path, HYBRID_BLEND), same size and place as EvalRecord.
+// With (dx, dy) = pixel - (cx, cy), where (cx, cy) is the projected centre of the Gaussian, the two planes through
+// the pixel ray (hybrid_blend/kernels/fast_inference.cuh:150-156) give m = w4 * (dy * a - dx * b) and
+// d = d0 + dx * dX + dy * dY, so rho^2 = (m.m)/(d.d) and depth = MT3.(d x m)/(d.d) + MT3.w are ratios of
+// quadratics in (dx, dy) whose coefficients are fixed per Gaussian (float64 in the preprocess, divided by d0.d0):
+//   e     = q1xx dx^2 + q1xy dx dy + q1yy dy^2           = -0.5 * log2(e) * (m.m) / (d0.d0)
+//   den   = 1 + q2x dx + q2y dy + q2xx dx^2 + q2xy dx dy + q2yy dy^2  = (d.d) / (d0.d0)
+//   num_z = q3x dx + q3y dy + q3xx dx^2 + q3xy dx dy + q3yy dy^2       = MT3.(d x m) / (d0.d0)
+//   alpha = min(exp2(e / den + log2_opacity), 1),   depth = num_z / den + depth_centre
+// The centre travels with the outline record (CullRecord: outline centre cx, cy plus the difference cx_lo, cy_lo to the
+// projected centre): a single float32 centre costs 6e-5 px at x ~ 1000, the dominant error of alpha for Gaussians of
+// sub-pixel extent.  The staging thread turns it into a tile-relative offset, dx = x_in_tile + dx0.
+struct __align__(16) FastRecord {
+    float q1xx, q1xy, q1yy, q2x;
+    float q2y, q2xx, q2xy, q2yy;
+    float q3x, q3y, q3xx, q3xy;
+    float q3yy, depth_centre, log2_opacity, r;
+    float g, b, pad0, pad1;
+};
+static_assert(sizeof(FastRecord) == sizeof(EvalRecord), "FastRecord shares the storage of EvalRecord");
 
 // Device-resident frame status, copied to the host at the end of a call.
 struct FrameStatus {
@@ -90,12 +112,6 @@ struct FrameStatus {
     unsigned long long candidate_pairs;     // statistics mode of the blend kernels
     unsigned long long accepted_fragments;  // statistics mode of the blend kernels
     unsigned int reserved[8];
-};
-
-struct CameraParams {             // read from device memory at kernel start (re-entrant, no __constant__ upload)
-    const float* M;               // [4,4] world -> view, row-major (only row 2 is used)
-    const float* VPM;             // [4,4] world -> screen
-    const float* cam_position;    // [3]
 };
 
 // ---------------------------------------------------------------------------

@@ -14,6 +14,7 @@ struct PrimBuffers {
     uint8_t* clamp;           // [N] bit c set: colour channel c was clamped at 0 (training only, else null)
     uint32_t* block_sums;     // [ceil(N/256)] instances emitted by each block of 256 Gaussians
     uint32_t* block_offsets;  // [ceil(N/256)] exclusive prefix of block_sums
+    uint32_t* visible_list;   // [N] indices of the Gaussians that survived culling (first n_visible entries, unordered)
 };
 
 struct InstBuffers {
@@ -46,8 +47,9 @@ struct FrameGeometry {
 FrameGeometry make_geometry(int mode, int width, int height);
 
 // preprocess.cu
+// `fast_records`: write FastRecord instead of EvalRecord (HYBRID_BLEND inference only; consumed by launch_blend_fast).
 cudaError_t launch_preprocess(int mode, bool train, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo,
-                              const PrimBuffers& prim, FrameStatus* status, cudaStream_t stream);
+                              const PrimBuffers& prim, FrameStatus* status, cudaStream_t stream, bool fast_records = false);
 
 // binning.cu: scan of block sums, instance emission, stable radix sort, tile ranges.
 // Everything after the scan reads the instance count from `status` on the device.
@@ -78,6 +80,11 @@ struct TrainPixelBuffers {
 int effective_k(int mode, int K);
 cudaError_t launch_blend(int mode, int K, bool train, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
                          const uint2* tile_ranges, const BlendOutputs& out, const TrainPixelBuffers& tout, FrameStatus* status, cudaStream_t stream);
+
+// blend_fast.cu: relaxed-precision HYBRID_BLEND inference (RGB only).  `supports` tells whether (mode, K) has a fast kernel.
+bool blend_fast_supports(int mode, int K);
+cudaError_t launch_blend_fast(int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                              float* image, bool to_chw, FrameStatus* status, cudaStream_t stream);
 
 // weights.cu
 cudaError_t launch_max_weights(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,

@@ -4,6 +4,9 @@
 // all Gaussians) and a conservative screen-space ellipse used by the blend
 // kernels to skip (pixel, Gaussian) pairs the exact test would reject.
 //
+// Two kernels: a cull pass over all Gaussians and a finish pass over the list of visible ones (typically one in
+// six), so that the expensive half (SH evaluation, float64 outline) runs in full warps.
+//
 // Replaces the sixteen preprocess_cu variants of the reference
 // (rasterization/include/*/kernels/{forward,inference}.cuh:10-76) and the device helpers
 // transform_and_cull / convert_sh_to_rgb (rasterization/include/kernel_utils.cuh:63-188).
@@ -128,16 +131,63 @@ __device__ __forceinline__ CullRecord make_cull_record(const float4& t1, const f
     return rec;
 }
 
+// Coefficients of the relaxed-precision record (see FastRecord): float64 from the float32 rows the exact path uses.
+// `centre` receives the projected centre (pixels), which the quadratics are expanded around.
+__device__ __forceinline__ void make_fast_record(const float4& t1, const float4& t2, const float4& t4, const float4& mt3, const float3& rgb,
+                                                 float opacity, float4* dst, double (&centre)[2]) {
+    struct D3 { double x, y, z; };
+    auto cross3 = [](const D3& a, const D3& b) { return D3{a.y * b.z - a.z * b.y, a.z * b.x - a.x * b.z, a.x * b.y - a.y * b.x}; };
+    auto dot3 = [](const D3& a, const D3& b) { return a.x * b.x + a.y * b.y + a.z * b.z; };
+    const double w4 = double(t4.w);
+    const double cx = double(t1.w) / w4, cy = double(t2.w) / w4;
+    const D3 n4{double(t4.x), double(t4.y), double(t4.z)};
+    const D3 a{double(t1.x) - n4.x * cx, double(t1.y) - n4.y * cx, double(t1.z) - n4.z * cx};
+    const D3 b{double(t2.x) - n4.x * cy, double(t2.y) - n4.y * cy, double(t2.z) - n4.z * cy};
+    const D3 d0 = cross3(a, b), dX = cross3(b, n4), dY = cross3(n4, a);
+    const double inv = 1.0 / dot3(d0, d0);
+    const double e_scale = -0.5 * 1.4426950408889634 * w4 * w4 * inv;
+    const D3 m3{double(mt3.x), double(mt3.y), double(mt3.z)};
+    const double z_scale = w4 * inv;
+    const D3 dXa = cross3(dX, a), dYb = cross3(dY, b);
+    float v[20] = {
+        float(e_scale * dot3(b, b)), float(-2.0 * e_scale * dot3(a, b)), float(e_scale * dot3(a, a)), float(2.0 * inv * dot3(d0, dX)),
+        float(2.0 * inv * dot3(d0, dY)), float(inv * dot3(dX, dX)), float(2.0 * inv * dot3(dX, dY)), float(inv * dot3(dY, dY)),
+        float(-z_scale * dot3(m3, cross3(d0, b))), float(z_scale * dot3(m3, cross3(d0, a))), float(-z_scale * dot3(m3, cross3(dX, b))),
+        float(z_scale * dot3(m3, D3{dXa.x - dYb.x, dXa.y - dYb.y, dXa.z - dYb.z})),
+        float(z_scale * dot3(m3, cross3(dY, a))), mt3.w, log2f(opacity), rgb.x,
+        rgb.y, rgb.z, 0.0f, 0.0f};
+    bool finite = isfinite(cx) && isfinite(cy);
+    #pragma unroll
+    for (int i = 0; i < 20; ++i) finite = finite && isfinite(v[i]);
+    if (!finite) {   // degenerate Gaussian: contributes nothing
+        #pragma unroll
+        for (int i = 0; i < 20; ++i) v[i] = 0.0f;
+        v[14] = -__int_as_float(0x7f800000);
+        centre[0] = centre[1] = 0.0;
+    } else {
+        centre[0] = cx; centre[1] = cy;
+    }
+    #pragma unroll
+    for (int i = 0; i < 5; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+
+// Pass 1, one thread per Gaussian: culling, tile box, and the rows VPMT1, VPMT2, VPMT4, MT3 (written where the
+// evaluation record lives).  The visible Gaussians of a block are appended to `visible_list` (the order of the list
+// depends on the order in which blocks finish; nothing downstream depends on it).
 template <int MODE, bool TRAIN>
-__global__ void __launch_bounds__(kPreprocessBlock) preprocess_kernel(
+__global__ void __launch_bounds__(kPreprocessBlock) preprocess_cull_kernel(
     const float* __restrict__ positions, const float* __restrict__ scales, const float* __restrict__ rotations,
-    const float* __restrict__ opacities, const float* __restrict__ sh_0, const float* __restrict__ sh_rest,
-    const float* __restrict__ M, const float* __restrict__ VPM, const float* __restrict__ cam_position_ptr,
+    const float* __restrict__ opacities, const float* __restrict__ M, const float* __restrict__ VPM,
     PrimBuffers out, FrameStatus* status, uint32_t n_primitives, uint32_t grid_w, uint32_t grid_h,
-    int active_sh_bases, int total_sh_bases, float near_plane, float far_plane, float scale_modifier_arg)
+    float near_plane, float far_plane, float scale_modifier_arg)
 {
     using MT = ModeTraits<MODE>;
+    __shared__ uint32_t warp_sum[kPreprocessBlock / 32];
+    __shared__ uint32_t warp_vis[kPreprocessBlock / 32];
+    __shared__ uint32_t list_base;
+
     const uint32_t idx = blockIdx.x * kPreprocessBlock + threadIdx.x;
+    const uint32_t warp = threadIdx.x >> 5;
     uint32_t n_touched = 0;
 
     if (idx < n_primitives) {
@@ -187,22 +237,10 @@ __global__ void __launch_bounds__(kPreprocessBlock) preprocess_kernel(
                     n_touched = (x_max - x_min) * (y_max - y_min);
                     if (n_touched != 0) {
                         out.bounds[idx] = make_ushort4((unsigned short)x_min, (unsigned short)x_max, (unsigned short)y_min, (unsigned short)y_max);
-                        EvalRecord rec;
-                        rec.vpmt1 = T1; rec.vpmt2 = T2; rec.vpmt4 = T4;
-                        if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) rec.mt3 = make_float4(0.0f, 0.0f, 0.0f, z);
-                        else rec.mt3 = make_float4(dot3_pinned_alt(f3(M3), u), dot3_pinned(f3(M3), v), dot3_pinned(f3(M3), w), z);
-                        const float3 cam_position = make_float3(__ldg(cam_position_ptr), __ldg(cam_position_ptr + 1), __ldg(cam_position_ptr + 2));
-                        uint8_t clamp_bits = 0;
-                        const float3 rgb = sh_0 ? sh_to_rgb<TRAIN>(sh_0, sh_rest, position, cam_position, idx, active_sh_bases, total_sh_bases, &clamp_bits)
-                                                : make_float3(0.0f, 0.0f, 0.0f);   // colour-less callers (update_max_weights)
-                        rec.rgba = make_float4(rgb.x, rgb.y, rgb.z, opacity);
                         float4* dst = reinterpret_cast<float4*>(out.eval + idx);
-                        dst[0] = rec.vpmt1; dst[1] = rec.vpmt2; dst[2] = rec.vpmt4; dst[3] = rec.mt3; dst[4] = rec.rgba;
-                        if constexpr (TRAIN) out.clamp[idx] = clamp_bits;
-                        const CullRecord cr = make_cull_record<MODE>(T1, T2, T4, opacity);
-                        float4* cdst = reinterpret_cast<float4*>(out.cull + idx);
-                        cdst[0] = make_float4(cr.cx, cr.cy, cr.a, cr.b2);
-                        cdst[1] = make_float4(cr.c, 0.0f, 0.0f, 0.0f);
+                        dst[0] = T1; dst[1] = T2; dst[2] = T4;
+                        if constexpr (MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) dst[3] = make_float4(0.0f, 0.0f, 0.0f, z);
+                        else dst[3] = make_float4(dot3_pinned_alt(f3(M3), u), dot3_pinned(f3(M3), v), dot3_pinned(f3(M3), w), z);
                     }
                 }
             }
@@ -210,42 +248,108 @@ __global__ void __launch_bounds__(kPreprocessBlock) preprocess_kernel(
         out.n_touched[idx] = n_touched;
     }
 
-    // per-block totals: instances and visible Gaussians
-    __shared__ uint32_t warp_sum[kPreprocessBlock / 32];
-    __shared__ uint32_t warp_vis[kPreprocessBlock / 32];
+    // per-block totals (instances, visible Gaussians) and the block's slice of the list of visible Gaussians
+    const bool visible = n_touched != 0;
+    const uint32_t ballot = __ballot_sync(0xffffffffu, visible);
     uint32_t sum = n_touched;
     #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const uint32_t vis = __popc(__ballot_sync(0xffffffffu, n_touched != 0));
-    if ((threadIdx.x & 31) == 0) { warp_sum[threadIdx.x >> 5] = sum; warp_vis[threadIdx.x >> 5] = vis; }
+    if ((threadIdx.x & 31) == 0) { warp_sum[warp] = sum; warp_vis[warp] = __popc(ballot); }
     __syncthreads();
     if (threadIdx.x == 0) {
         uint32_t total = 0, total_vis = 0;
         #pragma unroll
         for (int i = 0; i < kPreprocessBlock / 32; ++i) { total += warp_sum[i]; total_vis += warp_vis[i]; }
         out.block_sums[blockIdx.x] = total;
-        if (total_vis) atomicAdd(&status->n_visible, total_vis);
+        list_base = total_vis ? atomicAdd(&status->n_visible, total_vis) : 0u;
+    }
+    __syncthreads();
+    if (visible) {
+        uint32_t slot = list_base + __popc(ballot & lanemask_lt());
+        #pragma unroll
+        for (int i = 0; i < kPreprocessBlock / 32; ++i)
+            if (i < int(warp)) slot += warp_vis[i];
+        out.visible_list[slot] = idx;
     }
 }
 
-template <int MODE, bool TRAIN>
+// Pass 2, one thread per VISIBLE Gaussian (grid-stride over the list): colour from the SH coefficients, the
+// remaining parts of the evaluation record, the conservative outline.  Runs with full warps whatever the
+// fraction of Gaussians that survived culling.
+constexpr int kFinishBlock = 128;
+template <int MODE, bool TRAIN, bool FAST>
+__global__ void __launch_bounds__(kFinishBlock) preprocess_finish_kernel(
+    const float* __restrict__ positions, const float* __restrict__ opacities, const float* __restrict__ sh_0, const float* __restrict__ sh_rest,
+    const float* __restrict__ cam_position_ptr, PrimBuffers out, const FrameStatus* __restrict__ status, int active_sh_bases, int total_sh_bases)
+{
+    const uint32_t n_visible = status->n_visible;
+    const float3 cam_position = make_float3(__ldg(cam_position_ptr), __ldg(cam_position_ptr + 1), __ldg(cam_position_ptr + 2));
+    for (uint32_t i = blockIdx.x * kFinishBlock + threadIdx.x; i < n_visible; i += gridDim.x * kFinishBlock) {
+        const uint32_t gi = out.visible_list[i];
+        float4* dst = reinterpret_cast<float4*>(out.eval + gi);
+        const float4 t1 = dst[0], t2 = dst[1], t4 = dst[2], m3 = dst[3];
+        const float3 position = make_float3(__ldg(positions + 3 * size_t(gi)), __ldg(positions + 3 * size_t(gi) + 1), __ldg(positions + 3 * size_t(gi) + 2));
+        const float opacity = __ldg(opacities + gi);
+        uint8_t clamp_bits = 0;
+        const float3 rgb = sh_0 ? sh_to_rgb<TRAIN>(sh_0, sh_rest, position, cam_position, gi, active_sh_bases, total_sh_bases, &clamp_bits)
+                                : make_float3(0.0f, 0.0f, 0.0f);   // colour-less callers (update_max_weights)
+        [[maybe_unused]] double centre[2] = {0.0, 0.0};
+        if constexpr (FAST) make_fast_record(t1, t2, t4, m3, rgb, opacity, dst, centre);
+        else dst[4] = make_float4(rgb.x, rgb.y, rgb.z, opacity);
+        if constexpr (TRAIN) out.clamp[gi] = clamp_bits;
+        CullRecord cr = make_cull_record<MODE>(t1, t2, t4, opacity);
+        if constexpr (FAST) {
+            // The fragment evaluation measures from the projected centre, the outline test from the centre of
+            // the outline: the record carries the (small) difference, so that outline centre + difference
+            // gives the projected centre to better than float32 resolution at the pixel's magnitude.
+            cr.cx_lo = float(centre[0] - double(cr.cx));
+            cr.cy_lo = float(centre[1] - double(cr.cy));
+        }
+        float4* cdst = reinterpret_cast<float4*>(out.cull + gi);
+        cdst[0] = make_float4(cr.cx, cr.cy, cr.a, cr.b2);
+        cdst[1] = make_float4(cr.c, cr.cx_lo, cr.cy_lo, 0.0f);
+    }
+}
+
+int sm_count_of_current_device() {
+    static int cached[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64) return 148;
+    if (!cached[device]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+        cached[device] = n;
+    }
+    return cached[device];
+}
+
+template <int MODE, bool TRAIN, bool FAST>
 cudaError_t launch_t(const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim, FrameStatus* status, cudaStream_t stream) {
     const uint32_t n = uint32_t(scene.n_primitives);
     const uint32_t blocks = (n + kPreprocessBlock - 1) / kPreprocessBlock;
     if (blocks == 0) return cudaSuccess;
-    preprocess_kernel<MODE, TRAIN><<<blocks, kPreprocessBlock, 0, stream>>>(
-        scene.positions, scene.scales, scene.rotations, scene.opacities, scene.sh_0, scene.sh_rest, view.M, view.VPM, view.cam_position,
-        prim, status, n, uint32_t(geo.grid_w), uint32_t(geo.grid_h), view.active_sh_bases, scene.total_sh_bases, view.near_plane,
-        view.far_plane, view.scale_modifier);
+    preprocess_cull_kernel<MODE, TRAIN><<<blocks, kPreprocessBlock, 0, stream>>>(
+        scene.positions, scene.scales, scene.rotations, scene.opacities, view.M, view.VPM, prim, status, n, uint32_t(geo.grid_w),
+        uint32_t(geo.grid_h), view.near_plane, view.far_plane, view.scale_modifier);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    const uint32_t finish_blocks = min((n + kFinishBlock - 1) / kFinishBlock, uint32_t(sm_count_of_current_device()) * 8u);
+    preprocess_finish_kernel<MODE, TRAIN, FAST><<<finish_blocks, kFinishBlock, 0, stream>>>(
+        scene.positions, scene.opacities, scene.sh_0, scene.sh_rest, view.cam_position, prim, status, view.active_sh_bases, scene.total_sh_bases);
     return cudaGetLastError();
 }
 
 }  // namespace
 
 cudaError_t launch_preprocess(int mode, bool train, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo,
-                              const PrimBuffers& prim, FrameStatus* status, cudaStream_t stream) {
+                              const PrimBuffers& prim, FrameStatus* status, cudaStream_t stream, bool fast_records) {
+    if (fast_records) {
+        if (mode != HTGS_MODE_HYBRID_BLEND || train) return cudaErrorInvalidValue;
+        return launch_t<HTGS_MODE_HYBRID_BLEND, false, true>(scene, view, geo, prim, status, stream);
+    }
     switch (mode) {
-#define HTGS_CASE(M) case M: return train ? launch_t<M, true>(scene, view, geo, prim, status, stream) : launch_t<M, false>(scene, view, geo, prim, status, stream);
+#define HTGS_CASE(M) case M: return train ? launch_t<M, true, false>(scene, view, geo, prim, status, stream) : launch_t<M, false, false>(scene, view, geo, prim, status, stream);
         HTGS_CASE(HTGS_MODE_HYBRID_BLEND)
         HTGS_CASE(HTGS_MODE_ALPHA_BLEND_FIRST_K)
         HTGS_CASE(HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING)

@@ -12,7 +12,7 @@ from typing import Any, NamedTuple
 import torch
 from torch.autograd.function import once_differentiable
 
-from . import _C
+from . import _C, _C_benchmarking
 
 
 class RasterizerMode(Enum):
@@ -81,9 +81,8 @@ def rasterize(positions, scales, rotations, opacities, sh_0, sh_rest, settings: 
 
 
 def fast_rasterize(positions, scales, rotations, opacities, sh_0, sh_rest, settings: RasterizerSettings, to_chw: bool) -> torch.Tensor:
-    """The reference's relaxed-precision benchmark path.  Here it runs the exact path and drops the depth."""
-    image, _ = _C.render(positions, scales, rotations, opacities, sh_0, sh_rest, *settings.as_tuple(), to_chw, False)
-    return image
+    """The reference's relaxed-precision benchmark path (torch_bindings/rasterization.py:166-186): RGB only."""
+    return _C_benchmarking.benchmark(positions, scales, rotations, opacities, sh_0, sh_rest, *settings.as_tuple(), to_chw)
 
 
 def update_max_weights(max_weights, positions, scales, rotations, opacities, settings: RasterizerSettings, weight_threshold: float) -> None:

@@ -205,6 +205,16 @@ int htgs_backward_static(HtgsContext* ctx, const HtgsScene* scene, const HtgsVie
                          const float* grad_image, const float* image, const HtgsGradients* grads, void* stream);
 
 /*
+ * Relaxed-precision forward, RGB only.  Replaces `_C_benchmarking.benchmark` = fast_inference_wrapper
+ * (rasterization/include/fast_inference_api.h:7-25, rasterization/src/fast_inference_api.cu:21-162), the reference's
+ * fast-math build.  `image` is [3,H,W] (to_chw) or [H,W,3], clamped to [0,1].  HYBRID_BLEND with K rounded to 4, 8, 16
+ * or 32 runs a dedicated kernel whose result agrees with the reference's fast path to about 1e-3 per channel (not bit
+ * for bit); every other mode or K runs the exact kernels of htgs_render.  Workspace handling as htgs_render.
+ */
+int htgs_render_fast(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, int to_chw, void* workspace,
+                     size_t workspace_bytes, void* stream, HtgsFrameInfo* info);
+
+/*
  * Per-Gaussian maximum blending weight over the pixels of one view.  Replaces `_C.update_max_weights` =
  * update_max_weights_wrapper (rasterization/include/rasterization_api.h:79-97).  `max_weights` [N] is raised in place
  * (maximum with what it holds); scene->sh_0 / sh_rest are not read and may be NULL.  Workspace handling as htgs_render.

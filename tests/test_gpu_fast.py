@@ -1,0 +1,117 @@
+"""GPU: the relaxed-precision entry point (`fast_rasterize` -> `_C_benchmarking.benchmark` -> `htgs_render_fast`).
+
+The reference's fast path is its own approximation of `rasterize` (fast-math build, half-precision K-buffer: on the
+benchmark scene it differs from the exact image by 5e-5 on average, by up to 1e-2 at a handful of pixels where a
+fragment flips between core and tail).  The bar here follows that: against the reference's `fast_rasterize` (golden
+vectors and, when built, the live extension) the mean absolute difference must stay below 1e-5, at most 0.02 % of the
+values may differ by more than 1e-3, and none by more than 0.1; against the exact `rasterize` of this library the
+mean must stay below 2e-4.  Modes and K without a dedicated kernel must reproduce the exact image bit for bit."""
+import os
+
+import numpy as np
+import pytest
+
+import harness
+from htgs_b200 import scenes
+from golden.make_golden import CASES
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+MEAN_TOL = 1e-5          # vs the reference's fast path
+OUTLIER_TOL = 1e-3
+OUTLIER_FRACTION = 2e-4
+MAX_TOL = 0.1
+
+
+def check_close(got, want, mean_tol=MEAN_TOL):
+    d = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert d.mean() < mean_tol, f"mean abs difference {d.mean():.3e}"
+    assert (d > OUTLIER_TOL).mean() <= OUTLIER_FRACTION, f"{(d > OUTLIER_TOL).sum()} of {d.size} values differ by more than {OUTLIER_TOL}"
+    assert d.max() < MAX_TOL, f"max abs difference {d.max():.3e}"
+
+
+def fast(mod, scene, view, mode, K, to_chw=True):
+    import torch
+    st = harness.settings_for(mod, scene, view, mode, K)
+    img = mod.fast_rasterize(*harness.scene_tensors(scene), st, to_chw)
+    torch.cuda.synchronize()
+    return img
+
+
+def exact(mod, scene, view, mode, K, to_chw=True):
+    import torch
+    st = harness.settings_for(mod, scene, view, mode, K)
+    img, _ = mod.rasterize(*harness.scene_tensors(scene), st, to_chw, False)
+    torch.cuda.synchronize()
+    return img
+
+
+def hybrid_golden_cases():
+    for name, case in CASES.items():
+        for mode, K in case["modes"]:
+            if mode == scenes.HYBRID_BLEND:
+                yield name, K
+
+
+@pytest.mark.parametrize("name,K", list(hybrid_golden_cases()))
+def test_against_reference_golden(name, K):
+    gold = np.load(os.path.join(GOLDEN, f"{name}.npz"))
+    key = f"m0_k{K}_fast_image"
+    if key not in gold.files:
+        pytest.skip("golden file predates the fast_rasterize vectors")
+    scene = scenes.tiny_scene(**CASES[name]["kwargs"])
+    got = fast(harness.ours(), scene, scene.views[0], 0, K).cpu().numpy()
+    assert got.shape == gold[key].shape and got.min() >= 0.0 and got.max() <= 1.0
+    check_close(got, gold[key])
+
+
+@pytest.mark.parametrize("K", [4, 8, 16, 32])
+@pytest.mark.parametrize("to_chw", [True, False])
+def test_against_live_reference(K, to_chw):
+    ref = harness.reference()
+    if ref is None:
+        pytest.skip("reference extension not built")
+    scene = scenes.tiny_scene(n=20000, size=200, seed=70 + K, sh_degree=2)
+    view = scene.views[0]
+    got = fast(harness.ours(), scene, view, 0, K, to_chw).cpu().numpy()
+    want = fast(ref, scene, view, 0, K, to_chw).cpu().numpy()
+    assert got.shape == ((3, view.height, view.width) if to_chw else (view.height, view.width, 3))
+    check_close(got, want)
+
+
+@pytest.mark.parametrize("K", [4, 16, 32])
+def test_against_exact_path(K):
+    scene = scenes.tiny_scene(n=12000, size=160, seed=80 + K, sh_degree=1)
+    view = scene.views[0]
+    ours = harness.ours()
+    check_close(fast(ours, scene, view, 0, K).cpu().numpy(), exact(ours, scene, view, 0, K).cpu().numpy(), mean_tol=2e-4)
+
+
+@pytest.mark.parametrize("mode,K", [(0, 1), (0, 2), (1, 8), (2, 1), (3, 1)])
+def test_modes_without_fast_kernel_are_exact(mode, K):
+    scene = scenes.tiny_scene(n=5000, size=96, seed=90 + mode, sh_degree=0)
+    view = scene.views[0]
+    ours = harness.ours()
+    assert np.array_equal(fast(ours, scene, view, mode, K).cpu().numpy(), exact(ours, scene, view, mode, K).cpu().numpy())
+
+
+def test_benchmark_size_against_live_reference():
+    """Configuration 1 (3 M Gaussians, 1297x840) on two views."""
+    ref = harness.reference()
+    if ref is None:
+        pytest.skip("reference extension not built")
+    scene = scenes.outdoor_scene(n_views=200)
+    for vi in (0, 100):
+        got = fast(harness.ours(), scene, scene.views[vi], 0, 16).cpu().numpy()
+        want = fast(ref, scene, scene.views[vi], 0, 16).cpu().numpy()
+        check_close(got, want)
+
+
+def test_empty_and_offscreen():
+    import torch
+    ours = harness.ours()
+    scene = scenes.tiny_scene(n=64, size=64, seed=3, sh_degree=0)
+    scene.positions[:, 2] = -5.0   # everything behind the camera
+    img = fast(ours, scene, scene.views[0], 0, 16)
+    assert torch.count_nonzero(img).item() == 0
