@@ -14,8 +14,9 @@
 //  * K-buffer.  The K nearest core fragments of a pixel are kept UNSORTED in shared memory: one key per entry (the
 //    fragment depth with its low log2(K) mantissa bits replaced by the entry's position, so the largest key names
 //    the entry to evict) and a half-precision premultiplied RGBA payload (as the reference's fast path stores it).
-//    An insertion overwrites the entry of the largest key and recomputes the maximum with K/4 vector loads and
-//    three-input max instructions: about 15 ALU-pipe instructions instead of 5 per level of a sorted chain.
+//    An insertion overwrites the entry of the largest key, re-reads the one row of four keys that changed and
+//    updates the per-row maxima it keeps in registers: about 20 ALU-pipe instructions and 9 shared-memory wavefronts
+//    instead of 5 instructions per level of a sorted chain.
 //    Entries are sorted once per pixel when the tile is composited.  Fragments of exactly equal depth are ordered by
 //    position instead of by arrival.
 #include "kernels.h"
@@ -97,22 +98,24 @@ __device__ __forceinline__ float4 unpack_half4(uint2 p) {
 }
 
 // Replace the entry with the largest key by (depth, payload); returns the payload that fell out (zeros for an
-// entry that was still empty) and updates `kmax`.  Entry c keeps its key in component (c & 3) of uint4 row (c >> 2).
+// entry that was still empty).  Entry c keeps its key in component (c & 3) of uint4 row (c >> 2).  Registers hold
+// the maximum of every row (`row_max`), so that only the row that changed is read back: one vector load instead
+// of K/4 (shared-memory bandwidth is what bounds this kernel).
 template <int K>
-__device__ __forceinline__ uint2 core_replace(uint32_t* keys, uint2* pay, uint32_t tid, float depth, uint2 payload, uint32_t& kmax) {
+__device__ __forceinline__ uint2 core_replace(uint32_t* keys, uint2* pay, uint32_t tid, float depth, uint2 payload, uint32_t (&row_max)[K / 4],
+                                              uint32_t& kmax) {
     const uint32_t c = kmax & uint32_t(K - 1);
     uint2* slot = pay + c * kFastThreads + tid;
     const uint2 evicted = *slot;
     *slot = payload;
-    keys[((c >> 2) * kFastThreads + tid) * 4 + (c & 3u)] = KeyCodec<K>::encode(depth, c);
-    const uint4* rows = reinterpret_cast<const uint4*>(keys) + tid;
-    uint32_t v[K];
+    const uint32_t q = c >> 2;
+    uint4* row_ptr = reinterpret_cast<uint4*>(keys) + q * kFastThreads + tid;
+    reinterpret_cast<uint32_t*>(row_ptr)[c & 3u] = KeyCodec<K>::encode(depth, c);
+    const uint4 row = *row_ptr;
+    const uint32_t m = max(__vimax3_u32(row.x, row.y, row.z), row.w);
     #pragma unroll
-    for (int q = 0; q < K / 4; ++q) {
-        const uint4 row = rows[q * kFastThreads];
-        v[4 * q] = row.x; v[4 * q + 1] = row.y; v[4 * q + 2] = row.z; v[4 * q + 3] = row.w;
-    }
-    kmax = reduce_max<K>(v);
+    for (int i = 0; i < K / 4; ++i) row_max[i] = (q == uint32_t(i)) ? m : row_max[i];
+    kmax = reduce_max<K / 4>(row_max);
     return evicted;
 }
 
@@ -148,6 +151,9 @@ __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
         keys[((c >> 2) * kFastThreads + tid) * 4 + (c & 3)] = KeyCodec<K>::empty | uint32_t(c);
         pay[c * kFastThreads + tid] = make_uint2(0u, 0u);
     }
+    uint32_t row_max[K / 4];
+    #pragma unroll
+    for (int q = 0; q < K / 4; ++q) row_max[q] = KeyCodec<K>::empty | uint32_t(4 * q + 3);
     uint32_t kmax = 0xffffffffu;                             // position K-1
     float depth_max = __int_as_float(0x7f800000);            // depth a fragment has to beat to enter the core
     float4 tail = make_float4(0.0f, 0.0f, 0.0f, 0.0f);       // premultiplied rgb, alpha sum
@@ -244,7 +250,7 @@ __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
         };
         auto commit = [&](float depth, float4 frag) {
             if (HTGS_EXPERIMENT != 1 && depth < depth_max && frag.w >= FastTraits::min_alpha_core) {
-                frag = unpack_half4(core_replace<K>(keys, pay, tid, depth, pack_half4(frag.x, frag.y, frag.z, frag.w), kmax));
+                frag = unpack_half4(core_replace<K>(keys, pay, tid, depth, pack_half4(frag.x, frag.y, frag.z, frag.w), row_max, kmax));
                 depth_max = KeyCodec<K>::decode(kmax);
             }
             tail += frag;
