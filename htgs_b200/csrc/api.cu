@@ -126,6 +126,7 @@ struct HtgsContext {
     // measurement aids
     bool profiling = false;
     bool collect_stats = false;
+    bool fast_deterministic = false;        // htgs_render_fast: ordered (radix sort) instead of unordered (atomic) binning
     cudaEvent_t events[8] = {};
     bool events_created = false;
     float stage_ms[HTGS_N_STAGES] = {};
@@ -192,9 +193,12 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
     if ((err = launch_scan_only(scene, L.prim, L.inst.capacity, L.status, stream)) != cudaSuccess) return fail_cuda(err, "scan");
     if (prof) cudaEventRecord(ev[2], stream);
     *launches += (scene.n_primitives > 0 ? 2 : 0) + 1;
-    if ((err = launch_emit_sort_ranges(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream,
-                                       prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "binning");
     const uint32_t* prims_sorted = L.inst.prims[plan.final_buffer];
+    if (fast && !ctx->fast_deterministic) {
+        if ((err = launch_bin_unordered(scene, geo, L.prim, L.inst.prims[plan.final_buffer], L.inst.capacity, L.tile_ranges, L.status, ctx->sm_count,
+                                        stream, prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "unordered binning");
+    } else if ((err = launch_emit_sort_ranges(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream,
+                                              prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "binning");
     if (max_weights) {
         if ((err = launch_max_weights(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, max_weights, weight_threshold, stream)) != cudaSuccess) return fail_cuda(err, "max weights");
     } else if (fast) {
@@ -337,6 +341,12 @@ int htgs_set_profiling(HtgsContext* ctx, int enable) {
 int htgs_get_stage_ms(HtgsContext* ctx, float* out_ms) {
     if (!ctx || !out_ms) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     for (int i = 0; i < HTGS_N_STAGES; ++i) out_ms[i] = ctx->stage_ms[i];
+    return HTGS_OK;
+}
+
+int htgs_set_fast_deterministic(HtgsContext* ctx, int enable) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    ctx->fast_deterministic = enable != 0;
     return HTGS_OK;
 }
 

@@ -59,6 +59,13 @@ cudaError_t launch_emit_sort_ranges(int mode, const HtgsScene& scene, const Fram
                                     const InstBuffers& inst, uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream,
                                     cudaEvent_t* stage_events = nullptr, uint32_t* launches = nullptr);
 
+// binning_unordered.cu: per-tile lists without sort keys (counting sort with atomics; the order inside a list is not
+// defined).  Writes `tile_ranges` and `prims_sorted`; expects `status->n_instances / overflow` from launch_scan_only.
+// `stage_events` (optional): events recorded after the count pass, the tile scan and the placement pass.
+cudaError_t launch_bin_unordered(const HtgsScene& scene, const FrameGeometry& geo, const PrimBuffers& prim, uint32_t* prims_sorted, uint32_t capacity,
+                                 uint2* tile_ranges, FrameStatus* status, int sm_count, cudaStream_t stream, cudaEvent_t* stage_events = nullptr,
+                                 uint32_t* launches = nullptr);
+
 // blend.cu
 struct BlendOutputs {
     float* image;
