@@ -158,14 +158,26 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
     v0 = scene.views[0]
     gen = torch.Generator(device="cpu").manual_seed(1234)
     target = torch.rand((3, v0.height, v0.width), generator=gen).to(device)
-    leaves = [t.clone().requires_grad_(True) for t in tensors]
+    # The model's parameters are raw (log-scales, unnormalised quaternions, opacity logits; Model.py:45-49 of the reference)
+    # and activated inside autograd every step: element-wise PyTorch operations on the reference arm, as its model does,
+    # the fused activation kernel (`htgs_activate`) on this library's arm.
+    positions, scales, rotations, opacities, sh_0, sh_rest = tensors
+    raw = [positions.clone(), scales.log(), rotations * 1.5, torch.special.logit(opacities.clamp(1e-6, 1.0 - 1e-6)), sh_0.clone(), sh_rest.clone()]
+    leaves = [t.contiguous().requires_grad_(True) for t in raw]
     empty = torch.empty(0, device=device)
+    if is_reference:
+        def activate(raw_scales, raw_rotations, raw_opacities):
+            return torch.exp(raw_scales), torch.nn.functional.normalize(raw_rotations), torch.special.expit(raw_opacities)
+    else:
+        from htgs_b200 import glue
+        activate = glue.activate
 
     def step(s):
         vi = parallel.step_view_indices(s, 1, rank, world, n_views)[0]
         for l in leaves:
             l.grad = None
-        image = mod.diff_rasterize(*leaves, empty, settings(cams_dev[vi]), False)
+        act_scales, act_rotations, act_opacities = activate(leaves[1], leaves[2], leaves[3])
+        image = mod.diff_rasterize(leaves[0], act_scales, act_rotations, act_opacities, leaves[4], leaves[5], empty, settings(cams_dev[vi]), False)
         loss = (image - target).abs().mean()
         loss.backward()
         if dist is not None:

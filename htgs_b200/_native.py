@@ -130,6 +130,8 @@ def lib():
                                                ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.POINTER(HtgsFrameInfo)]
                 l.htgs_update_3d_filter.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                                     ctypes.c_int32] + [ctypes.c_float] * 7 + [ctypes.c_void_p]
+                l.htgs_activate.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int32, ctypes.c_void_p]
+                l.htgs_activate_backward.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int32, ctypes.c_void_p]
                 l.htgs_set_profiling.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_set_collect_stats.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_set_fast_deterministic.argtypes = [ctypes.c_void_p, ctypes.c_int]

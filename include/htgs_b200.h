@@ -238,6 +238,22 @@ int htgs_update_3d_filter(const float* positions, const float* w2c, float* filte
                           int32_t width, int32_t height, float focal_x, float focal_y, float center_x, float center_y, float near_plane,
                           float clipping_tolerance, float distance2filter, void* stream);
 
+/*
+ * Fused parameter activations of the Gaussian model, forward and backward (one pass over N).  Replaces the element-wise
+ * PyTorch operations the reference's model applies before every rasterizer call (Model.py:45-49 exp / normalize / expit,
+ * Model.py:82-100 the 3D-filter adjustment):
+ *   scales = exp(raw_scales), rotations = raw_rotations / max(|raw_rotations|, 1e-12), opacities = expit(raw_opacities);
+ *   with filter_3d [N] != NULL: scales = sqrt(scales^2 + f^2), opacities *= prod_i exp(raw_scales_i) / scales_i.
+ * raw_scales / scales [N,3], raw_rotations / rotations [N,4], raw_opacities / opacities [N]; outputs may not alias inputs.
+ * The backward takes the gradients with respect to the three outputs and returns those with respect to the raw inputs.
+ * Stream-ordered, no host synchronisation.
+ */
+int htgs_activate(const float* raw_scales, const float* raw_rotations, const float* raw_opacities, const float* filter_3d, float* scales,
+                  float* rotations, float* opacities, int32_t n_primitives, void* stream);
+int htgs_activate_backward(const float* raw_scales, const float* raw_rotations, const float* raw_opacities, const float* filter_3d,
+                           const float* grad_scales, const float* grad_rotations, const float* grad_opacities, float* grad_raw_scales,
+                           float* grad_raw_rotations, float* grad_raw_opacities, int32_t n_primitives, void* stream);
+
 /* Measurement aids (off by default; they do not change results).
  * Profiling: CUDA events are recorded on the frame's stream between the stages; after the call
  * htgs_get_stage_ms fills out_ms[0..HTGS_N_STAGES) with the device time of each stage in ms.
