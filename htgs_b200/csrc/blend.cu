@@ -94,22 +94,34 @@ __device__ __forceinline__ FragmentFront fragment_front(const float4& VPMT1, con
 // slot is still passed from level to level (one select per level on the critical path instead of a compare
 // and a select).  Results, including the reference's behaviour for equal depths, are bit-identical to the chain.
 // On return `depth` is the depth of the entry that fell out of the buffer and the result its slot.
+// Slot numbers travel as floats (0..K are exact): the two selects per level that pass the slots along the chain become
+// one add and two multiply-adds on the FMA pipes, which are mostly idle in this kernel, instead of two instructions on
+// the ALU pipe that bounds it.  The comparison is materialised as 1.0f / 0.0f by a single `set` instruction.
+using slot_t = float;
+__device__ __forceinline__ uint32_t slot_index(slot_t s) { return uint32_t(__float2int_rz(s)); }
+__device__ __forceinline__ float less_than_as_float(float a, float b) {
+    float r;
+    asm("set.lt.f32.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+
 template <int K>
-__device__ __forceinline__ uint32_t kbuffer_insert(float (&kd)[K], uint32_t (&ks)[K], float& depth, uint32_t slot) {
-    bool p[K];
+__device__ __forceinline__ slot_t kbuffer_insert(float (&kd)[K], slot_t (&ks)[K], float& depth, slot_t slot) {
+    float p[K];
     float nd[K];
     #pragma unroll
     for (int k = 0; k < K; ++k) {
         const float carried = k == 0 ? depth : fmaxf(depth, kd[k - 1]);
-        p[k] = carried < kd[k];
-        nd[k] = p[k] ? carried : kd[k];
+        p[k] = less_than_as_float(carried, kd[k]);
+        nd[k] = fminf(carried, kd[k]);   // = carried where carried < kd[k], else kd[k]
     }
     const float out_depth = fmaxf(depth, kd[K - 1]);
     #pragma unroll
     for (int k = 0; k < K; ++k) {
-        const uint32_t mine = ks[k];
-        ks[k] = p[k] ? slot : mine;
-        slot = p[k] ? mine : slot;
+        const slot_t mine = ks[k];
+        const float t = slot - mine;
+        ks[k] = fmaf(t, p[k], mine);      // p ? slot : mine
+        slot = fmaf(-t, p[k], slot);      // p ? mine : slot
         kd[k] = nd[k];
     }
     depth = out_depth;
@@ -148,15 +160,15 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
 
     // ---- per-pixel state -------------------------------------------------------------------
     [[maybe_unused]] float kd[SL::has_kbuffer ? K : 1];
-    [[maybe_unused]] uint32_t ks[SL::has_kbuffer ? K : 1];
+    [[maybe_unused]] slot_t ks[SL::has_kbuffer ? K : 1];
     [[maybe_unused]] float4* pool4 = reinterpret_cast<float4*>(smem + SL::pool_off);
     [[maybe_unused]] float2* pool2 = reinterpret_cast<float2*>(smem + SL::pool_off);
     [[maybe_unused]] uint32_t* pool_idx = reinterpret_cast<uint32_t*>(smem + SL::pool_idx_off);
-    [[maybe_unused]] uint32_t free_slot = K;
+    [[maybe_unused]] uint32_t free_slot = K;   // index of the pool slot no buffer entry refers to
     if constexpr (SL::has_kbuffer) {
         #pragma unroll
         for (int k = 0; k < K; ++k) {
-            kd[k] = FLT_MAX; ks[k] = k;
+            kd[k] = FLT_MAX; ks[k] = slot_t(k);
             if constexpr (kHybrid) pool4[k * TS::threads + tid] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             else pool2[k * TS::threads + tid] = make_float2(0.0f, __uint_as_float(0xffffffffu));
             if constexpr (SL::has_pool_idx) pool_idx[k * TS::threads + tid] = 0xffffffffu;
@@ -290,7 +302,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                     if (HTGS_EXPERIMENT != 1 && depth < kd[K - 1] && frag.w >= MT::min_alpha_core) {
                         pool4[free_slot * TS::threads + tid] = frag;
                         if constexpr (TRAIN) pool_idx[free_slot * TS::threads + tid] = s_prim[j];
-                        free_slot = kbuffer_insert<K>(kd, ks, depth, free_slot);   // the entry that fell out: a real fragment or an empty one
+                        free_slot = slot_index(kbuffer_insert<K>(kd, ks, depth, slot_t(free_slot)));   // the entry that fell out: a real fragment or an empty one
                         frag = pool4[free_slot * TS::threads + tid];
                     }
                     if constexpr (TRAIN) {
@@ -334,7 +346,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                         if (alpha < MT::min_alpha) continue;
                         if constexpr (STATS) ++stat_accepted;
                         pool2[free_slot * TS::threads + tid] = make_float2(alpha, __uint_as_float(s_prim[j]));
-                        free_slot = kbuffer_insert<K>(kd, ks, depth, free_slot);
+                        free_slot = slot_index(kbuffer_insert<K>(kd, ks, depth, slot_t(free_slot)));
                     } else if constexpr (kGlobal) {
                         const float4 rgba_in = rec[4];
                         const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
@@ -394,7 +406,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
             #pragma unroll
             for (int k = 0; k < K; ++k) {
                 if (transmittance_core >= kTransmittanceThreshold) {
-                    const float4 rgba = pool4[ks[k] * TS::threads + tid];
+                    const float4 rgba = pool4[slot_index(ks[k]) * TS::threads + tid];
                     const float blending_weight = transmittance_core * rgba.w;
                     rgb_pixel += blending_weight * f3(rgba);
                     transmittance_core *= 1.0f - rgba.w;
@@ -416,11 +428,11 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
             transmittance_core = 1.0f;
             #pragma unroll
             for (int k = 0; k < K; ++k) {
-                const uint32_t primitive_idx = pool_idx[ks[k] * TS::threads + tid];
+                const uint32_t primitive_idx = pool_idx[slot_index(ks[k]) * TS::threads + tid];
                 const bool skip = primitive_idx == 0xffffffffu || transmittance_core < kTransmittanceThreshold;
                 tout.idx_core[k * PP + slot_base] = skip ? 0xffffffffu : primitive_idx;
                 if (!skip) {
-                    const float4 rgba = pool4[ks[k] * TS::threads + tid];
+                    const float4 rgba = pool4[slot_index(ks[k]) * TS::threads + tid];
                     const float blending_weight = transmittance_core * rgba.w;
                     rgb_pixel_new += blending_weight * f3(rgba);
                     const float one_minus_alpha = 1.0f - rgba.w;
@@ -443,7 +455,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
             for (int k = 0; k < K; ++k) {
                 rgbs_core[k] = make_float3(0.0f, 0.0f, 0.0f);
                 if (!stop && t >= kTransmittanceThreshold) {
-                    const float2 cell = pool2[ks[k] * TS::threads + tid];
+                    const float2 cell = pool2[slot_index(ks[k]) * TS::threads + tid];
                     const uint32_t primitive_idx = __float_as_uint(cell.y);
                     if (primitive_idx == 0xffffffffu) stop = true;
                     else {
@@ -460,7 +472,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
             t = 1.0f;
             #pragma unroll
             for (int k = 0; k < K; ++k) {
-                const float2 cell = pool2[ks[k] * TS::threads + tid];
+                const float2 cell = pool2[slot_index(ks[k]) * TS::threads + tid];
                 const uint32_t primitive_idx = __float_as_uint(cell.y);
                 const bool skip = primitive_idx == 0xffffffffu || t < kTransmittanceThreshold;
                 tout.idx_core[k * PP + slot_base] = skip ? 0xffffffffu : primitive_idx;
@@ -507,7 +519,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
         #pragma unroll
         for (int k = 0; k < K; ++k) {
             if (transmittance_core >= kTransmittanceThreshold) {
-                const float4 rgba_premultiplied = pool4[ks[k] * TS::threads + tid];
+                const float4 rgba_premultiplied = pool4[slot_index(ks[k]) * TS::threads + tid];
                 rgb_pixel += transmittance_core * f3(rgba_premultiplied);
                 const float depth = kd[k];
                 if (use_median_depth) depth_pixel = (transmittance_core > 0.5f && depth < FLT_MAX) ? depth : depth_pixel;
@@ -531,7 +543,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
         #pragma unroll
         for (int k = 0; k < K; ++k) {
             if (!stop && t >= kTransmittanceThreshold) {
-                const float2 cell = pool2[ks[k] * TS::threads + tid];
+                const float2 cell = pool2[slot_index(ks[k]) * TS::threads + tid];
                 const uint32_t primitive_idx = __float_as_uint(cell.y);
                 if (primitive_idx == 0xffffffffu) { stop = true; }
                 else {
