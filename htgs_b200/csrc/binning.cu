@@ -20,6 +20,8 @@
 //    pass stages the locally sorted tile in shared memory so that global writes are runs.
 #include "kernels.h"
 
+#include <algorithm>
+
 namespace htgs {
 
 FrameGeometry make_geometry(int mode, int width, int height) {
@@ -244,17 +246,18 @@ __device__ __forceinline__ void block_exclusive_scan_512(uint32_t* vals, uint32_
 // in shared memory chain the rounds; a scan over warps and digits turns them into positions in the
 // locally sorted tile, which is staged in shared memory and written out as runs.
 template <typename KeyT>
-__global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(
+__global__ void __launch_bounds__(kSortThreads, 3) radix_scatter_kernel(
     const KeyT* __restrict__ keys_in, const uint32_t* __restrict__ prims_in, KeyT* __restrict__ keys_out, uint32_t* __restrict__ prims_out,
     const uint32_t* __restrict__ table, uint32_t table_stride, const uint32_t* __restrict__ digit_totals,
     const FrameStatus* status, uint32_t capacity, int shift, int bits)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t* warp_count = reinterpret_cast<uint32_t*>(smem_raw);                 // [kSortWarps][n_bins]
-    uint32_t* block_excl = warp_count + kSortWarps * kMaxRadixBins;               // [n_bins]
-    uint32_t* global_base = block_excl + kMaxRadixBins;                           // [n_bins]
-    uint32_t* digit_base = global_base + kMaxRadixBins;                           // [n_bins]
-    uint32_t* prims_s = digit_base + kMaxRadixBins;                               // [kSortTile]
+    const uint32_t n_bins_layout = 1u << bits;
+    uint32_t* block_excl = warp_count + kSortWarps * n_bins_layout;               // [n_bins]
+    uint32_t* global_base = block_excl + n_bins_layout;                           // [n_bins]
+    uint32_t* digit_base = global_base + n_bins_layout;                           // [n_bins]
+    uint32_t* prims_s = digit_base + n_bins_layout;                               // [kSortTile]
     KeyT* keys_s = reinterpret_cast<KeyT*>(prims_s + kSortTile);                  // [kSortTile]
     __shared__ uint32_t warp_tot[kSortWarps];
 
@@ -269,7 +272,7 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(
     block_exclusive_scan_512(digit_base, n_bins, warp_tot);
 
     for (uint32_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
-        for (uint32_t i = threadIdx.x; i < kSortWarps * n_bins; i += kSortThreads) warp_count[(i / n_bins) * kMaxRadixBins + (i % n_bins)] = 0;
+        for (uint32_t i = threadIdx.x; i < kSortWarps * n_bins; i += kSortThreads) warp_count[i] = 0;
         __syncthreads();
         const uint32_t base = blk * kSortTile + warp * (kSortItems * 32);
         KeyT key[kSortItems];
@@ -281,7 +284,7 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(
             if (idx < n) { key[r] = keys_in[idx]; prim[r] = prims_in[idx]; }
             else { key[r] = KeyT(0); prim[r] = 0; }
         }
-        uint32_t* my_count = warp_count + warp * kMaxRadixBins;
+        uint32_t* my_count = warp_count + warp * n_bins;
         #pragma unroll
         for (int r = 0; r < kSortItems; ++r) {
             const uint32_t idx = base + r * 32 + lane;
@@ -311,7 +314,7 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(
         for (uint32_t d = threadIdx.x; d < n_bins; d += kSortThreads) {
             uint32_t running = 0;
             #pragma unroll
-            for (int w = 0; w < kSortWarps; ++w) { const uint32_t t = warp_count[w * kMaxRadixBins + d]; warp_count[w * kMaxRadixBins + d] = running; running += t; }
+            for (int w = 0; w < kSortWarps; ++w) { const uint32_t t = warp_count[w * n_bins + d]; warp_count[w * n_bins + d] = running; running += t; }
             block_excl[d] = running;
         }
         __syncthreads();
@@ -345,8 +348,8 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(
     }
 }
 
-template <typename KeyT> constexpr size_t scatter_smem_bytes() {
-    return (size_t(kSortWarps) * kMaxRadixBins + 3 * kMaxRadixBins + kSortTile) * sizeof(uint32_t) + size_t(kSortTile) * sizeof(KeyT);
+template <typename KeyT> constexpr size_t scatter_smem_bytes(int bits = kMaxRadixBits) {
+    return (size_t(kSortWarps + 3) * (size_t(1) << bits) + kSortTile) * sizeof(uint32_t) + size_t(kSortTile) * sizeof(KeyT);
 }
 
 // Tile ranges from the sorted keys (rasterization/src/shared_kernels.cu:56-95); ranges were zeroed before.
@@ -381,7 +384,6 @@ cudaError_t emit_sort_ranges_t(const HtgsScene& scene, const FrameGeometry& geo,
     if (ev) cudaEventRecord(ev[0], stream);
     if (launches) *launches += 1;
     const uint32_t persistent = uint32_t(sm_count) * 4;
-    const uint32_t sort_grid = inst.sort_blocks_cap < persistent ? (inst.sort_blocks_cap ? inst.sort_blocks_cap : 1) : persistent;
     static bool configured[64] = {};
     int device = 0;
     cudaGetDevice(&device);
@@ -394,9 +396,13 @@ cudaError_t emit_sort_ranges_t(const HtgsScene& scene, const FrameGeometry& geo,
     for (int p = 0; p < plan.n_passes; ++p) {
         KeyT* kin = static_cast<KeyT*>(inst.keys[cur]);
         KeyT* kout = static_cast<KeyT*>(inst.keys[cur ^ 1]);
-        radix_histogram_kernel<KeyT><<<sort_grid, kSortThreads, 0, stream>>>(kin, inst.radix_table, inst.sort_blocks_cap, status, inst.capacity, plan.shift[p], plan.bits[p]);
+        const size_t smem = scatter_smem_bytes<KeyT>(plan.bits[p]);
+        const uint32_t resident = uint32_t(std::min<size_t>(3, (227 * 1024) / (smem + 1024)));   // scatter blocks one SM holds (3 by registers)
+        const uint32_t scatter_grid = std::min<uint32_t>(inst.sort_blocks_cap ? inst.sort_blocks_cap : 1u, uint32_t(sm_count) * resident);
+        const uint32_t hist_grid = std::min<uint32_t>(inst.sort_blocks_cap ? inst.sort_blocks_cap : 1u, uint32_t(sm_count) * 16u);
+        radix_histogram_kernel<KeyT><<<hist_grid, kSortThreads, 0, stream>>>(kin, inst.radix_table, inst.sort_blocks_cap, status, inst.capacity, plan.shift[p], plan.bits[p]);
         radix_scan_rows_kernel<<<1u << plan.bits[p], kSortThreads, 0, stream>>>(inst.radix_table, inst.sort_blocks_cap, inst.digit_totals, status, inst.capacity);
-        radix_scatter_kernel<KeyT><<<sort_grid, kSortThreads, scatter_smem_bytes<KeyT>(), stream>>>(
+        radix_scatter_kernel<KeyT><<<scatter_grid, kSortThreads, smem, stream>>>(
             kin, inst.prims[cur], kout, inst.prims[cur ^ 1], inst.radix_table, inst.sort_blocks_cap, inst.digit_totals, status, inst.capacity,
             plan.shift[p], plan.bits[p]);
         cur ^= 1;

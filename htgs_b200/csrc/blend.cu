@@ -30,7 +30,7 @@
 #include "kernels.h"
 
 #ifndef HTGS_EXPERIMENT
-#define HTGS_EXPERIMENT 0   // timing experiments only (wrong images): 1 no insertion, 2 no exact pass, 3 staging only
+#define HTGS_EXPERIMENT 0   // timing experiments only (wrong images): 1 no insertion, 2 / 4 no exact pass (4 keeps the masks), 3 staging only
 #endif
 
 namespace htgs {
@@ -265,6 +265,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                 copies_landed = true;
             }
             const uint32_t n_cand = __popcll(cand);
+            if (HTGS_EXPERIMENT == 4) transmittance += float(n_cand);   // keeps the candidate masks alive when the exact pass is disabled
             if constexpr (STATS) stat_candidates += n_cand;
             const uint32_t n_iter = __reduce_max_sync(0xffffffffu, n_cand);
             const uint32_t chunk_base = chunk * TS::chunk;
