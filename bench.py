@@ -262,7 +262,9 @@ def main():
     tensors = [torch.from_numpy(np.ascontiguousarray(a)).to(device) for a in scene.arrays()]
     n_views = len(scene.views)
     cams_dev = [(torch.from_numpy(v.M).to(device), torch.from_numpy(v.VPM).to(device), torch.from_numpy(v.cam_position).to(device)) for v in scene.views]
-    cams_host = [tuple(torch.from_numpy(a).pin_memory() for a in (v.M, v.VPM, v.cam_position)) for v in scene.views]
+    # per view ONE pinned host buffer (M, VPM, camera position = 35 floats): one host-to-device copy per frame
+    cams_host = [torch.from_numpy(np.concatenate([v.M.reshape(-1), v.VPM.reshape(-1), v.cam_position.reshape(-1)]).astype(np.float32)).pin_memory()
+                 for v in scene.views]
     v0 = scene.views[0]
     mode_enum = mod.RasterizerMode(scene.mode)
 
@@ -300,7 +302,8 @@ def main():
     e2e_count = [0]
 
     def render_e2e(view_idx):
-        cam = tuple(a.to(device, non_blocking=True) for a in cams_host[view_idx])
+        packed = cams_host[view_idx].to(device, non_blocking=True)
+        cam = (packed[:16].view(4, 4), packed[16:32].view(4, 4), packed[32:35])
         image, depth = render_any(cam)
         h_img, h_depth, done = host_out[e2e_count[0] % 2]
         e2e_count[0] += 1

@@ -326,61 +326,69 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                     if (ok1) commit(depth1, frag1, j1);
                 }
             } else {
-                for (uint32_t it = 0; it < n_iter; ++it) {
-                    bool valid;
-                    const uint32_t j = pop_candidate(valid);
-                    if (!valid || done) continue;
+                // The other three modes use the same two-candidates-per-trip shape: both evaluations (divide, expf, depth) are
+                // independent instruction streams; the state updates happen in list order.  A fragment counts iff it passes
+                // the cutoff, the alpha threshold and (FIRST_K) the depth test against the buffer - conditions that do not
+                // depend on the order in which they are checked (alpha_blend_first_k/kernels/inference.cuh:147-160,
+                // alpha_blend_global_ordering/kernels/inference.cuh:139-160, oit_blend/kernels/inference.cuh:139-160).
+                constexpr bool kNeedsPointDepth = kFirstK || (!kGlobal && !TRAIN);
+                auto evaluate = [&](bool valid, uint32_t j, float& alpha, float& depth, float4& rgba_in) -> bool {
                     const float4* rec = reinterpret_cast<const float4*>(s_eval + j);
                     const FragmentFront fr = fragment_front(rec[0], rec[1], rec[2], pixel_x, pixel_y);
                     const float numerator_rho2 = fr.numerator_rho2;
                     const float denominator = fr.denominator;
-                    if (numerator_rho2 > MT::max_cutoff_sq * denominator) continue;
+                    const bool inside_cutoff = !(numerator_rho2 > MT::max_cutoff_sq * denominator);
                     const float denominator_rcp = 1.0f / denominator;
-                    if constexpr (kFirstK) {
-                        // depth test before expf (alpha_blend_first_k/kernels/inference.cuh:147-153)
+                    rgba_in = rec[4];
+                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                    alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
+                    const float4 MT3 = rec[3];
+                    if constexpr (kNeedsPointDepth) {
                         const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
-                        const float4 MT3 = rec[3];
-                        float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
-                        if (depth >= kd[K - 1]) continue;
-                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                        const float alpha = fminf(rec[4].w * G, kMaxFragmentAlpha);
-                        if (alpha < MT::min_alpha) continue;
+                        depth = dot(f3(MT3), eval_point_diag) + MT3.w;
+                    } else {
+                        depth = MT3.w;
+                    }
+                    return valid && inside_cutoff && !(alpha < MT::min_alpha);
+                };
+                auto commit = [&](uint32_t j, float alpha, float depth, const float4& rgba_in) {
+                    if constexpr (kFirstK) {
+                        if (depth >= kd[K - 1]) return;
                         if constexpr (STATS) ++stat_accepted;
                         pool2[free_slot * TS::threads + tid] = make_float2(alpha, __uint_as_float(s_prim[j]));
                         free_slot = slot_index(kbuffer_insert<K>(kd, ks, depth, slot_t(free_slot)));
                     } else if constexpr (kGlobal) {
-                        const float4 rgba_in = rec[4];
-                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                        const float opacity = rgba_in.w;
-                        const float alpha = fminf(opacity * G, kMaxFragmentAlpha);
-                        if (alpha < MT::min_alpha) continue;
+                        if (done) return;
                         if constexpr (STATS) ++stat_accepted;
                         const float blending_weight = transmittance * alpha;
                         acc.x += blending_weight * rgba_in.x; acc.y += blending_weight * rgba_in.y; acc.z += blending_weight * rgba_in.z;
                         if constexpr (!TRAIN) {
-                            const float depth = rec[3].w;
                             if (use_median_depth) acc.w = (transmittance > 0.5f) ? depth : acc.w;
                             else acc.w += blending_weight * depth;
                         }
                         transmittance *= 1.0f - alpha;
                         if (transmittance < kTransmittanceThreshold) done = true;
                     } else {   // OIT_BLEND
-                        const float4 rgba_in = rec[4];
-                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                        const float alpha = fminf(rgba_in.w * G, kMaxFragmentAlpha);
-                        if (alpha < MT::min_alpha) continue;
                         if constexpr (STATS) ++stat_accepted;
                         if constexpr (TRAIN) {
                             acc.x += alpha * rgba_in.x; acc.y += alpha * rgba_in.y; acc.z += alpha * rgba_in.z;
                         } else {
-                            const float3 eval_point_diag = cross(fr.d, fr.m) * denominator_rcp;
-                            const float4 MT3 = rec[3];
-                            const float depth = dot(f3(MT3), eval_point_diag) + MT3.w;
                             acc += alpha * make_float4(rgba_in.x, rgba_in.y, rgba_in.z, depth);
                         }
                         acc_depth += alpha;
                         transmittance *= 1.0f - alpha;
                     }
+                };
+                for (uint32_t it = 0; it < n_iter; it += 2) {
+                    bool v0, v1;
+                    const uint32_t j0 = pop_candidate(v0);
+                    const uint32_t j1 = pop_candidate(v1);
+                    float alpha0, alpha1, depth0, depth1;
+                    float4 rgba0, rgba1;
+                    const bool ok0 = evaluate(v0, j0, alpha0, depth0, rgba0);
+                    const bool ok1 = evaluate(v1, j1, alpha1, depth1, rgba1);
+                    if (ok0) commit(j0, alpha0, depth0, rgba0);
+                    if (ok1) commit(j1, alpha1, depth1, rgba1);
                 }
             }
         }   // chunk loop
