@@ -43,6 +43,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--views-per-step", type=int, default=8)
+    ap.add_argument("--streams", type=int, default=2, help="frames in flight per GPU on this library's arm (host threads, one CUDA stream each)")
     ap.add_argument("--n-gaussians", type=int, default=3_000_000, help="scale the workload down for quick checks (invalid as a benchmark)")
     ap.add_argument("--workload", default="render", choices=["render", "render_fast", "train"],
                     help="render: configuration 1 (default, the headline metric); train: configuration 2 (fwd+bwd, L1 loss, one view per GPU, gradient all-reduce)")
@@ -276,87 +277,154 @@ def main():
         run_training(args, mod, ref_mod is not None, scene, tensors, cams_dev, settings, device, dist, rank, world, workload_name)
         return
 
-    launches = [0]
     fast = args.workload == "render_fast"   # the relaxed-precision RGB-only entry point (`fast_rasterize`) of either implementation
     if fast:
         workload_name = workload_name.replace("config1", "config1 via fast_rasterize (relaxed precision, RGB only)")
+    # Frames in flight.  This library's contexts are re-entrant (one per host thread, no global device state), so the job
+    # is driven by `--streams` host threads, each with its own CUDA stream, rendering alternate views: the small kernels and
+    # the tail of one frame overlap the next frame's work.  The reference keeps per-call state in module-global constant
+    # memory and a function-static stream (rasterization/include/kernel_utils.cuh:10-12), so its arm runs one frame at a time.
+    n_lanes = 1 if ref_mod is not None else max(1, args.streams)
 
     def render_any(cam):
         if fast:
             return mod.fast_rasterize(*tensors, settings(cam), True), None
         return mod.rasterize(*tensors, settings(cam), True, False)
 
-    def render_resident(view_idx):
-        out = render_any(cams_dev[view_idx])
-        if ref_mod is None:
-            launches[0] += our_C.last_frame_info.kernel_launches
-        return out
-
     n_pix = v0.width * v0.height
 
-    # end-to-end frame: camera H2D from pinned memory -> rasterize -> image + depth D2H into pinned memory.  The copies back
-    # run on a second stream into two alternating pinned buffers, so that they overlap the next frame's kernels.
-    copy_stream = torch.cuda.Stream(device=device)
-    host_out = [(torch.empty((3, v0.height, v0.width), dtype=torch.float32).pin_memory(),
-                 torch.empty((1, v0.height, v0.width), dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(2)]
-    e2e_count = [0]
+    class Lane:
+        """One host thread's share of the job: its CUDA stream, its copy-back stream and two alternating pinned buffers."""
 
-    def render_e2e(view_idx):
-        packed = cams_host[view_idx].to(device, non_blocking=True)
-        cam = (packed[:16].view(4, 4), packed[16:32].view(4, 4), packed[32:35])
-        image, depth = render_any(cam)
-        h_img, h_depth, done = host_out[e2e_count[0] % 2]
-        e2e_count[0] += 1
-        done.synchronize()                       # the copy that used this pinned buffer two frames ago has finished
-        copy_stream.wait_stream(torch.cuda.current_stream(device))
-        with torch.cuda.stream(copy_stream):
-            h_img.copy_(image, non_blocking=True)
+        def __init__(self, own_stream: bool):
+            self.stream = torch.cuda.Stream(device=device) if own_stream else torch.cuda.current_stream(device)
+            self.copy_stream = torch.cuda.Stream(device=device)
+            self.host_out = [(torch.empty((3, v0.height, v0.width), dtype=torch.float32).pin_memory(),
+                              torch.empty((1, v0.height, v0.width), dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+            self.count = 0
+            self.launches = 0
+
+        def resident(self, view_idx):
+            render_any(cams_dev[view_idx])
+            if ref_mod is None:
+                self.launches += our_C.last_frame_info.kernel_launches
+
+        def e2e(self, view_idx):
+            # camera H2D from pinned memory -> rasterize -> image (+ depth) D2H into pinned memory; the copies back run on the
+            # lane's second stream into two alternating pinned buffers, so that they overlap the next frame's kernels
+            packed = cams_host[view_idx].to(device, non_blocking=True)
+            cam = (packed[:16].view(4, 4), packed[16:32].view(4, 4), packed[32:35])
+            image, depth = render_any(cam)
+            h_img, h_depth, done = self.host_out[self.count % 2]
+            self.count += 1
+            done.synchronize()                       # the copy that used this pinned buffer two frames ago has finished
+            self.copy_stream.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(self.copy_stream):
+                h_img.copy_(image, non_blocking=True)
+                if depth is not None:
+                    h_depth.copy_(depth, non_blocking=True)
+                done.record(self.copy_stream)
+            image.record_stream(self.copy_stream)
             if depth is not None:
-                h_depth.copy_(depth, non_blocking=True)
-            done.record(copy_stream)
-        image.record_stream(copy_stream)
-        if depth is not None:
-            depth.record_stream(copy_stream)
+                depth.record_stream(self.copy_stream)
 
-    def timed(fn, steps, warmup, sample_clocks=False):
-        # untimed pass over the views of the timed region: lets either implementation grow its buffers / allocator pools
-        for s in range(warmup, warmup + steps):
-            for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views):
-                fn(vi)
-        for s in range(warmup):
-            for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views):
-                fn(vi)
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-        sampler = ClockSampler(local_rank) if sample_clocks else None
-        if sampler:
-            sampler.start()
-            time.sleep(0.25)
-        launches[0] = 0
+    lanes = [Lane(own_stream=n_lanes > 1) for _ in range(n_lanes)]
+    launches = [0]
+
+    def timed(kind, steps, warmup, sample_clocks=False, n_lanes=n_lanes):
+        import threading
+        timed_views = [vi for s in range(warmup, warmup + steps) for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views)]
+        warm_views = [vi for s in range(warmup) for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views)]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.time()
-        e0.record()
-        for s in range(warmup, warmup + steps):
-            for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views):
+        gate = threading.Barrier(n_lanes + 1)
+        errors = []
+        for lane in lanes:
+            lane.launches = 0
+
+        def lane_body(k):
+            lane = lanes[k]
+            fn = lane.resident if kind == "resident" else lane.e2e
+            try:
+                torch.cuda.set_device(device)
+                with torch.cuda.stream(lane.stream):
+                    # untimed: the views of the timed region once (either implementation grows its buffers / allocator pools), then the warm-up steps
+                    for vi in timed_views[k::n_lanes] + warm_views[k::n_lanes]:
+                        fn(vi)
+                    lane.stream.synchronize()
+                    lane.copy_stream.synchronize()
+                    if n_lanes > 1:
+                        gate.wait()          # everybody is warm
+                        gate.wait()          # the main thread has recorded the start event
+                        lane.stream.wait_event(e0)
+                    lane.launches = 0
+                    for vi in timed_views[k::n_lanes]:
+                        fn(vi)
+                    lane.stream.wait_stream(lane.copy_stream)   # outstanding copies back belong to the timed region
+            except Exception as exc:  # noqa: BLE001 - reported by the main thread
+                errors.append(exc)
+                if n_lanes > 1:
+                    gate.abort()
+
+        def prepare():
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            sampler = ClockSampler(local_rank) if sample_clocks else None
+            if sampler:
+                sampler.start()
+                time.sleep(0.25)
+            return sampler
+
+        main_stream = torch.cuda.current_stream(device)
+        if n_lanes == 1:
+            lane = lanes[0]
+            fn = lane.resident if kind == "resident" else lane.e2e
+            for vi in timed_views + warm_views:
                 fn(vi)
-        torch.cuda.current_stream(device).wait_stream(copy_stream)   # outstanding copies back belong to the timed region
-        e1.record()
+            sampler = prepare()
+            lane.launches = 0
+            t0 = time.time()
+            e0.record()
+            for vi in timed_views:
+                fn(vi)
+            main_stream.wait_stream(lane.copy_stream)   # outstanding copies back belong to the timed region
+            e1.record()
+        else:
+            threads = [threading.Thread(target=lane_body, args=(k,)) for k in range(n_lanes)]
+            for th in threads:
+                th.start()
+            try:
+                gate.wait()
+                sampler = prepare()
+                t0 = time.time()
+                e0.record(main_stream)
+                gate.wait()
+            except threading.BrokenBarrierError:
+                sampler = None
+                t0 = time.time()
+            for th in threads:
+                th.join()
+            if errors:
+                raise errors[0]
+            for lane in lanes:
+                main_stream.wait_stream(lane.stream)
+            e1.record(main_stream)
         torch.cuda.synchronize()
         t1 = time.time()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
         clocks = sampler.stop(t0, t1) if sampler else None
+        launches[0] = sum(lane.launches for lane in lanes)
         ms = parallel.max_over_ranks(e0.elapsed_time(e1), device)
         return ms, clocks
 
-    ms_total, clocks = timed(render_resident, args.steps, args.warmup, sample_clocks=True)
+    ms_total, clocks = timed("resident", args.steps, args.warmup, sample_clocks=True)
     frames_total = args.steps * args.views_per_step * world
     value = frames_total / (ms_total / 1000.0)
     timed_launches = launches[0] * world
-    ms_e2e, _ = timed(render_e2e, args.steps, args.warmup)
+    ms_e2e, _ = timed("e2e", args.steps, args.warmup)
     e2e_value = frames_total / (ms_e2e / 1000.0)
 
     line = {
@@ -365,12 +433,19 @@ def main():
         "data": "synthetic",
         "config": {"workload": workload_name, "views_per_step_per_gpu": args.views_per_step, "parallelism": f"view-partitioned x{world}",
                    "l2": "per-frame working set (708 MB scene + >300 MB per-Gaussian records) exceeds the 126 MB L2; no explicit flush",
-                   "scene_residency": "scene resident in HBM; per-frame inputs are the camera matrices"},
+                   "scene_residency": "scene resident in HBM; per-frame inputs are the camera matrices",
+                   "frames_in_flight": n_lanes},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": args.views_per_step * (16 + 16 + 3) * 4,
                 "d2h_bytes_per_step": args.views_per_step * n_pix * 4 * (3 if fast else 4), "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": timed_launches,
     }
+
+    if ref_mod is None and n_lanes > 1:
+        # the same job with one frame in flight (one host thread, one stream), for comparison
+        ms_1, _ = timed("resident", args.steps, args.warmup, n_lanes=1)
+        ms_1e, _ = timed("e2e", args.steps, args.warmup, n_lanes=1)
+        line["one_frame_in_flight"] = {"value": frames_total / (ms_1 / 1000.0), "e2e": frames_total / (ms_1e / 1000.0), "unit": "frames/s"}
 
     if ref_mod is not None:
         line.update({"impl": "reference", "reference_kind": "cuda-extension (unmodified HTGSCudaBackend built for sm_100a under baseline/_ref)",
@@ -392,7 +467,7 @@ def main():
     infos = []
     for _ in range(2):   # second round is the one kept (warm)
         for i, vi in enumerate(probe_views):
-            render_resident(vi)
+            render_any(cams_dev[vi])
             lib.htgs_get_stage_ms(ctx, buf)
             stage[i] = np.array(buf[:], np.float64)
     lib.htgs_set_profiling(ctx, 0)

@@ -160,16 +160,19 @@ _ctx_lock = threading.Lock()
 
 
 def context(device_index: int) -> int:
-    """One library context per CUDA device of this process (created on first use)."""
-    ctx = _contexts.get(device_index)
+    """One library context per (CUDA device, host thread) of this process, created on first use.  A context owns its
+    workspace and its pinned status word, so two host threads that render concurrently (each on its own CUDA stream)
+    must not share one; giving every thread its own makes the Python surface safe to call from several threads."""
+    key = (int(device_index), threading.get_ident())
+    ctx = _contexts.get(key)
     if ctx is None:
         with _ctx_lock:
-            ctx = _contexts.get(device_index)
+            ctx = _contexts.get(key)
             if ctx is None:
                 ctx = lib().htgs_create(int(device_index))
                 if not ctx:
                     raise RuntimeError(f"htgs_create({device_index}) failed: {last_error()}")
-                _contexts[device_index] = ctx
+                _contexts[key] = ctx
     return ctx
 
 
