@@ -43,7 +43,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--views-per-step", type=int, default=8)
-    ap.add_argument("--streams", type=int, default=2, help="frames in flight per GPU on this library's arm (host threads, one CUDA stream each)")
+    ap.add_argument("--streams", type=int, default=0,
+                    help="frames in flight per GPU on this library's arm (host threads, one CUDA stream each); 0 = 2 if the host has at least 3 hardware threads per rank, else 1")
     ap.add_argument("--n-gaussians", type=int, default=3_000_000, help="scale the workload down for quick checks (invalid as a benchmark)")
     ap.add_argument("--workload", default="render", choices=["render", "render_fast", "train"],
                     help="render: configuration 1 (default, the headline metric); train: configuration 2 (fwd+bwd, L1 loss, one view per GPU, gradient all-reduce)")
@@ -284,7 +285,16 @@ def main():
     # is driven by `--streams` host threads, each with its own CUDA stream, rendering alternate views: the small kernels and
     # the tail of one frame overlap the next frame's work.  The reference keeps per-call state in module-global constant
     # memory and a function-static stream (rasterization/include/kernel_utils.cuh:10-12), so its arm runs one frame at a time.
-    n_lanes = 1 if ref_mod is not None else max(1, args.streams)
+    if args.streams > 0:
+        n_lanes = args.streams
+    else:
+        try:
+            host_threads = len(os.sched_getaffinity(0))
+        except AttributeError:
+            host_threads = os.cpu_count() or 1
+        n_lanes = 2 if host_threads >= 3 * world else 1   # a lane's thread busy-waits on its stream: do not oversubscribe the host
+    if ref_mod is not None:
+        n_lanes = 1
 
     def render_any(cam):
         if fast:
