@@ -202,7 +202,7 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
     if (max_weights) {
         if ((err = launch_max_weights(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, max_weights, weight_threshold, stream)) != cudaSuccess) return fail_cuda(err, "max weights");
     } else if (fast) {
-        if ((err = launch_blend_fast(view.K, geo, L.prim, prims_sorted, L.tile_ranges, out.image, out.to_chw, L.status, stream)) != cudaSuccess) return fail_cuda(err, "fast blend");
+        if ((err = launch_blend_fast(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, out.image, out.to_chw, L.status, stream)) != cudaSuccess) return fail_cuda(err, "fast blend");
     } else if ((err = launch_blend(view.mode, view.K, false, geo, L.prim, prims_sorted, L.tile_ranges, out, TrainPixelBuffers{}, L.status, stream)) != cudaSuccess) return fail_cuda(err, "blend");
     *launches += 1;
     if (prof) cudaEventRecord(ev[6], stream);

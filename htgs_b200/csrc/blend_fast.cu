@@ -1,7 +1,7 @@
-// Relaxed-precision HYBRID_BLEND inference: the kernel behind fast_rasterize.
+// Relaxed-precision inference for HYBRID_BLEND, ALPHA_BLEND_FIRST_K and OIT_BLEND: the kernels behind fast_rasterize.
 //
-// Replaces blend_cu of rasterization/include/hybrid_blend/kernels/fast_inference.cuh:81-218 (the reference's
-// fast-math build with a half-precision K-buffer; RGB only, no depth output).  Results agree with that kernel to
+// Replaces blend_cu of rasterization/include/{hybrid_blend,alpha_blend_first_k,oit_blend}/kernels/fast_inference.cuh
+// (the reference's fast-math build; HYBRID keeps a half-precision K-buffer; RGB only, no depth output).  Results agree with that kernel to
 // about 1e-3 per channel, not bit for bit: this path trades the operation-for-operation evaluation of the
 // exact kernel (blend.cu) for fewer instructions per fragment.
 //
@@ -18,7 +18,8 @@
 //    updates the per-row maxima it keeps in registers: about 20 ALU-pipe instructions and 9 shared-memory wavefronts
 //    instead of 5 instructions per level of a sorted chain.
 //    Entries are sorted once per pixel when the tile is composited.  Fragments of exactly equal depth are ordered by
-//    position instead of by arrival.
+//    position instead of by arrival.  FIRST_K uses the same buffer with (alpha, Gaussian index) payloads and no tail;
+//    OIT has no buffer at all and skips the depth polynomial.
 #include "kernels.h"
 
 #include <cuda_fp16.h>
@@ -33,19 +34,21 @@ namespace {
 
 constexpr int kFastThreads = 64;     // 8 x 8 pixel tile, one thread per pixel
 constexpr int kFastBatch = 64;       // instances staged per iteration, one per thread
-using FastTraits = ModeTraits<HTGS_MODE_HYBRID_BLEND>;
 
-template <int K> struct FastSmem {
+template <int MODE, int K> struct FastSmem {
+    static constexpr bool has_kbuffer = MODE != HTGS_MODE_OIT_BLEND;
+    static constexpr bool has_prim = MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K;
     static constexpr size_t rec_off = 0;
     static constexpr size_t rec_bytes = size_t(kFastBatch) * sizeof(FastRecord);
     static constexpr size_t cull4_off = rec_off + rec_bytes;
     static constexpr size_t cullc_off = cull4_off + size_t(kFastBatch) * 16;
     static constexpr size_t ctr_off = cullc_off + size_t(kFastBatch) * 4;      // float2: projected centre relative to the tile origin
-    static constexpr size_t bar_off = ctr_off + size_t(kFastBatch) * 8;
+    static constexpr size_t prim_off = ctr_off + size_t(kFastBatch) * 8;        // Gaussian index of every staged instance (FIRST_K)
+    static constexpr size_t bar_off = prim_off + (has_prim ? size_t(kFastBatch) * 4 : 0);
     static constexpr size_t keys_off = bar_off + 16;
-    static constexpr size_t keys_bytes = size_t(K) * kFastThreads * 4;     // uint4 [K/4][threads]
+    static constexpr size_t keys_bytes = has_kbuffer ? size_t(K) * kFastThreads * 4 : 0;     // uint4 [K/4][threads]
     static constexpr size_t pay_off = keys_off + keys_bytes;
-    static constexpr size_t pay_bytes = size_t(K) * kFastThreads * 8;      // half4 [K][threads]
+    static constexpr size_t pay_bytes = has_kbuffer ? size_t(K) * kFastThreads * 8 : 0;      // 8-byte payload [K][threads]
     static constexpr size_t total = pay_off + pay_bytes;
     static_assert(bar_off % 16 == 0 && keys_off % 16 == 0, "shared-memory sections must stay 16-byte aligned");
 };
@@ -119,21 +122,27 @@ __device__ __forceinline__ uint2 core_replace(uint32_t* keys, uint2* pay, uint32
     return evicted;
 }
 
-template <int K>
+template <int MODE, int K>
 __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const FastRecord* __restrict__ records,
     const CullRecord* __restrict__ cull, float* __restrict__ image, uint32_t width, uint32_t height, uint32_t grid_w, bool to_chw,
     FrameStatus* status)
 {
-    using SL = FastSmem<K>;
+    using SL = FastSmem<MODE, K>;
+    using MT = ModeTraits<MODE>;
+    constexpr bool kHybrid = MODE == HTGS_MODE_HYBRID_BLEND;
+    constexpr bool kFirstK = MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K;
+    constexpr bool kOit = MODE == HTGS_MODE_OIT_BLEND;
+    static_assert(kHybrid || kFirstK || kOit, "no relaxed-precision kernel for this mode");
     extern __shared__ __align__(128) unsigned char smem[];
     FastRecord* s_rec = reinterpret_cast<FastRecord*>(smem + SL::rec_off);
     float4* s_cull4 = reinterpret_cast<float4*>(smem + SL::cull4_off);
     float* s_cullc = reinterpret_cast<float*>(smem + SL::cullc_off);
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + SL::bar_off);
     float2* s_ctr = reinterpret_cast<float2*>(smem + SL::ctr_off);
-    uint32_t* keys = reinterpret_cast<uint32_t*>(smem + SL::keys_off);
-    uint2* pay = reinterpret_cast<uint2*>(smem + SL::pay_off);
+    [[maybe_unused]] uint32_t* s_prim = reinterpret_cast<uint32_t*>(smem + SL::prim_off);
+    [[maybe_unused]] uint32_t* keys = reinterpret_cast<uint32_t*>(smem + SL::keys_off);
+    [[maybe_unused]] uint2* pay = reinterpret_cast<uint2*>(smem + SL::pay_off);
 
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = tid >> 5, lane = tid & 31;
@@ -145,18 +154,20 @@ __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
 
     if (tid == 0) { mbar_init(s_bar, kFastThreads); mbar_fence_init(); }
 
-    // empty core: the largest keys, carrying their position; zero payloads
-    #pragma unroll
-    for (int c = 0; c < K; ++c) {
-        keys[((c >> 2) * kFastThreads + tid) * 4 + (c & 3)] = KeyCodec<K>::empty | uint32_t(c);
-        pay[c * kFastThreads + tid] = make_uint2(0u, 0u);
+    // empty core: the largest keys, carrying their position; zero payloads (FIRST_K: alpha 0, no Gaussian)
+    if constexpr (SL::has_kbuffer) {
+        #pragma unroll
+        for (int c = 0; c < K; ++c) {
+            keys[((c >> 2) * kFastThreads + tid) * 4 + (c & 3)] = KeyCodec<K>::empty | uint32_t(c);
+            pay[c * kFastThreads + tid] = make_uint2(0u, kFirstK ? 0xffffffffu : 0u);
+        }
     }
-    uint32_t row_max[K / 4];
+    [[maybe_unused]] uint32_t row_max[K / 4];
     #pragma unroll
     for (int q = 0; q < K / 4; ++q) row_max[q] = KeyCodec<K>::empty | uint32_t(4 * q + 3);
-    uint32_t kmax = 0xffffffffu;                             // position K-1
-    float depth_max = __int_as_float(0x7f800000);            // depth a fragment has to beat to enter the core
-    float4 tail = make_float4(0.0f, 0.0f, 0.0f, 0.0f);       // premultiplied rgb, alpha sum
+    [[maybe_unused]] uint32_t kmax = 0xffffffffu;            // position K-1
+    [[maybe_unused]] float depth_max = __int_as_float(0x7f800000);   // depth a fragment has to beat to enter the core
+    float4 tail = make_float4(0.0f, 0.0f, 0.0f, 0.0f);       // HYBRID tail / OIT sums: premultiplied rgb, alpha sum
     float transmittance_tail = 1.0f;
 
     const uint2 range = tile_ranges[tile_y * grid_w + tile_x];
@@ -186,6 +197,7 @@ __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
         if (valid_inst) {
             mbar_arrive_expect_tx(s_bar, uint32_t(sizeof(FastRecord)));
             bulk_copy_g2s(s_rec + tid, records + g_next, uint32_t(sizeof(FastRecord)), s_bar);
+            if constexpr (SL::has_prim) s_prim[tid] = g_next;
         } else {
             mbar_arrive(s_bar);
         }
@@ -237,24 +249,40 @@ __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
         auto evaluate = [&](uint32_t j, float& depth, float4& frag) {
             const float4* rec = reinterpret_cast<const float4*>(s_rec + j);
             const float2 ctr = s_ctr[j];
-            const float4 r0 = rec[0], r1 = rec[1], r2 = rec[2], r3 = rec[3], r4 = rec[4];
+            const float4 r0 = rec[0], r1 = rec[1], r3 = rec[3], r4 = rec[4];
             const float dx = local_x + ctr.x, dy = local_y + ctr.y;
             const float xx = dx * dx, xy = dx * dy, yy = dy * dy;
             const float e = fmaf(r0.x, xx, fmaf(r0.y, xy, r0.z * yy));
             const float den = fmaf(r0.w, dx, fmaf(r1.y, xx, 1.0f)) + fmaf(r1.x, dy, fmaf(r1.z, xy, r1.w * yy));
-            const float num_z = fmaf(r2.x, dx, fmaf(r2.z, xx, r2.w * xy)) + fmaf(r2.y, dy, r3.x * yy);
             const float den_rcp = rcp_approx(den);
             const float alpha = fminf(exp2_approx(fmaf(e, den_rcp, r3.z)), kMaxFragmentAlpha);
-            depth = fmaf(num_z, den_rcp, r3.y);
-            frag = make_float4(r3.w * alpha, r4.x * alpha, r4.y * alpha, alpha);
-        };
-        auto commit = [&](float depth, float4 frag) {
-            if (HTGS_EXPERIMENT != 1 && depth < depth_max && frag.w >= FastTraits::min_alpha_core) {
-                frag = unpack_half4(core_replace<K>(keys, pay, tid, depth, pack_half4(frag.x, frag.y, frag.z, frag.w), row_max, kmax));
-                depth_max = KeyCodec<K>::decode(kmax);
+            if constexpr (kOit) {
+                depth = 0.0f;   // the RGB-only OIT result does not depend on depth
+            } else {
+                const float4 r2 = rec[2];
+                const float num_z = fmaf(r2.x, dx, fmaf(r2.z, xx, r2.w * xy)) + fmaf(r2.y, dy, r3.x * yy);
+                depth = fmaf(num_z, den_rcp, r3.y);
             }
-            tail += frag;
-            transmittance_tail *= 1.0f - frag.w;
+            if constexpr (kFirstK) frag = make_float4(0.0f, 0.0f, 0.0f, alpha);   // the colour is fetched when the tile is composited
+            else frag = make_float4(r3.w * alpha, r4.x * alpha, r4.y * alpha, alpha);
+        };
+        auto commit = [&](uint32_t j, float depth, float4 frag) {
+            if constexpr (kHybrid) {
+                if (HTGS_EXPERIMENT != 1 && depth < depth_max && frag.w >= MT::min_alpha_core) {
+                    frag = unpack_half4(core_replace<K>(keys, pay, tid, depth, pack_half4(frag.x, frag.y, frag.z, frag.w), row_max, kmax));
+                    depth_max = KeyCodec<K>::decode(kmax);
+                }
+                tail += frag;
+                transmittance_tail *= 1.0f - frag.w;
+            } else if constexpr (kFirstK) {
+                if (depth < depth_max) {   // whatever falls out of the buffer is dropped (alpha_blend_first_k/kernels/fast_inference.cuh:147-160)
+                    core_replace<K>(keys, pay, tid, depth, make_uint2(__float_as_uint(frag.w), s_prim[j]), row_max, kmax);
+                    depth_max = KeyCodec<K>::decode(kmax);
+                }
+            } else {   // oit_blend/kernels/fast_inference.cuh:138-141
+                tail += frag;
+                transmittance_tail *= 1.0f - frag.w;
+            }
         };
         for (uint32_t it = 0; it < (HTGS_EXPERIMENT >= 2 ? 0u : n_iter); it += 2) {
             bool v0, v1;
@@ -264,52 +292,70 @@ __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
             float4 frag0, frag1;
             evaluate(j0, depth0, frag0);
             evaluate(j1, depth1, frag1);
-            if (v0 && !(frag0.w < FastTraits::min_alpha)) commit(depth0, frag0);
-            if (v1 && !(frag1.w < FastTraits::min_alpha)) commit(depth1, frag1);
+            if (v0 && !(frag0.w < MT::min_alpha)) commit(j0, depth0, frag0);
+            if (v1 && !(frag1.w < MT::min_alpha)) commit(j1, depth1, frag1);
         }
     }
 
     if (wait_failed) atomicOr(&status->error, 1u);
     if (!inside) return;
 
-    // ---- composite (hybrid_blend/kernels/fast_inference.cuh:193-216): sort the core entries by key, blend front to back
-    uint32_t v[K];
-    {
-        const uint4* rows = reinterpret_cast<const uint4*>(keys) + tid;
-        #pragma unroll
-        for (int q = 0; q < K / 4; ++q) {
-            const uint4 row = rows[q * kFastThreads];
-            v[4 * q] = row.x; v[4 * q + 1] = row.y; v[4 * q + 2] = row.z; v[4 * q + 3] = row.w;
-        }
-    }
-    #pragma unroll
-    for (int k = 2; k <= K; k <<= 1) {
-        #pragma unroll
-        for (int j = k >> 1; j > 0; j >>= 1) {
+    float3 rgb_pixel = make_float3(0.0f, 0.0f, 0.0f);
+    if constexpr (SL::has_kbuffer) {
+        // ---- composite: sort the core entries by key, blend front to back (hybrid_blend/kernels/fast_inference.cuh:193-216,
+        // alpha_blend_first_k/kernels/fast_inference.cuh:166-180)
+        uint32_t v[K];
+        {
+            const uint4* rows = reinterpret_cast<const uint4*>(keys) + tid;
             #pragma unroll
-            for (int i = 0; i < K; ++i) {
-                const int l = i ^ j;
-                if (l > i) {
-                    const uint32_t lo = min(v[i], v[l]), hi = max(v[i], v[l]);
-                    if ((i & k) == 0) { v[i] = lo; v[l] = hi; } else { v[i] = hi; v[l] = lo; }
+            for (int q = 0; q < K / 4; ++q) {
+                const uint4 row = rows[q * kFastThreads];
+                v[4 * q] = row.x; v[4 * q + 1] = row.y; v[4 * q + 2] = row.z; v[4 * q + 3] = row.w;
+            }
+        }
+        #pragma unroll
+        for (int k = 2; k <= K; k <<= 1) {
+            #pragma unroll
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                #pragma unroll
+                for (int i = 0; i < K; ++i) {
+                    const int l = i ^ j;
+                    if (l > i) {
+                        const uint32_t lo = min(v[i], v[l]), hi = max(v[i], v[l]);
+                        if ((i & k) == 0) { v[i] = lo; v[l] = hi; } else { v[i] = hi; v[l] = lo; }
+                    }
                 }
             }
         }
-    }
-    float3 rgb_pixel = make_float3(0.0f, 0.0f, 0.0f);
-    float transmittance_core = 1.0f;
-    #pragma unroll
-    for (int k = 0; k < K; ++k) {
-        if (transmittance_core >= kTransmittanceThreshold) {
-            const uint32_t c = v[k] & uint32_t(K - 1);
-            const float4 rgba = unpack_half4(pay[c * kFastThreads + tid]);
-            rgb_pixel += transmittance_core * f3(rgba);
-            transmittance_core *= 1.0f - rgba.w;
+        float transmittance_core = 1.0f;
+        #pragma unroll
+        for (int k = 0; k < K; ++k) {
+            if (transmittance_core >= kTransmittanceThreshold) {
+                const uint32_t c = v[k] & uint32_t(K - 1);
+                const uint2 cell = pay[c * kFastThreads + tid];
+                if constexpr (kHybrid) {
+                    const float4 rgba = unpack_half4(cell);
+                    rgb_pixel += transmittance_core * f3(rgba);
+                    transmittance_core *= 1.0f - rgba.w;
+                } else {
+                    if (cell.y == 0xffffffffu) { transmittance_core = 0.0f; continue; }   // empty entries sort last: nothing follows
+                    const float alpha = __uint_as_float(cell.x);
+                    const float* rec = reinterpret_cast<const float*>(records + cell.y);
+                    const float3 rgb = make_float3(__ldg(rec + 15), __ldg(rec + 16), __ldg(rec + 17));   // FastRecord::r, g, b
+                    rgb_pixel += (transmittance_core * alpha) * rgb;
+                    transmittance_core *= 1.0f - alpha;
+                }
+            }
         }
-    }
-    if (transmittance_core >= kTransmittanceThreshold && tail.w >= FastTraits::min_alpha) {
-        const float weight_tail = transmittance_core * (1.0f - transmittance_tail);
-        rgb_pixel += weight_tail * (1.0f / tail.w) * f3(tail);
+        if constexpr (kHybrid) {
+            if (transmittance_core >= kTransmittanceThreshold && tail.w >= MT::min_alpha) {
+                const float weight_tail = transmittance_core * (1.0f - transmittance_tail);
+                rgb_pixel += weight_tail * (1.0f / tail.w) * f3(tail);
+            }
+        }
+    } else {
+        // oit_blend/kernels/fast_inference.cuh:147-152
+        if (tail.w >= MT::min_alpha) rgb_pixel = ((1.0f - transmittance_tail) * (1.0f / tail.w)) * f3(tail);
     }
     const uint32_t pixel_idx = width * py_i + px_i;
     if (to_chw) {
@@ -324,42 +370,54 @@ __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
     }
 }
 
-template <int K>
+template <int MODE, int K>
 cudaError_t launch_fast_k(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges, float* image,
                           bool to_chw, FrameStatus* status, cudaStream_t stream) {
-    using SL = FastSmem<K>;
+    using SL = FastSmem<MODE, K>;
     static bool configured[64] = {};
     int device = 0;
     cudaGetDevice(&device);
     if (device >= 0 && device < 64 && !configured[device]) {
-        cudaError_t err = cudaFuncSetAttribute(blend_fast_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SL::total));
+        cudaError_t err = cudaFuncSetAttribute(blend_fast_kernel<MODE, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SL::total));
         if (err != cudaSuccess) return err;
-        err = cudaFuncSetAttribute(blend_fast_kernel<K>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        err = cudaFuncSetAttribute(blend_fast_kernel<MODE, K>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (err != cudaSuccess) return err;
         configured[device] = true;
     }
     if (geo.n_tiles == 0) return cudaSuccess;
-    blend_fast_kernel<K><<<dim3(geo.grid_w, geo.grid_h), kFastThreads, SL::total, stream>>>(
+    blend_fast_kernel<MODE, K><<<dim3(geo.grid_w, geo.grid_h), kFastThreads, SL::total, stream>>>(
         tile_ranges, prims_sorted, reinterpret_cast<const FastRecord*>(prim.eval), prim.cull, image, uint32_t(geo.width), uint32_t(geo.height),
         uint32_t(geo.grid_w), to_chw, status);
     return cudaGetLastError();
 }
 
+template <int MODE>
+cudaError_t launch_fast_mode(int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+                             float* image, bool to_chw, FrameStatus* status, cudaStream_t stream) {
+    switch (effective_k(MODE, K)) {
+        case 4: return launch_fast_k<MODE, 4>(geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
+        case 8: return launch_fast_k<MODE, 8>(geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
+        case 16: return launch_fast_k<MODE, 16>(geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
+        case 32: return launch_fast_k<MODE, 32>(geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
 }  // namespace
 
 bool blend_fast_supports(int mode, int K) {
-    if (mode != HTGS_MODE_HYBRID_BLEND) return false;
+    if (mode == HTGS_MODE_OIT_BLEND) return true;
+    if (mode != HTGS_MODE_HYBRID_BLEND && mode != HTGS_MODE_ALPHA_BLEND_FIRST_K) return false;
     const int k = effective_k(mode, K);
     return k == 4 || k == 8 || k == 16 || k == 32;
 }
 
-cudaError_t launch_blend_fast(int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+cudaError_t launch_blend_fast(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
                               float* image, bool to_chw, FrameStatus* status, cudaStream_t stream) {
-    switch (effective_k(HTGS_MODE_HYBRID_BLEND, K)) {
-        case 4: return launch_fast_k<4>(geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
-        case 8: return launch_fast_k<8>(geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
-        case 16: return launch_fast_k<16>(geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
-        case 32: return launch_fast_k<32>(geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
+    switch (mode) {
+        case HTGS_MODE_HYBRID_BLEND: return launch_fast_mode<HTGS_MODE_HYBRID_BLEND>(K, geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
+        case HTGS_MODE_ALPHA_BLEND_FIRST_K: return launch_fast_mode<HTGS_MODE_ALPHA_BLEND_FIRST_K>(K, geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
+        case HTGS_MODE_OIT_BLEND: return launch_fast_k<HTGS_MODE_OIT_BLEND, 4>(geo, prim, prims_sorted, tile_ranges, image, to_chw, status, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -47,7 +47,7 @@ struct FrameGeometry {
 FrameGeometry make_geometry(int mode, int width, int height);
 
 // preprocess.cu
-// `fast_records`: write FastRecord instead of EvalRecord (HYBRID_BLEND inference only; consumed by launch_blend_fast).
+// `fast_records`: write FastRecord instead of EvalRecord (inference of the modes launch_blend_fast supports).
 cudaError_t launch_preprocess(int mode, bool train, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo,
                               const PrimBuffers& prim, FrameStatus* status, cudaStream_t stream, bool fast_records = false);
 
@@ -88,9 +88,10 @@ int effective_k(int mode, int K);
 cudaError_t launch_blend(int mode, int K, bool train, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
                          const uint2* tile_ranges, const BlendOutputs& out, const TrainPixelBuffers& tout, FrameStatus* status, cudaStream_t stream);
 
-// blend_fast.cu: relaxed-precision HYBRID_BLEND inference (RGB only).  `supports` tells whether (mode, K) has a fast kernel.
+// blend_fast.cu: relaxed-precision inference (RGB only) for HYBRID_BLEND, ALPHA_BLEND_FIRST_K and OIT_BLEND.  `supports` tells
+// whether (mode, K) has a fast kernel; these kernels do not depend on the order of a tile's list.
 bool blend_fast_supports(int mode, int K);
-cudaError_t launch_blend_fast(int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
+cudaError_t launch_blend_fast(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
                               float* image, bool to_chw, FrameStatus* status, cudaStream_t stream);
 
 // weights.cu

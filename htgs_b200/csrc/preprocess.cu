@@ -345,8 +345,13 @@ cudaError_t launch_t(const HtgsScene& scene, const HtgsView& view, const FrameGe
 cudaError_t launch_preprocess(int mode, bool train, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo,
                               const PrimBuffers& prim, FrameStatus* status, cudaStream_t stream, bool fast_records) {
     if (fast_records) {
-        if (mode != HTGS_MODE_HYBRID_BLEND || train) return cudaErrorInvalidValue;
-        return launch_t<HTGS_MODE_HYBRID_BLEND, false, true>(scene, view, geo, prim, status, stream);
+        if (train) return cudaErrorInvalidValue;
+        switch (mode) {
+            case HTGS_MODE_HYBRID_BLEND: return launch_t<HTGS_MODE_HYBRID_BLEND, false, true>(scene, view, geo, prim, status, stream);
+            case HTGS_MODE_ALPHA_BLEND_FIRST_K: return launch_t<HTGS_MODE_ALPHA_BLEND_FIRST_K, false, true>(scene, view, geo, prim, status, stream);
+            case HTGS_MODE_OIT_BLEND: return launch_t<HTGS_MODE_OIT_BLEND, false, true>(scene, view, geo, prim, status, stream);
+            default: return cudaErrorInvalidValue;
+        }
     }
     switch (mode) {
 #define HTGS_CASE(M) case M: return train ? launch_t<M, true, false>(scene, view, geo, prim, status, stream) : launch_t<M, false, false>(scene, view, geo, prim, status, stream);

@@ -11,8 +11,7 @@ inputs is stored with every case so that a drifting generator is detected.
 Per case and blend mode the file holds: the `rasterize` image and depth, the tile boxes and
 tile counts of the preprocess, the sorted instance list and tile ranges (parsed from the
 scratch blobs `_C.forward` returns), the training-forward image, the six gradients of
-`diff_rasterize` for an L1 loss against a seeded target, the `update_max_weights` result and, for HYBRID_BLEND,
-the `fast_rasterize` image.
+`diff_rasterize` for an L1 loss against a seeded target, the `update_max_weights` result and the `fast_rasterize` image.
 """
 from __future__ import annotations
 
@@ -70,9 +69,8 @@ def main():
                 img, depth = ref.rasterize(*tensors, st, True, median)
                 out[f"{tag}_image" + ("_median" if median else "")] = img.cpu().numpy()
                 out[f"{tag}_depth" + ("_median" if median else "")] = depth.cpu().numpy()
-            if mode == scenes.HYBRID_BLEND:
-                # the reference's relaxed-precision path (fast-math build, half-precision K-buffer): RGB only
-                out[f"{tag}_fast_image"] = ref.fast_rasterize(*tensors, st, True).cpu().numpy()
+            # the reference's relaxed-precision path (fast-math build; HYBRID keeps a half-precision K-buffer): RGB only
+            out[f"{tag}_fast_image"] = ref.fast_rasterize(*tensors, st, True).cpu().numpy()
             fwd = RC.forward(*tensors, *st.as_tuple())
             torch.cuda.synchronize()
             _, pp, pt, pi, _, n_inst, sel = fwd

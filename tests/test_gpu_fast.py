@@ -5,7 +5,8 @@ benchmark scene it differs from the exact image by 5e-5 on average, by up to 1e-
 fragment flips between core and tail).  The bar here follows that: against the reference's `fast_rasterize` (golden
 vectors and, when built, the live extension) the mean absolute difference must stay below 1e-5, at most 0.02 % of the
 values may differ by more than 1e-3, and none by more than 0.1; against the exact `rasterize` of this library the
-mean must stay below 2e-4.  Modes and K without a dedicated kernel must reproduce the exact image bit for bit."""
+mean must stay below 2e-4.  HYBRID_BLEND, ALPHA_BLEND_FIRST_K (K >= 4) and OIT_BLEND have dedicated kernels; the other
+modes and K must reproduce the exact image bit for bit."""
 import os
 
 import numpy as np
@@ -47,48 +48,47 @@ def exact(mod, scene, view, mode, K, to_chw=True):
     return img
 
 
-def hybrid_golden_cases():
+def golden_cases():
     for name, case in CASES.items():
         for mode, K in case["modes"]:
-            if mode == scenes.HYBRID_BLEND:
-                yield name, K
+            yield name, mode, K
 
 
-@pytest.mark.parametrize("name,K", list(hybrid_golden_cases()))
-def test_against_reference_golden(name, K):
+@pytest.mark.parametrize("name,mode,K", list(golden_cases()))
+def test_against_reference_golden(name, mode, K):
     gold = np.load(os.path.join(GOLDEN, f"{name}.npz"))
-    key = f"m0_k{K}_fast_image"
+    key = f"m{mode}_k{K}_fast_image"
     if key not in gold.files:
-        pytest.skip("golden file predates the fast_rasterize vectors")
+        pytest.skip("golden file predates the fast_rasterize vectors of this mode")
     scene = scenes.tiny_scene(**CASES[name]["kwargs"])
-    got = fast(harness.ours(), scene, scene.views[0], 0, K).cpu().numpy()
+    got = fast(harness.ours(), scene, scene.views[0], mode, K).cpu().numpy()
     assert got.shape == gold[key].shape and got.min() >= 0.0 and got.max() <= 1.0
     check_close(got, gold[key])
 
 
-@pytest.mark.parametrize("K", [4, 8, 16, 32])
+@pytest.mark.parametrize("mode,K", [(0, 4), (0, 8), (0, 16), (0, 32), (1, 4), (1, 16), (1, 32), (3, 1)])
 @pytest.mark.parametrize("to_chw", [True, False])
-def test_against_live_reference(K, to_chw):
+def test_against_live_reference(mode, K, to_chw):
     ref = harness.reference()
     if ref is None:
         pytest.skip("reference extension not built")
-    scene = scenes.tiny_scene(n=20000, size=200, seed=70 + K, sh_degree=2)
+    scene = scenes.tiny_scene(n=20000, size=200, seed=70 + K + 7 * mode, sh_degree=2)
     view = scene.views[0]
-    got = fast(harness.ours(), scene, view, 0, K, to_chw).cpu().numpy()
-    want = fast(ref, scene, view, 0, K, to_chw).cpu().numpy()
+    got = fast(harness.ours(), scene, view, mode, K, to_chw).cpu().numpy()
+    want = fast(ref, scene, view, mode, K, to_chw).cpu().numpy()
     assert got.shape == ((3, view.height, view.width) if to_chw else (view.height, view.width, 3))
     check_close(got, want)
 
 
-@pytest.mark.parametrize("K", [4, 16, 32])
-def test_against_exact_path(K):
-    scene = scenes.tiny_scene(n=12000, size=160, seed=80 + K, sh_degree=1)
+@pytest.mark.parametrize("mode,K", [(0, 4), (0, 16), (0, 32), (1, 8), (3, 1)])
+def test_against_exact_path(mode, K):
+    scene = scenes.tiny_scene(n=12000, size=160, seed=80 + K + mode, sh_degree=1)
     view = scene.views[0]
     ours = harness.ours()
-    check_close(fast(ours, scene, view, 0, K).cpu().numpy(), exact(ours, scene, view, 0, K).cpu().numpy(), mean_tol=2e-4)
+    check_close(fast(ours, scene, view, mode, K).cpu().numpy(), exact(ours, scene, view, mode, K).cpu().numpy(), mean_tol=2e-4)
 
 
-@pytest.mark.parametrize("mode,K", [(0, 1), (0, 2), (1, 8), (2, 1), (3, 1)])
+@pytest.mark.parametrize("mode,K", [(0, 1), (0, 2), (1, 2), (2, 1)])
 def test_modes_without_fast_kernel_are_exact(mode, K):
     scene = scenes.tiny_scene(n=5000, size=96, seed=90 + mode, sh_degree=0)
     view = scene.views[0]
@@ -97,14 +97,14 @@ def test_modes_without_fast_kernel_are_exact(mode, K):
 
 
 def test_benchmark_size_against_live_reference():
-    """Configuration 1 (3 M Gaussians, 1297x840) on two views."""
+    """Configuration 1 (3 M Gaussians, 1297x840): HYBRID on two views, FIRST_K and OIT on one."""
     ref = harness.reference()
     if ref is None:
         pytest.skip("reference extension not built")
     scene = scenes.outdoor_scene(n_views=200)
-    for vi in (0, 100):
-        got = fast(harness.ours(), scene, scene.views[vi], 0, 16).cpu().numpy()
-        want = fast(ref, scene, scene.views[vi], 0, 16).cpu().numpy()
+    for vi, mode in ((0, 0), (100, 0), (50, 1), (50, 3)):
+        got = fast(harness.ours(), scene, scene.views[vi], mode, 16).cpu().numpy()
+        want = fast(ref, scene, scene.views[vi], mode, 16).cpu().numpy()
         check_close(got, want)
 
 
