@@ -207,11 +207,12 @@ int htgs_backward_static(HtgsContext* ctx, const HtgsScene* scene, const HtgsVie
 /*
  * Relaxed-precision forward, RGB only.  Replaces `_C_benchmarking.benchmark` = fast_inference_wrapper
  * (rasterization/include/fast_inference_api.h:7-25, rasterization/src/fast_inference_api.cu:21-162), the reference's
- * fast-math build.  `image` is [3,H,W] (to_chw) or [H,W,3], clamped to [0,1].  HYBRID_BLEND with K rounded to 4, 8, 16
- * or 32 runs a dedicated kernel whose result agrees with the reference's fast path to about 1e-3 per channel (not bit
- * for bit); every other mode or K runs the exact kernels of htgs_render.  Workspace handling as htgs_render.
+ * fast-math build.  `image` is [3,H,W] (to_chw) or [H,W,3], clamped to [0,1].  HYBRID_BLEND and ALPHA_BLEND_FIRST_K with K
+ * rounded to 4, 8, 16 or 32, and OIT_BLEND, run dedicated kernels whose result agrees with the reference's fast path to about
+ * 1e-3 per channel (not bit for bit); GLOBAL_ORDERING and smaller K run the exact kernels of htgs_render.  Workspace handling
+ * as htgs_render.
  *
- * The dedicated kernel does not depend on the order of a tile's list, so by default the lists are built with atomics
+ * The dedicated kernels do not depend on the order of a tile's list, so by default the lists are built with atomics
  * instead of the stable sort: two renders of the same frame can then differ in the last bits (the order of a float
  * sum), never by more than the tolerance above.  htgs_set_fast_deterministic(ctx, 1) selects the ordered binning
  * (bit-reproducible, about 0.25 ms slower per frame at 3 M Gaussians).  No counterpart in the reference.
