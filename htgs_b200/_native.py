@@ -75,6 +75,11 @@ class HtgsGradients(ctypes.Structure):
     ]
 
 
+class HtgsFilterView(ctypes.Structure):
+    _fields_ = [("w2c", ctypes.c_float * 16), ("width", ctypes.c_int32), ("height", ctypes.c_int32), ("focal_x", ctypes.c_float),
+                ("focal_y", ctypes.c_float), ("center_x", ctypes.c_float), ("center_y", ctypes.c_float), ("near_plane", ctypes.c_float)]
+
+
 class HtgsError(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(message)
@@ -130,6 +135,8 @@ def lib():
                                                ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.POINTER(HtgsFrameInfo)]
                 l.htgs_update_3d_filter.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                                     ctypes.c_int32] + [ctypes.c_float] * 7 + [ctypes.c_void_p]
+                l.htgs_update_3d_filter_views.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsFilterView), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p,
+                                                          ctypes.c_int32, ctypes.c_float, ctypes.c_float, ctypes.c_void_p]
                 l.htgs_activate.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int32, ctypes.c_void_p]
                 l.htgs_activate_backward.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int32, ctypes.c_void_p]
                 l.htgs_set_profiling.argtypes = [ctypes.c_void_p, ctypes.c_int]

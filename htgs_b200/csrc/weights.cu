@@ -5,8 +5,12 @@
 //   rasterization/include/alpha_blend_global_ordering/kernels/update_max_weights.cuh:59-
 //   rasterization/include/oit_blend/kernels/update_max_weights.cuh:57-
 // The result is a maximum (atomicMax on the bit pattern of non-negative floats), so it does not depend on the
-// order of evaluation and is bit-identical to the reference's.  This helper is called a few times per training
-// run, not per frame; it uses plain staged loads and the conservative outline only as a per-pixel skip test.
+// order of evaluation and is bit-identical to the reference's.  The kernel has the shape of the blend kernel: a batch
+// of instances is staged in shared memory, lane = Gaussian evaluates the conservative outline at the warp's 32 pixels
+// and warp ballots transpose the result, then every lane walks the bit mask of its own candidates.  HYBRID and OIT
+// need a second walk over the tile's list (every fragment is credited `alpha * tail weight` of its pixel), which has
+// no alpha test of its own: its candidates are those of the outline only when `weight_threshold >= min_alpha`
+// (then alpha * weight >= threshold implies alpha >= min_alpha), otherwise every staged instance.
 #include "kernels.h"
 
 namespace htgs {
@@ -15,6 +19,9 @@ namespace {
 
 template <int MODE> struct WShape {
     static constexpr int tw = ModeTraits<MODE>::tile_w, th = ModeTraits<MODE>::tile_h, threads = tw * th;
+    static constexpr int rows_per_warp = 32 / tw;
+    static constexpr int chunk = 64;                   // candidate masks cover 64 staged instances
+    static constexpr int chunks = threads / chunk;
 };
 
 __device__ __forceinline__ void raise_weight(unsigned int* max_weights, uint32_t primitive_idx, float weight) {
@@ -36,9 +43,12 @@ __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
     __shared__ float s_cc[WS::threads], s_op[WS::threads];
     __shared__ uint32_t s_g[WS::threads];
     const uint32_t tid = threadIdx.x;
+    const uint32_t warp = tid >> 5, lane = tid & 31;
     const uint32_t px_i = blockIdx.x * WS::tw + (tid % WS::tw), py_i = blockIdx.y * WS::th + (tid / WS::tw);
     const bool inside = px_i < width && py_i < height;
     const float pixel_x = __uint2float_rn(px_i), pixel_y = __uint2float_rn(py_i);
+    const float rect_x0 = float(blockIdx.x * WS::tw);
+    const float rect_y0 = float(blockIdx.y * WS::th + warp * WS::rows_per_warp);
     const uint2 range = tile_ranges[blockIdx.y * grid_w + blockIdx.x];
 
     [[maybe_unused]] float kd[kBuffer ? K : 1], ka[kBuffer ? K : 1];
@@ -50,8 +60,11 @@ __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
     float alpha_sum = 0.0f, transmittance = 1.0f;   // HB: tail; OIT / GO: pixel
     bool done = !inside;
     float second_pass_weight = 0.0f;
+    const bool outline_in_second_pass = weight_threshold >= MT::min_alpha;
 
     for (int pass = 0; pass < ((kHybrid || kOit) ? 2 : 1); ++pass) {
+        const bool lane_active = !done && (pass == 0 || second_pass_weight >= weight_threshold);
+        if (pass == 1 && __syncthreads_count(lane_active) == 0) break;   // no pixel of the tile has a tail to credit
         for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += WS::threads) {
             if constexpr (kGlobal) { if (__syncthreads_count(done) == WS::threads) break; } else __syncthreads();
             const uint32_t batch = min(uint32_t(WS::threads), range.y - batch_begin);
@@ -63,77 +76,113 @@ __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
                 s_op[tid] = __ldg(rec + 19);
                 s_c0[tid] = ldg4(reinterpret_cast<const float*>(cull + g));
                 s_cc[tid] = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
+            } else {
+                s_c0[tid] = make_float4(__int_as_float(0x7f800000), 0.0f, 0.0f, 0.0f);   // outline that rejects every pixel
+                s_cc[tid] = 0.0f;
             }
             __syncthreads();
-            if (done || (pass == 1 && !(second_pass_weight >= weight_threshold))) continue;
-            for (uint32_t j = 0; j < batch; ++j) {
-                if (pass == 0) {   // fragments that can pass the alpha test lie inside the outline; the second pass has no alpha test
-                    const float4 c0 = s_c0[j];
-                    const float dx = pixel_x - c0.x, dy = pixel_y - c0.y;
-                    if (!(dx * (c0.z * dx + c0.w * dy) + s_cc[j] * dy * dy <= 1.0f)) continue;
-                }
-                const float4 plane_x_diag = s_T1[j] - s_T4[j] * pixel_x;
-                const float4 plane_y_diag = s_T2[j] - s_T4[j] * pixel_y;
-                const float3 nx = f3(plane_x_diag), ny = f3(plane_y_diag);
-                const float3 m = plane_x_diag.w * ny - nx * plane_y_diag.w;
-                const float3 d = cross(nx, ny);
-                const float numerator_rho2 = dot(m, m);
-                const float denominator = dot(d, d);
-                if (numerator_rho2 > MT::max_cutoff_sq * denominator) continue;
-                const float denominator_rcp = 1.0f / denominator;
-                if (pass == 1) {
-                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                    const float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
-                    const float blending_weight = alpha * second_pass_weight;
-                    if (blending_weight < weight_threshold) continue;
-                    raise_weight(max_weights, s_g[j], blending_weight);
-                    continue;
-                }
-                if constexpr (kFirstK) {
-                    const float3 e = cross(d, m) * denominator_rcp;
-                    const float4 MT3 = s_M3[j];
-                    float depth = dot(f3(MT3), e) + MT3.w;
-                    if (depth >= kd[K - 1]) continue;
-                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                    float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
-                    if (alpha < MT::min_alpha) continue;
-                    uint32_t primitive_idx = s_g[j];
+            #pragma unroll 1
+            for (int chunk = 0; chunk < WS::chunks; ++chunk) {
+                const uint32_t chunk_base = chunk * WS::chunk;
+                if (chunk_base >= batch) break;
+                // ---- candidate masks ---------------------------------------------------------------------
+                uint64_t cand = 0;
+                if (pass == 0 || outline_in_second_pass) {
                     #pragma unroll
-                    for (int k = 0; k < K; ++k)
-                        if (depth < kd[k]) {
-                            const float td = kd[k]; kd[k] = depth; depth = td;
-                            const float ta = ka[k]; ka[k] = alpha; alpha = ta;
-                            const uint32_t ti = ki[k]; ki[k] = primitive_idx; primitive_idx = ti;
+                    for (int half = 0; half < 2; ++half) {
+                        const uint32_t j = chunk_base + half * 32 + lane;
+                        const float4 c0 = s_c0[j];
+                        const float cc = s_cc[j];
+                        const float dx0 = rect_x0 - c0.x, dy0 = rect_y0 - c0.y;
+                        uint32_t mine = 0;
+                        #pragma unroll
+                        for (int r = 0; r < WS::rows_per_warp; ++r) {
+                            const float dy = dy0 + float(r);
+                            const float b2dy = c0.w * dy, cdy2 = cc * dy * dy;
+                            #pragma unroll
+                            for (int i = 0; i < WS::tw; ++i) {
+                                const float dx = dx0 + float(i);
+                                const float q = dx * (c0.z * dx + b2dy) + cdy2;
+                                const uint32_t touched = __ballot_sync(0xffffffffu, q <= 1.0f);
+                                if (int(lane) == r * WS::tw + i) mine = touched;
+                            }
                         }
+                        cand |= uint64_t(mine) << (32 * half);
+                    }
                 } else {
-                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                    float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
-                    if (alpha < MT::min_alpha) continue;
-                    if constexpr (kHybrid) {
+                    const uint32_t in_chunk = min(uint32_t(WS::chunk), batch - chunk_base);
+                    cand = in_chunk >= 64 ? ~0ull : ((1ull << in_chunk) - 1ull);
+                }
+                if (done || (pass == 1 && !(second_pass_weight >= weight_threshold))) cand = 0;
+                // ---- every lane walks its own candidates, in list order ---------------------------------------
+                const uint32_t n_iter = __reduce_max_sync(0xffffffffu, uint32_t(__popcll(cand)));
+                for (uint32_t it = 0; it < n_iter; ++it) {
+                    const bool valid = cand != 0;
+                    const uint32_t j = chunk_base + (valid ? uint32_t(__ffsll((long long)cand) - 1) : 0u);
+                    cand &= cand - 1;
+                    if (!valid || done) continue;
+                    const float4 plane_x_diag = s_T1[j] - s_T4[j] * pixel_x;
+                    const float4 plane_y_diag = s_T2[j] - s_T4[j] * pixel_y;
+                    const float3 nx = f3(plane_x_diag), ny = f3(plane_y_diag);
+                    const float3 m = plane_x_diag.w * ny - nx * plane_y_diag.w;
+                    const float3 d = cross(nx, ny);
+                    const float numerator_rho2 = dot(m, m);
+                    const float denominator = dot(d, d);
+                    if (numerator_rho2 > MT::max_cutoff_sq * denominator) continue;
+                    const float denominator_rcp = 1.0f / denominator;
+                    if (pass == 1) {
+                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                        const float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
+                        const float blending_weight = alpha * second_pass_weight;
+                        if (blending_weight < weight_threshold) continue;
+                        raise_weight(max_weights, s_g[j], blending_weight);
+                        continue;
+                    }
+                    if constexpr (kFirstK) {
                         const float3 e = cross(d, m) * denominator_rcp;
                         const float4 MT3 = s_M3[j];
                         float depth = dot(f3(MT3), e) + MT3.w;
-                        if (depth < kd[K - 1] && alpha >= MT::min_alpha_core) {
-                            uint32_t primitive_idx = s_g[j];
-                            #pragma unroll
-                            for (int k = 0; k < K; ++k)
-                                if (depth < kd[k]) {
-                                    const float td = kd[k]; kd[k] = depth; depth = td;
-                                    const float ta = ka[k]; ka[k] = alpha; alpha = ta;
-                                    const uint32_t ti = ki[k]; ki[k] = primitive_idx; primitive_idx = ti;
-                                }
-                        }
-                        alpha_sum += alpha;
-                        transmittance *= 1.0f - alpha;
-                    } else if constexpr (kGlobal) {
-                        const float blending_weight = transmittance * alpha;
-                        transmittance *= 1.0f - alpha;
-                        if (transmittance < kTransmittanceThreshold) done = true;
-                        if (!(blending_weight < weight_threshold)) raise_weight(max_weights, s_g[j], blending_weight);
-                        if (done) break;
+                        if (depth >= kd[K - 1]) continue;
+                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                        float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
+                        if (alpha < MT::min_alpha) continue;
+                        uint32_t primitive_idx = s_g[j];
+                        #pragma unroll
+                        for (int k = 0; k < K; ++k)
+                            if (depth < kd[k]) {
+                                const float td = kd[k]; kd[k] = depth; depth = td;
+                                const float ta = ka[k]; ka[k] = alpha; alpha = ta;
+                                const uint32_t ti = ki[k]; ki[k] = primitive_idx; primitive_idx = ti;
+                            }
                     } else {
-                        alpha_sum += alpha;
-                        transmittance *= 1.0f - alpha;
+                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                        float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
+                        if (alpha < MT::min_alpha) continue;
+                        if constexpr (kHybrid) {
+                            const float3 e = cross(d, m) * denominator_rcp;
+                            const float4 MT3 = s_M3[j];
+                            float depth = dot(f3(MT3), e) + MT3.w;
+                            if (depth < kd[K - 1] && alpha >= MT::min_alpha_core) {
+                                uint32_t primitive_idx = s_g[j];
+                                #pragma unroll
+                                for (int k = 0; k < K; ++k)
+                                    if (depth < kd[k]) {
+                                        const float td = kd[k]; kd[k] = depth; depth = td;
+                                        const float ta = ka[k]; ka[k] = alpha; alpha = ta;
+                                        const uint32_t ti = ki[k]; ki[k] = primitive_idx; primitive_idx = ti;
+                                    }
+                            }
+                            alpha_sum += alpha;
+                            transmittance *= 1.0f - alpha;
+                        } else if constexpr (kGlobal) {
+                            const float blending_weight = transmittance * alpha;
+                            transmittance *= 1.0f - alpha;
+                            if (transmittance < kTransmittanceThreshold) done = true;
+                            if (!(blending_weight < weight_threshold)) raise_weight(max_weights, s_g[j], blending_weight);
+                        } else {
+                            alpha_sum += alpha;
+                            transmittance *= 1.0f - alpha;
+                        }
                     }
                 }
             }

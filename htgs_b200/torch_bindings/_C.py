@@ -214,3 +214,41 @@ def update_3d_filter_cuda(positions, w2c, filter_3d, visibility_mask, width, hei
                                                  int(height), float(focal_x), float(focal_y), float(center_x), float(center_y), float(near_plane),
                                                  float(clipping_tolerance), float(distance2filter), torch.cuda.current_stream(device).cuda_stream)
     _native.check(rc)
+
+
+def update_3d_filter_views_cuda(positions, w2cs, filter_3d, visibility_mask, widths, heights, focal_xs, focal_ys, center_xs, center_ys, near_planes,
+                                clipping_tolerance, distance2filter):
+    """All views of a dataset in one pass over the points (`htgs_update_3d_filter_views`): equal, bit for bit, to
+    `update_3d_filter_cuda` called once per view in order.  `w2cs` is [V,4,4] (any device: the matrices travel as kernel
+    arguments); the per-view camera parameters are sequences of length V."""
+    import numpy as np
+    device = positions.device
+    if device.type != "cuda":
+        raise ValueError("htgs_b200: tensors must live on a CUDA device")
+    n = positions.shape[0]
+    if positions.dtype != torch.float32 or filter_3d.dtype != torch.float32 or visibility_mask.dtype != torch.bool:
+        raise TypeError("positions, filter_3d must be float32 and visibility_mask bool")
+    if tuple(positions.shape) != (n, 3) or filter_3d.numel() != n or visibility_mask.numel() != n:
+        raise ValueError("expected positions [N,3], filter_3d [N,1], visibility_mask [N]")
+    if not (filter_3d.is_contiguous() and visibility_mask.is_contiguous()):
+        raise ValueError("filter_3d and visibility_mask are updated in place and must be contiguous")
+    mats = (w2cs.detach().cpu().numpy() if isinstance(w2cs, torch.Tensor) else np.asarray(w2cs)).astype(np.float32).reshape(-1, 16)
+    n_views = mats.shape[0]
+    per_view = [widths, heights, focal_xs, focal_ys, center_xs, center_ys, near_planes]
+    if any(len(x) != n_views for x in per_view):
+        raise ValueError("one camera parameter per view expected")
+    # the host array of HtgsFilterView (16 floats, 2 ints, 5 floats), filled column-wise
+    packed = np.zeros(max(n_views, 1), dtype=np.dtype([("w2c", np.float32, 16), ("width", np.int32), ("height", np.int32), ("focal_x", np.float32),
+                                                       ("focal_y", np.float32), ("center_x", np.float32), ("center_y", np.float32),
+                                                       ("near_plane", np.float32)], align=False))
+    assert packed.dtype.itemsize == ctypes.sizeof(_native.HtgsFilterView)
+    if n_views:
+        packed["w2c"][:n_views] = mats
+        for name, values in zip(("width", "height", "focal_x", "focal_y", "center_x", "center_y", "near_plane"), per_view):
+            packed[name][:n_views] = np.asarray(values)
+    views = packed.ctypes.data_as(ctypes.POINTER(_native.HtgsFilterView))
+    positions = positions.contiguous()
+    with torch.cuda.device(device):
+        rc = _native.lib().htgs_update_3d_filter_views(positions.data_ptr(), views, n_views, filter_3d.data_ptr(), visibility_mask.data_ptr(), n,
+                                                       float(clipping_tolerance), float(distance2filter), torch.cuda.current_stream(device).cuda_stream)
+    _native.check(rc)

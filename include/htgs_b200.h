@@ -240,6 +240,20 @@ int htgs_update_3d_filter(const float* positions, const float* w2c, float* filte
                           float clipping_tolerance, float distance2filter, void* stream);
 
 /*
+ * The same update for several views in one pass over the points (no counterpart in the reference, whose caller loops over
+ * the views, Model.py:126-145): equal, bit for bit, to calling htgs_update_3d_filter once per view in order, but the
+ * positions are read once per 48 views instead of once per view.  `views` is a HOST array (camera parameters travel as
+ * kernel arguments); every other pointer is a device pointer.  Stream-ordered, no host synchronisation, no allocation.
+ */
+typedef struct HtgsFilterView {
+    float w2c[16];                 /* world -> view, row-major */
+    int32_t width, height;
+    float focal_x, focal_y, center_x, center_y, near_plane;
+} HtgsFilterView;
+int htgs_update_3d_filter_views(const float* positions, const HtgsFilterView* views, int32_t n_views, float* filter_3d, uint8_t* visibility_mask,
+                                int32_t n_points, float clipping_tolerance, float distance2filter, void* stream);
+
+/*
  * Fused parameter activations of the Gaussian model, forward and backward (one pass over N).  Replaces the element-wise
  * PyTorch operations the reference's model applies before every rasterizer call (Model.py:45-49 exp / normalize / expit,
  * Model.py:82-100 the 3D-filter adjustment):

@@ -47,3 +47,40 @@ def test_bit_exact_against_reference_extension():
     harness.ours().update_3d_filter(*ours, *ARGS.values())
     ref.update_3d_filter(*theirs, *ARGS.values())
     assert torch.equal(ours[2], theirs[2]) and torch.equal(ours[3], theirs[3])
+
+
+@pytest.mark.parametrize("n_views", [1, 7, 48, 113])
+def test_all_views_in_one_pass_equals_the_loop(n_views):
+    """`update_3d_filter_views` must equal, bit for bit, one `update_3d_filter` call per view in order (and, when the reference is
+    built, the reference's loop)."""
+    import torch
+    tb = harness.ours()
+    rng = np.random.default_rng(40 + n_views)
+    n = 150_000
+    positions = (rng.standard_normal((n, 3)) * 3.0).astype(np.float32)
+    w2cs = np.stack([scenes.look_at(p).astype(np.float32) for p in scenes.orbit_positions(n_views, 4.0, 1.5)]) if hasattr(scenes, "orbit_positions") else \
+        np.stack([scenes.look_at((4.0 * np.cos(a), 1.5 + 0.3 * np.sin(3 * a), 4.0 * np.sin(a))).astype(np.float32) for a in np.linspace(0, 2 * np.pi, n_views, endpoint=False)])
+    widths = [1297 - 8 * (v % 5) for v in range(n_views)]
+    heights = [840 + 4 * (v % 3) for v in range(n_views)]
+    fxs = [1150.0 + v for v in range(n_views)]
+    fys = [1100.0 - v for v in range(n_views)]
+    cxs = [640.0 + 0.5 * v for v in range(n_views)]
+    cys = [425.0 - 0.25 * v for v in range(n_views)]
+    nears = [0.2 + 0.01 * (v % 4) for v in range(n_views)]
+    start_f = np.full((n, 1), np.finfo(np.float32).max, np.float32)
+    start_f[::5] = 0.002       # a few points start below what some views would give
+    pos_t = torch.from_numpy(positions).cuda()
+    loop_f, loop_m = torch.from_numpy(start_f).cuda(), torch.zeros(n, dtype=torch.bool, device="cuda")
+    for v in range(n_views):
+        tb.update_3d_filter(pos_t, torch.from_numpy(w2cs[v]).cuda(), loop_f, loop_m, widths[v], heights[v], fxs[v], fys[v], cxs[v], cys[v], nears[v], 0.15, 0.0007)
+    one_f, one_m = torch.from_numpy(start_f).cuda(), torch.zeros(n, dtype=torch.bool, device="cuda")
+    tb.update_3d_filter_views(pos_t, torch.from_numpy(w2cs), one_f, one_m, widths, heights, fxs, fys, cxs, cys, nears, 0.15, 0.0007)
+    torch.cuda.synchronize()
+    assert torch.equal(one_f, loop_f) and torch.equal(one_m, loop_m)
+    assert one_m.any() and not one_m.all()
+    ref = harness.reference()
+    if ref is not None:
+        ref_f, ref_m = torch.from_numpy(start_f).cuda(), torch.zeros(n, dtype=torch.bool, device="cuda")
+        for v in range(n_views):
+            ref.update_3d_filter(pos_t, torch.from_numpy(w2cs[v]).cuda(), ref_f, ref_m, widths[v], heights[v], fxs[v], fys[v], cxs[v], cys[v], nears[v], 0.15, 0.0007)
+        assert torch.equal(one_f, ref_f) and torch.equal(one_m, ref_m.reshape(-1))
