@@ -8,6 +8,9 @@
 //   1. count:  every (Gaussian, tile) instance adds 1 to its tile's counter,
 //   2. scan:   exclusive prefix over the tiles -> begin of every tile's list,
 //   3. place:  every instance takes the next free position of its tile with an atomic and stores the Gaussian index.
+// A (Gaussian, tile) instance of the Gaussian's tile box is dropped when the conservative outline of the Gaussian (the
+// ellipse the blend kernels test per pixel) does not reach the tile's 8 x 8 pixel square at all: the box of a slanted or
+// round outline has empty corners, and such an instance could only be staged and rejected pixel by pixel.
 // Passes 1 and 3 walk the list of VISIBLE Gaussians (about one in six), 256 per block iteration, and generate the
 // block's instances cooperatively (slot -> owner by binary search over the in-block prefix, as the ordered emission
 // kernel does).  The order inside a tile's list is the order in which the atomics arrive: two runs of the same frame
@@ -29,16 +32,36 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan_u32(uint32_t v) {
     return v;
 }
 
+// Smallest value of the outline form q = a x^2 + b2 x y + c y^2 (x, y relative to the outline's centre) over the square
+// [x0, x0 + 7] x [y0, y0 + 7]: zero if the centre lies inside, else attained on one of the four edges, where q is a
+// parabola in the free coordinate.  "Accept everything" records (a = b2 = c = 0) give 0, "reject everything" records
+// (centre at infinity) give NaN, which compares false.
+// `slopes` = (-b2 / (2 c), -b2 / (2 a)): where the parabola along a vertical / horizontal edge has its vertex, per unit of
+// the fixed coordinate (computed once per Gaussian).
+__device__ __forceinline__ bool outline_reaches_tile(const float4& c0, float cc, float2 slopes, float tile_x0, float tile_y0) {
+    const float a = c0.z, b2 = c0.w;
+    const float x0 = tile_x0 - c0.x, x1 = x0 + 7.0f, y0 = tile_y0 - c0.y, y1 = y0 + 7.0f;
+    if (x0 <= 0.0f && x1 >= 0.0f && y0 <= 0.0f && y1 >= 0.0f) return true;
+    auto q = [&](float x, float y) { return x * (a * x + b2 * y) + cc * y * y; };
+    auto along_y = [&](float x) { return q(x, fminf(fmaxf(slopes.x * x, y0), y1)); };   // edge x = const
+    auto along_x = [&](float y) { return q(fminf(fmaxf(slopes.y * y, x0), x1), y); };   // edge y = const
+    const float q_min = fminf(fminf(along_y(x0), along_y(x1)), fminf(along_x(y0), along_x(y1)));
+    return q_min <= 1.001f;
+}
+
 // PLACE = false: pass 1 (ranges[tile].y counts the tile's instances).  PLACE = true: pass 3 (ranges[tile].y is the
 // tile's cursor, it starts at the tile's begin and ends at its end).
 template <bool PLACE>
 __global__ void __launch_bounds__(kBinBlock) bin_visible_kernel(
     const uint32_t* __restrict__ visible_list, const uint32_t* __restrict__ n_touched, const ushort4* __restrict__ bounds,
-    uint2* __restrict__ ranges, uint32_t* __restrict__ prims_sorted, const FrameStatus* __restrict__ status, uint32_t grid_w, uint32_t capacity)
+    const CullRecord* __restrict__ cull, uint2* __restrict__ ranges, uint32_t* __restrict__ prims_sorted, const FrameStatus* __restrict__ status, uint32_t grid_w, uint32_t capacity)
 {
     __shared__ uint32_t excl[kBinBlock + 1];
     __shared__ ushort4 box[kBinBlock];
     __shared__ uint32_t owner[kBinBlock];
+    __shared__ float4 outline4[kBinBlock];
+    __shared__ float outline_c[kBinBlock];
+    __shared__ float2 outline_slopes[kBinBlock];
     __shared__ uint32_t warp_tot[kBinBlock / 32];
     if (status->overflow) return;   // the frame is re-run with larger buffers
     const uint32_t n_visible = status->n_visible;
@@ -50,6 +73,11 @@ __global__ void __launch_bounds__(kBinBlock) bin_visible_kernel(
             cnt = n_touched[g];
             box[threadIdx.x] = bounds[g];
             owner[threadIdx.x] = g;
+            outline4[threadIdx.x] = ldg4(reinterpret_cast<const float*>(cull + g));
+            const float c_yy = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
+            outline_c[threadIdx.x] = c_yy;
+            // a = b2 = c = 0 ("accept everything") gives 0 / 0 = NaN, which the clamps below turn into an edge end point
+            outline_slopes[threadIdx.x] = make_float2(-0.5f * outline4[threadIdx.x].w / c_yy, -0.5f * outline4[threadIdx.x].w / outline4[threadIdx.x].z);
         }
         const uint32_t inc = warp_inclusive_scan_u32(cnt);
         if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = inc;
@@ -76,7 +104,9 @@ __global__ void __launch_bounds__(kBinBlock) bin_visible_kernel(
             const uint32_t w = uint32_t(b.y) - uint32_t(b.x);
             const uint32_t ly = local / w;
             const uint32_t lx = local - ly * w;
-            const uint32_t tile = (uint32_t(b.z) + ly) * grid_w + uint32_t(b.x) + lx;
+            const uint32_t tile_xi = uint32_t(b.x) + lx, tile_yi = uint32_t(b.z) + ly;
+            if (!outline_reaches_tile(outline4[lo], outline_c[lo], outline_slopes[lo], float(tile_xi * 8), float(tile_yi * 8))) continue;
+            const uint32_t tile = tile_yi * grid_w + tile_xi;
             if constexpr (PLACE) {
                 const uint32_t pos = atomicAdd(&ranges[tile].y, 1u);
                 if (pos < capacity) prims_sorted[pos] = owner[lo];
@@ -126,12 +156,12 @@ cudaError_t launch_bin_unordered(const HtgsScene& scene, const FrameGeometry& ge
     }
     const uint32_t max_blocks = (uint32_t(scene.n_primitives) + kBinBlock - 1) / kBinBlock;
     const uint32_t grid = min(max_blocks, uint32_t(sm_count) * 8u);
-    bin_visible_kernel<false><<<grid, kBinBlock, 0, stream>>>(prim.visible_list, prim.n_touched, prim.bounds, tile_ranges, prims_sorted, status,
+    bin_visible_kernel<false><<<grid, kBinBlock, 0, stream>>>(prim.visible_list, prim.n_touched, prim.bounds, prim.cull, tile_ranges, prims_sorted, status,
                                                               uint32_t(geo.grid_w), capacity);
     if (ev) cudaEventRecord(ev[0], stream);
     scan_tiles_kernel<<<1, 1024, 0, stream>>>(tile_ranges, uint32_t(geo.n_tiles));
     if (ev) cudaEventRecord(ev[1], stream);
-    bin_visible_kernel<true><<<grid, kBinBlock, 0, stream>>>(prim.visible_list, prim.n_touched, prim.bounds, tile_ranges, prims_sorted, status,
+    bin_visible_kernel<true><<<grid, kBinBlock, 0, stream>>>(prim.visible_list, prim.n_touched, prim.bounds, prim.cull, tile_ranges, prims_sorted, status,
                                                              uint32_t(geo.grid_w), capacity);
     if (ev) cudaEventRecord(ev[2], stream);
     if (launches) *launches += 3;

@@ -118,8 +118,8 @@ def test_empty_and_offscreen():
 
 
 def test_unordered_binning_builds_the_same_tile_lists():
-    """The default binning of the fast path (counting sort with atomics) must produce, per tile, the same multiset of
-    Gaussians as the stable sort of the exact path; only the order inside a tile's list is free."""
+    """The default binning of the fast path (counting sort with atomics) must produce, per tile, the Gaussians of the exact
+    path's stable sort in any order, minus only those whose conservative outline reaches none of the tile's 64 pixels."""
     from htgs_b200.torch_bindings import _C
     scene = scenes.tiny_scene(n=30000, size=256, seed=97, sh_degree=1)
     view = scene.views[0]
@@ -128,13 +128,27 @@ def test_unordered_binning_builds_the_same_tile_lists():
     n_inst = _C.last_frame_info.n_instances
     want = harness.our_intermediates(0, scene.n, n_inst)
     fast(ours, scene, view, 0, 16)
-    assert _C.last_frame_info.n_instances == n_inst
+    assert _C.last_frame_info.n_instances == n_inst          # the count of the tile boxes (an upper bound on this path)
     got = harness.our_intermediates(0, scene.n, n_inst)
-    assert np.array_equal(got["ranges"], want["ranges"])
-    assert not np.array_equal(got["prims_sorted"], want["prims_sorted"]) or n_inst < 64   # the order is (almost surely) different
+    cull = got["cull"]                                       # cx, cy, a, b2, c per Gaussian
+    ys, xs = np.meshgrid(np.arange(8, dtype=np.float64), np.arange(8, dtype=np.float64), indexing="ij")
+    n_dropped = n_kept = 0
+    assert got["ranges"][-1, 1] <= n_inst
     for t in np.nonzero(want["ranges"][:, 1] > want["ranges"][:, 0])[0]:
-        b, e = want["ranges"][t]
-        assert np.array_equal(np.sort(got["prims_sorted"][b:e]), want["prims_sorted"][b:e]), f"tile {t}"
+        wb, we = want["ranges"][t]
+        gb, ge = got["ranges"][t]
+        w_set, g_list = want["prims_sorted"][wb:we], got["prims_sorted"][gb:ge]
+        assert len(np.unique(g_list)) == len(g_list) and np.isin(g_list, w_set).all(), f"tile {t}"
+        dropped = np.setdiff1d(w_set, g_list)
+        n_dropped += len(dropped); n_kept += len(g_list)
+        if len(dropped):
+            tx, ty = (t % got["grid_w"]) * 8, (t // got["grid_w"]) * 8
+            c = cull[dropped].astype(np.float64)
+            dx = (tx + xs)[None] - c[:, 0, None, None]
+            dy = (ty + ys)[None] - c[:, 1, None, None]
+            q = c[:, 2, None, None] * dx * dx + c[:, 3, None, None] * dx * dy + c[:, 4, None, None] * dy * dy
+            assert not (q <= 1.0).any(), f"tile {t}: a dropped Gaussian has a candidate pixel"
+    assert n_kept > 0 and n_dropped > 0
 
 
 def test_deterministic_switch():
