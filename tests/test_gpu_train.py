@@ -100,3 +100,30 @@ def test_backward_twice_is_deterministic_enough_and_culled_gradients_are_zero():
     for a, b in zip(g1, g2):
         assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-12)   # float atomics reorder sums
         assert not a[:100].any(), "culled Gaussians must get exactly zero gradient"
+
+
+def _draw_training_case(seed):
+    rng = np.random.default_rng(3000 + seed)
+    mode = int(rng.integers(0, 4))
+    K = int(rng.choice([1, 2, 4, 8, 16, 32])) if mode < 2 else 1
+    return dict(mode=mode, K=K, n=int(rng.choice([40, 700, 5000])), size=int(rng.choice([24, 75, 160])), sh_degree=int(rng.integers(0, 4)),
+                rows=int(rng.choice([0, 2, 3])), distance_scaling=bool(rng.integers(0, 2)))
+
+
+@pytest.mark.parametrize("seed", list(range(16)))
+def test_random_training_cases_against_reference_extension(seed):
+    """Seeded sweep over mode, K, scene size, image size, SH degree and the densification options."""
+    import torch
+    ref = harness.reference()
+    if ref is None:
+        pytest.skip("reference extension not built under baseline/_ref")
+    c = _draw_training_case(seed)
+    scene = scenes.tiny_scene(n=c["n"], size=c["size"], seed=400 + seed, sh_degree=c["sh_degree"])
+    view = scene.views[0]
+    image, grads, dens = run_training_step(harness.ours(), scene, view, c["mode"], c["K"], c["rows"], c["distance_scaling"])
+    r_image, r_grads, r_dens = run_training_step(ref, scene, view, c["mode"], c["K"], c["rows"], c["distance_scaling"])
+    assert (image - r_image).abs().max().item() <= 1e-5, c
+    assert_grads_close(grads, r_grads, f"case {c}")
+    if c["rows"]:
+        scale = r_dens.abs().max().item()
+        assert (dens - r_dens).abs().max().item() <= 1e-3 * max(scale, 1e-12), c
