@@ -341,7 +341,7 @@ def main():
     lanes = [Lane(own_stream=n_lanes > 1) for _ in range(n_lanes)]
     launches = [0]
 
-    def timed(kind, steps, warmup, sample_clocks=False, n_lanes=n_lanes):
+    def timed(kind, steps, warmup, sample_clocks=False, n_lanes=n_lanes, frame_marks=None):
         import threading
         timed_views = [vi for s in range(warmup, warmup + steps) for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views)]
         warm_views = [vi for s in range(warmup) for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views)]
@@ -396,10 +396,17 @@ def main():
             lane.launches = 0
             t0 = time.time()
             e0.record()
+            marks = []
             for vi in timed_views:
                 fn(vi)
+                if frame_marks is not None:
+                    marks.append(torch.cuda.Event(enable_timing=True))
+                    marks[-1].record()
             main_stream.wait_stream(lane.copy_stream)   # outstanding copies back belong to the timed region
             e1.record()
+            if frame_marks is not None:
+                torch.cuda.synchronize()
+                frame_marks.extend(a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks))
         else:
             threads = [threading.Thread(target=lane_body, args=(k,)) for k in range(n_lanes)]
             for th in threads:
@@ -430,7 +437,8 @@ def main():
         ms = parallel.max_over_ranks(e0.elapsed_time(e1), device)
         return ms, clocks
 
-    ms_total, clocks = timed("resident", args.steps, args.warmup, sample_clocks=True)
+    ref_frames = [] if ref_mod is not None else None   # per-frame times of the reference arm (it runs one frame at a time anyway)
+    ms_total, clocks = timed("resident", args.steps, args.warmup, sample_clocks=True, frame_marks=ref_frames)
     frames_total = args.steps * args.views_per_step * world
     value = frames_total / (ms_total / 1000.0)
     timed_launches = launches[0] * world
@@ -453,11 +461,16 @@ def main():
 
     if ref_mod is None and n_lanes > 1:
         # the same job with one frame in flight (one host thread, one stream), for comparison
-        ms_1, _ = timed("resident", args.steps, args.warmup, n_lanes=1)
+        per_frame = []
+        ms_1, _ = timed("resident", args.steps, args.warmup, n_lanes=1, frame_marks=per_frame)
         ms_1e, _ = timed("e2e", args.steps, args.warmup, n_lanes=1)
-        line["one_frame_in_flight"] = {"value": frames_total / (ms_1 / 1000.0), "e2e": frames_total / (ms_1e / 1000.0), "unit": "frames/s"}
+        line["one_frame_in_flight"] = {"value": frames_total / (ms_1 / 1000.0), "e2e": frames_total / (ms_1e / 1000.0), "unit": "frames/s",
+                                       "frame_ms": {"p10": float(np.percentile(per_frame, 10)), "p50": float(np.percentile(per_frame, 50)),
+                                                    "p90": float(np.percentile(per_frame, 90)), "frames": len(per_frame)}}
 
     if ref_mod is not None:
+        line["frame_ms"] = {"p10": float(np.percentile(ref_frames, 10)), "p50": float(np.percentile(ref_frames, 50)),
+                            "p90": float(np.percentile(ref_frames, 90)), "frames": len(ref_frames)}
         line.update({"impl": "reference", "reference_kind": "cuda-extension (unmodified HTGSCudaBackend built for sm_100a under baseline/_ref)",
                      "gpu_launches": 0,
                      "cpu_baseline": {"value": None, "unit": "frames/s", "cores": 0, "kind": "reference",
