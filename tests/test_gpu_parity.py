@@ -208,3 +208,36 @@ def test_bit_exact_against_reference_extension(mode, K):
             rimg, rdepth = ref.rasterize(*tensors, harness.settings_for(ref, scene, view, mode, K), True, median)
             assert torch.equal(img, rimg), f"max diff {(img - rimg).abs().max().item():.3e}"
             assert torch.equal(depth, rdepth), f"max depth diff {(depth - rdepth).abs().max().item():.3e}"
+
+
+@pytest.mark.parametrize("mode,K,width,height", [(0, 32, 3840, 2160), (3, 1, 3840, 2160), (2, 1, 3000, 2400)])
+def test_large_images_use_wider_sort_keys(mode, K, width, height):
+    """More than 65 536 tiles (4K images with 8x8 tiles): 32-bit tile keys, 17 bits in two radix passes; GLOBAL_ORDERING with
+    16x16 tiles sorts 47-bit (tile, depth) keys in six.  Lists, images and depth must still equal the reference's bit for bit."""
+    import torch
+    from htgs_b200.torch_bindings import _C
+    ref = harness.reference()
+    if ref is None:
+        pytest.skip("reference extension not built under baseline/_ref")
+    scene = scenes.outdoor_scene(n=150_000, n_views=2, seed=33, width=width, height=height, focal=0.9 * width)
+    view = scene.views[1]
+    tensors = harness.scene_tensors(scene)
+    img, depth = harness.ours().rasterize(*tensors, harness.settings_for(harness.ours(), scene, view, mode, K), True, False)
+    info = _C.last_frame_info
+    n_tiles_8 = ((width + 7) // 8) * ((height + 7) // 8)
+    assert info.key_bytes == (8 if mode == 2 else (4 if n_tiles_8 > 65536 else 2))
+    rimg, rdepth = ref.rasterize(*tensors, harness.settings_for(ref, scene, view, mode, K), True, False)
+    assert torch.equal(img, rimg) and torch.equal(depth, rdepth)
+    # the sorted lists against the reference's scratch blobs
+    from HTGSCudaBackend import _C as RC
+    fwd = RC.forward(*tensors, *harness.settings_for(ref, scene, view, mode, K).as_tuple())
+    torch.cuda.synchronize()
+    _, pp, pt, pi, _, n_inst, sel = fwd
+    assert n_inst == info.n_instances
+    tw = 16 if mode == 2 else 8
+    n_tiles = ((width + tw - 1) // tw) * ((height + tw - 1) // tw)
+    rinst = harness.parse_ref_per_instance(pi.cpu().numpy(), n_inst, harness.sort_key_bytes(mode, n_tiles), sel)
+    inter = harness.our_intermediates(0, scene.n, n_inst)
+    assert np.array_equal(inter["prims_sorted"], rinst["prims_sorted"])
+    assert np.array_equal(inter["keys_sorted"].astype(np.uint64), rinst["keys_sorted"].astype(np.uint64))
+    assert np.array_equal(inter["ranges"], harness.parse_ref_per_tile(pt.cpu().numpy(), n_tiles))
