@@ -114,13 +114,16 @@ __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
                     cand = in_chunk >= 64 ? ~0ull : ((1ull << in_chunk) - 1ull);
                 }
                 if (done || (pass == 1 && !(second_pass_weight >= weight_threshold))) cand = 0;
-                // ---- every lane walks its own candidates, in list order ---------------------------------------
+                // ---- every lane walks its own candidates, in list order, two per trip: the two evaluations (divide, expf,
+                // depth) are independent instruction streams, the state updates follow in order ----------------------
                 const uint32_t n_iter = __reduce_max_sync(0xffffffffu, uint32_t(__popcll(cand)));
-                for (uint32_t it = 0; it < n_iter; ++it) {
-                    const bool valid = cand != 0;
+                auto pop_candidate = [&](bool& valid) -> uint32_t {
+                    valid = cand != 0;
                     const uint32_t j = chunk_base + (valid ? uint32_t(__ffsll((long long)cand) - 1) : 0u);
                     cand &= cand - 1;
-                    if (!valid || done) continue;
+                    return j;
+                };
+                auto evaluate = [&](bool valid, uint32_t j, float& alpha, float& depth) -> bool {
                     const float4 plane_x_diag = s_T1[j] - s_T4[j] * pixel_x;
                     const float4 plane_y_diag = s_T2[j] - s_T4[j] * pixel_y;
                     const float3 nx = f3(plane_x_diag), ny = f3(plane_y_diag);
@@ -128,24 +131,28 @@ __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
                     const float3 d = cross(nx, ny);
                     const float numerator_rho2 = dot(m, m);
                     const float denominator = dot(d, d);
-                    if (numerator_rho2 > MT::max_cutoff_sq * denominator) continue;
+                    const bool inside_cutoff = !(numerator_rho2 > MT::max_cutoff_sq * denominator);
                     const float denominator_rcp = 1.0f / denominator;
-                    if (pass == 1) {
-                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                        const float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
-                        const float blending_weight = alpha * second_pass_weight;
-                        if (blending_weight < weight_threshold) continue;
-                        raise_weight(max_weights, s_g[j], blending_weight);
-                        continue;
-                    }
-                    if constexpr (kFirstK) {
+                    const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
+                    alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
+                    if constexpr (kBuffer) {
                         const float3 e = cross(d, m) * denominator_rcp;
                         const float4 MT3 = s_M3[j];
-                        float depth = dot(f3(MT3), e) + MT3.w;
-                        if (depth >= kd[K - 1]) continue;
-                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                        float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
-                        if (alpha < MT::min_alpha) continue;
+                        depth = dot(f3(MT3), e) + MT3.w;
+                    } else {
+                        depth = 0.0f;
+                    }
+                    return valid && inside_cutoff;
+                };
+                auto commit = [&](uint32_t j, float alpha, float depth) {
+                    if (done) return;
+                    if (pass == 1) {   // no alpha test in the second walk
+                        const float blending_weight = alpha * second_pass_weight;
+                        if (!(blending_weight < weight_threshold)) raise_weight(max_weights, s_g[j], blending_weight);
+                        return;
+                    }
+                    if constexpr (kFirstK) {
+                        if (depth >= kd[K - 1] || alpha < MT::min_alpha) return;
                         uint32_t primitive_idx = s_g[j];
                         #pragma unroll
                         for (int k = 0; k < K; ++k)
@@ -155,13 +162,8 @@ __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
                                 const uint32_t ti = ki[k]; ki[k] = primitive_idx; primitive_idx = ti;
                             }
                     } else {
-                        const float G = expf(-0.5f * numerator_rho2 * denominator_rcp);
-                        float alpha = fminf(s_op[j] * G, kMaxFragmentAlpha);
-                        if (alpha < MT::min_alpha) continue;
+                        if (alpha < MT::min_alpha) return;
                         if constexpr (kHybrid) {
-                            const float3 e = cross(d, m) * denominator_rcp;
-                            const float4 MT3 = s_M3[j];
-                            float depth = dot(f3(MT3), e) + MT3.w;
                             if (depth < kd[K - 1] && alpha >= MT::min_alpha_core) {
                                 uint32_t primitive_idx = s_g[j];
                                 #pragma unroll
@@ -184,6 +186,16 @@ __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
                             transmittance *= 1.0f - alpha;
                         }
                     }
+                };
+                for (uint32_t it = 0; it < n_iter; it += 2) {
+                    bool v0, v1;
+                    const uint32_t j0 = pop_candidate(v0);
+                    const uint32_t j1 = pop_candidate(v1);
+                    float alpha0, alpha1, depth0, depth1;
+                    const bool ok0 = evaluate(v0, j0, alpha0, depth0);
+                    const bool ok1 = evaluate(v1, j1, alpha1, depth1);
+                    if (ok0) commit(j0, alpha0, depth0);
+                    if (ok1) commit(j1, alpha1, depth1);
                 }
             }
         }
