@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                     if constexpr (STATS) ++stat_accepted;
                     if (HTGS_EXPERIMENT != 1 && depth < kd[K - 1] && frag.w >= MT::min_alpha_core) {
                         pool4[free_slot * TS::threads + tid] = frag;
-                        if constexpr (TRAIN) pool_idx[free_slot * TS::threads + tid] = s_prim[j];
+                        if constexpr (TRAIN) pool_idx[free_slot * TS::threads + tid] = batch_begin - range.x + j;   // position in the tile's list: what the backward pass looks up
                         free_slot = slot_index(kbuffer_insert<K>(kd, ks, depth, slot_t(free_slot)));   // the entry that fell out: a real fragment or an empty one
                         frag = pool4[free_slot * TS::threads + tid];
                     }
@@ -355,7 +355,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                     if constexpr (kFirstK) {
                         if (depth >= kd[K - 1]) return;
                         if constexpr (STATS) ++stat_accepted;
-                        pool2[free_slot * TS::threads + tid] = make_float2(alpha, __uint_as_float(s_prim[j]));
+                        pool2[free_slot * TS::threads + tid] = make_float2(alpha, __uint_as_float(TRAIN ? batch_begin - range.x + j : s_prim[j]));
                         free_slot = slot_index(kbuffer_insert<K>(kd, ks, depth, slot_t(free_slot)));
                     } else if constexpr (kGlobal) {
                         if (done) return;
@@ -465,10 +465,11 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                 rgbs_core[k] = make_float3(0.0f, 0.0f, 0.0f);
                 if (!stop && t >= kTransmittanceThreshold) {
                     const float2 cell = pool2[slot_index(ks[k]) * TS::threads + tid];
-                    const uint32_t primitive_idx = __float_as_uint(cell.y);
-                    if (primitive_idx == 0xffffffffu) stop = true;
+                    const uint32_t position = __float_as_uint(cell.y);       // in the tile's list (training stores positions)
+                    if (position == 0xffffffffu) stop = true;
                     else {
                         const float alpha = cell.x;
+                        const uint32_t primitive_idx = __ldg(prims_sorted + range.x + position);
                         const float3 rgb = f3(ldg4(reinterpret_cast<const float*>(eval + primitive_idx) + 16));
                         rgbs_core[k] = rgb;
                         const float blending_weight = t * alpha;

@@ -78,7 +78,7 @@ struct BlendOutputs {
 // per-pixel buffers the training forward leaves for the backward pass; pixel slots are tile-major
 // (slot = tile * pixels_per_tile + pixel_in_tile) and every array is plane-major over `padded_pixels` slots
 struct TrainPixelBuffers {
-    uint32_t* idx_core;      // [K][padded_pixels] Gaussian index per core entry, 0xffffffff = none (HYBRID, FIRST_K)
+    uint32_t* idx_core;      // [K][padded_pixels] per core entry the position of its Gaussian in the tile's sorted list, 0xffffffff = none (HYBRID, FIRST_K)
     float4* info_core;       // [K][padded_pixels] (dC/dalpha factors, blending weight)                 (HYBRID, FIRST_K)
     float* info_tail;        // [6][padded_pixels] HYBRID tail terms / [5][padded_pixels] OIT terms
     uint32_t padded_pixels;  // n_tiles * pixels_per_tile

@@ -66,6 +66,9 @@ __device__ __forceinline__ CameraCols load_camera_cols(const float* __restrict__
     return {make_float3(r1.x, r2.x, r4.x), make_float3(r1.y, r2.y, r4.y), make_float3(r1.z, r2.z, r4.z)};
 }
 
+constexpr int kBwdThreads = 128;       // threads per tile: one staged instance each, and an even share of the batch's pairs
+constexpr int kBwdThreadsLog2 = 7;
+constexpr int kBwdMinBlocks = 5;       // resident CTAs per SM the register budget is held to (shared memory allows as many)
 template <int MODE, int K> struct BwdSmem {
     static constexpr bool has_core = (MODE == HTGS_MODE_HYBRID_BLEND || MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K);
     static constexpr bool has_tail = (MODE == HTGS_MODE_HYBRID_BLEND || MODE == HTGS_MODE_OIT_BLEND);
@@ -79,13 +82,15 @@ template <int MODE, int K> struct BwdSmem {
     static constexpr size_t ta_off = tc_off + tc_bytes;
     static constexpr size_t ta_bytes = has_tail ? 64 * 4 : 0;
     static constexpr size_t stage_off = (ta_off + ta_bytes + 15) & ~size_t(15);
-    static constexpr size_t stage_bytes = 64 * (4 * 16 + 8 + 4) + 65 * 4 + 12;
-    static constexpr size_t total = stage_off + stage_bytes;
+    static constexpr size_t stage_bytes = kBwdThreads * (4 * 16 + 8 + 4) + (kBwdThreads + 1) * 4 + 12;
+    static constexpr size_t core_off = (stage_off + stage_bytes + 15) & ~size_t(15);     // [NT][64] core entry of each (staged instance, pixel) pair
+    static constexpr size_t core_bytes = has_core ? size_t(kBwdThreads) * 64 : 0;
+    static constexpr size_t total = core_off + core_bytes;
 };
 
-// HYBRID_BLEND / ALPHA_BLEND_FIRST_K / OIT_BLEND: one CTA per 8x8 tile, one thread per Gaussian of a batch.
+// HYBRID_BLEND / ALPHA_BLEND_FIRST_K / OIT_BLEND: one CTA per 8x8 tile, one thread per Gaussian of a batch of kBwdThreads.
 template <int MODE, int K, bool ABS_GRAD>
-__global__ void __launch_bounds__(64) backward_tile_kernel(
+__global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
     const CullRecord* __restrict__ cull, TrainPixelBuffers tin, const float* __restrict__ grad_image, const float* __restrict__ VPM,
     float4* __restrict__ accum, uint32_t width, uint32_t height, uint32_t grid_w)
@@ -95,7 +100,8 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
     constexpr bool kHybrid = MODE == HTGS_MODE_HYBRID_BLEND;
     constexpr bool kFirstK = MODE == HTGS_MODE_ALPHA_BLEND_FIRST_K;
     extern __shared__ __align__(16) unsigned char smem[];
-    [[maybe_unused]] uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem + SM::idx_off);   // [64 pixels][idx_stride]
+    [[maybe_unused]] uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem + SM::idx_off);   // [64 pixels][idx_stride] positions in the tile's list
+    [[maybe_unused]] signed char* s_core = reinterpret_cast<signed char*>(smem + SM::core_off);
     [[maybe_unused]] float4* s_cg = reinterpret_cast<float4*>(smem + SM::cg_off);          // [K][64] (W * grad_pixel, A . grad_pixel)
     [[maybe_unused]] float4* s_tc = reinterpret_cast<float4*>(smem + SM::tc_off);          // [64] (full_weight * grad_pixel, common term)
     [[maybe_unused]] float* s_ta = reinterpret_cast<float*>(smem + SM::ta_off);            // [64] term divided by (1 - alpha)
@@ -106,11 +112,13 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
     if (range.x >= range.y) return;
     const uint32_t n_pixels = width * height;
     const uint32_t PP = tin.padded_pixels;
-    const uint32_t slot = (tile_y * grid_w + tile_x) * 64 + tid;
+    constexpr uint32_t NT = kBwdThreads;
+    const uint32_t pix = tid & 63, part = tid >> 6;          // the per-pixel terms are set up by NT / 64 threads per pixel
+    const uint32_t slot = (tile_y * grid_w + tile_x) * 64 + pix;
 
     // ---- per-pixel terms of this tile (hybrid_blend/kernels/backward.cuh:137-176, oit_blend/kernels/backward.cuh:131-156)
     {
-        const uint32_t px_i = tile_x * 8 + (tid & 7), py_i = tile_y * 8 + (tid >> 3);
+        const uint32_t px_i = tile_x * 8 + (pix & 7), py_i = tile_y * 8 + (pix >> 3);
         const bool inside = px_i < width && py_i < height;
         float3 grad_pixel = make_float3(0.0f, 0.0f, 0.0f);
         if (inside) {
@@ -119,7 +127,9 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
         }
         if constexpr (SM::has_core) {
             #pragma unroll
-            for (int k = 0; k < K; ++k) {
+            for (int k0 = 0; k0 < K; k0 += int(NT / 64)) {
+                const int k = k0 + int(part);
+                if (k >= K) break;
                 uint32_t idx = 0xffffffffu;
                 float4 cg = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 if (inside) {
@@ -130,8 +140,8 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
                         cg = make_float4(drgb.x, drgb.y, drgb.z, dot(f3(info), grad_pixel));
                     }
                 }
-                s_idx[tid * SM::idx_stride + k] = idx;
-                s_cg[k * 64 + tid] = cg;
+                s_idx[pix * SM::idx_stride + k] = idx;
+                s_cg[k * 64 + pix] = cg;
             }
         }
         if constexpr (SM::has_tail) {
@@ -149,8 +159,10 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
                 tc = make_float4(part.x, part.y, part.z, -full_weight_tail * alpha_sum_rcp * rgb_dot_grad);
                 ta = weight_tail * transmittance_tail * rgb_dot_grad;
             }
-            s_tc[tid] = tc;
-            s_ta[tid] = ta;
+            if (part == 0) {
+                s_tc[pix] = tc;
+                s_ta[pix] = ta;
+            }
         }
     }
     // pixels of the tile that exist in the image, as a 64-bit mask (bit = row * 8 + column)
@@ -164,29 +176,53 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
     if constexpr (ABS_GRAD) cam = load_camera_cols(VPM);
     __syncthreads();
 
-    // ---- batches of 64 instances; the (Gaussian, pixel) candidate pairs of a batch are split EVENLY over the
-    //      64 threads (pairs of one Gaussian are contiguous, so a thread walks a few Gaussians back to back)
+    // ---- batches of NT instances; the (Gaussian, pixel) candidate pairs of a batch are split EVENLY over the
+    //      NT threads (pairs of one Gaussian are contiguous, so a thread walks a few Gaussians back to back)
     float4* s_T1 = reinterpret_cast<float4*>(smem + SM::stage_off);
-    float4* s_T2 = s_T1 + 64;
-    float4* s_T4 = s_T2 + 64;
-    float4* s_rgba = s_T4 + 64;
-    unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(s_rgba + 64);
-    uint32_t* s_g = reinterpret_cast<uint32_t*>(s_mask + 64);
-    uint32_t* s_off = s_g + 64;          // [65] exclusive prefix of the per-Gaussian pair counts
-    __shared__ uint32_t s_warp_total[2];
+    float4* s_T2 = s_T1 + NT;
+    float4* s_T4 = s_T2 + NT;
+    float4* s_rgba = s_T4 + NT;
+    unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(s_rgba + NT);
+    uint32_t* s_g = reinterpret_cast<uint32_t*>(s_mask + NT);
+    uint32_t* s_off = s_g + NT;          // [NT + 1] exclusive prefix of the per-Gaussian pair counts
+    __shared__ uint32_t s_warp_total[NT / 32];
     const float x0 = float(tile_x * 8), y0 = float(tile_y * 8);
     const uint32_t lane = tid & 31, warp = tid >> 5;
-    for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += 64) {
+    // Software pipeline of the staging loads: the record and outline of the instance a thread stages in batch b + 1 are
+    // requested while batch b is processed (its index was requested one batch earlier still), so that their latency
+    // overlaps the pair loop instead of sitting between two barriers.
+    uint32_t g_cur = 0, g_nxt = 0;
+    float4 pT1 = make_float4(0, 0, 0, 0), pT2 = pT1, pT4 = pT1, pRGBA = pT1, pc0 = pT1;
+    float pcc = 0.0f;
+    auto request = [&](uint32_t g) {
+        const float* rec = reinterpret_cast<const float*>(eval + g);
+        pT1 = ldg4(rec); pT2 = ldg4(rec + 4); pT4 = ldg4(rec + 8); pRGBA = ldg4(rec + 16);
+        pc0 = ldg4(reinterpret_cast<const float*>(cull + g));
+        pcc = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
+    };
+    if (range.x + tid < range.y) { g_cur = __ldg(prims_sorted + range.x + tid); request(g_cur); }
+    if (range.x + NT + tid < range.y) g_nxt = __ldg(prims_sorted + range.x + NT + tid);
+    for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += NT) {
         __syncthreads();                  // previous batch fully consumed
         const uint32_t inst = batch_begin + tid;
         uint64_t my_mask = 0;
-        if (inst < range.y) {
-            const uint32_t g = __ldg(prims_sorted + inst);
-            const float4 c0 = ldg4(reinterpret_cast<const float*>(cull + g));
-            const float cc = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
-            const float* rec = reinterpret_cast<const float*>(eval + g);
-            s_T1[tid] = ldg4(rec); s_T2[tid] = ldg4(rec + 4); s_T4[tid] = ldg4(rec + 8); s_rgba[tid] = ldg4(rec + 16);
-            s_g[tid] = g;
+        const bool valid = inst < range.y;
+        const float4 c0 = pc0;
+        const float cc = pcc;
+        if (valid) {
+            s_T1[tid] = pT1; s_T2[tid] = pT2; s_T4[tid] = pT4; s_rgba[tid] = pRGBA;
+            s_g[tid] = g_cur;
+        }
+        if constexpr (SM::has_core) {      // no pair of my instance is a core entry until the scatter below says so
+            uint4* row = reinterpret_cast<uint4*>(s_core + tid * 64);
+            const uint4 none = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+            row[0] = none; row[1] = none; row[2] = none; row[3] = none;
+        }
+        // next batch: its index is here, request its data; request the index of the batch after it
+        g_cur = g_nxt;
+        if (inst + NT < range.y) request(g_cur);
+        if (inst + 2 * NT < range.y) g_nxt = __ldg(prims_sorted + inst + 2 * NT);
+        if (valid) {
             const float dx0 = x0 - c0.x, dy0 = y0 - c0.y;
             #pragma unroll
             for (int r = 0; r < 8; ++r) {
@@ -208,21 +244,43 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
         for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= uint32_t(o)) inc += t; }
         if (lane == 31) s_warp_total[warp] = inc;
         __syncthreads();
-        const uint32_t excl = inc - cnt + (warp ? s_warp_total[0] : 0u);
+        uint32_t excl = inc - cnt, total_pairs = 0;
+        #pragma unroll
+        for (uint32_t w = 0; w < NT / 32; ++w) {
+            const uint32_t t = s_warp_total[w];
+            if (w < warp) excl += t;
+            total_pairs += t;
+        }
         s_off[tid] = excl;
-        const uint32_t total_pairs = s_warp_total[0] + s_warp_total[1];
-        if (tid == 0) s_off[64] = total_pairs;
+        if (tid == 0) s_off[NT] = total_pairs;
+        if constexpr (SM::has_core) {
+            // The training forward saved, per pixel and core entry, the POSITION of the entry's Gaussian in the tile's list,
+            // so the entries that belong to this batch are those within NT of its start, and position - start is the staged slot.
+            const uint32_t batch_pos = batch_begin - range.x;
+            const uint4* row = reinterpret_cast<const uint4*>(s_idx + pix * SM::idx_stride);
+            #pragma unroll
+            for (int k4 = 0; k4 < (K + 3) / 4; k4 += int(NT / 64)) {
+                const int q = k4 + int(part);
+                if (q >= (K + 3) / 4) break;
+                const uint4 v = row[q];
+                const uint32_t j0 = v.x - batch_pos, j1 = v.y - batch_pos, j2 = v.z - batch_pos, j3 = v.w - batch_pos;
+                if (j0 < NT) s_core[j0 * 64 + pix] = (signed char)(4 * q);
+                if (4 * q + 1 < K && j1 < NT) s_core[j1 * 64 + pix] = (signed char)(4 * q + 1);
+                if (4 * q + 2 < K && j2 < NT) s_core[j2 * 64 + pix] = (signed char)(4 * q + 2);
+                if (4 * q + 3 < K && j3 < NT) s_core[j3 * 64 + pix] = (signed char)(4 * q + 3);
+            }
+        }
         __syncthreads();
         if (total_pairs == 0) continue;
         // my share of the pairs
-        const uint32_t lo = uint32_t((uint64_t(tid) * total_pairs) >> 6), hi = uint32_t((uint64_t(tid + 1) * total_pairs) >> 6);
+        const uint32_t lo = uint32_t((uint64_t(tid) * total_pairs) >> kBwdThreadsLog2), hi = uint32_t((uint64_t(tid + 1) * total_pairs) >> kBwdThreadsLog2);
         uint32_t remaining = hi - lo;
         if (remaining == 0) continue;
         uint32_t j = 0;
         {
-            uint32_t a = 0, b = 64;      // last j with s_off[j] <= lo
+            uint32_t a = 0, b = NT;      // last j with s_off[j] <= lo
             #pragma unroll
-            for (int it = 0; it < 6; ++it) { const uint32_t mid = (a + b) >> 1; if (s_off[mid] <= lo) a = mid; else b = mid; }
+            for (int it = 0; it < kBwdThreadsLog2; ++it) { const uint32_t mid = (a + b) >> 1; if (s_off[mid] <= lo) a = mid; else b = mid; }
             j = a;
         }
         uint64_t mask = s_mask[j];
@@ -258,17 +316,7 @@ __global__ void __launch_bounds__(64) backward_tile_kernel(
             const float numerator_rho2 = dot(m, m);
             const float denominator = dot(d, d);
             int core_idx = -1;
-            if constexpr (SM::has_core) {
-                const uint4* row = reinterpret_cast<const uint4*>(s_idx + p * SM::idx_stride);
-                #pragma unroll
-                for (int k4 = 0; k4 < (K + 3) / 4; ++k4) {
-                    const uint4 v = row[k4];
-                    if (v.x == g) core_idx = 4 * k4;
-                    if (4 * k4 + 1 < K && v.y == g) core_idx = 4 * k4 + 1;
-                    if (4 * k4 + 2 < K && v.z == g) core_idx = 4 * k4 + 2;
-                    if (4 * k4 + 3 < K && v.w == g) core_idx = 4 * k4 + 3;
-                }
-            }
+            if constexpr (SM::has_core) core_idx = s_core[j * 64 + p];
             if constexpr (kFirstK) {
                 if (core_idx < 0) continue;                    // only stored fragments carry gradient (first_k backward.cuh:84-87)
             } else {
@@ -561,15 +609,16 @@ cudaError_t launch_tile_backward(bool abs_grad, const FrameGeometry& geo, const 
     using SM = BwdSmem<MODE, K>;
     const dim3 grid(geo.grid_w, geo.grid_h, 1);
     auto launch = [&](auto kernel) -> cudaError_t {
-        static bool configured[64] = {};
+        // both instantiations have the same function-pointer type, so this lambda (and a static in it) is shared by them
+        static bool configured[2][64] = {};
         int device = 0;
         cudaGetDevice(&device);
-        if (SM::total > 48 * 1024 && device >= 0 && device < 64 && !configured[device]) {
+        if (SM::total > 48 * 1024 && device >= 0 && device < 64 && !configured[abs_grad][device]) {
             const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SM::total));
             if (err != cudaSuccess) return err;
-            configured[device] = true;
+            configured[abs_grad][device] = true;
         }
-        kernel<<<grid, 64, SM::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, tin, grad_image, VPM, accum,
+        kernel<<<grid, kBwdThreads, SM::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, tin, grad_image, VPM, accum,
                                                 uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w));
         return cudaGetLastError();
     };
