@@ -116,6 +116,21 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
     const uint32_t pix = tid & 63, part = tid >> 6;          // the per-pixel terms are set up by NT / 64 threads per pixel
     const uint32_t slot = (tile_y * grid_w + tile_x) * 64 + pix;
 
+    // Software pipeline of the staging loads: the record and outline of the instance a thread stages in batch b + 1 are
+    // requested while batch b is processed (its index was requested one batch earlier still), so that their latency
+    // overlaps the pair loop instead of sitting between two barriers.  The first indices are requested before the
+    // per-pixel terms are read, so that the two chains of dependent loads at the start of a tile overlap as well.
+    uint32_t g_cur = 0, g_nxt = 0;
+    float4 pT1 = make_float4(0, 0, 0, 0), pT2 = pT1, pT4 = pT1, pRGBA = pT1, pc0 = pT1;
+    float pcc = 0.0f;
+    auto request = [&](uint32_t g) {
+        const float* rec = reinterpret_cast<const float*>(eval + g);
+        pT1 = ldg4(rec); pT2 = ldg4(rec + 4); pT4 = ldg4(rec + 8); pRGBA = ldg4(rec + 16);
+        pc0 = ldg4(reinterpret_cast<const float*>(cull + g));
+        pcc = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
+    };
+    if (range.x + tid < range.y) g_cur = __ldg(prims_sorted + range.x + tid);
+    if (range.x + NT + tid < range.y) g_nxt = __ldg(prims_sorted + range.x + NT + tid);
     // ---- per-pixel terms of this tile (hybrid_blend/kernels/backward.cuh:137-176, oit_blend/kernels/backward.cuh:131-156)
     {
         const uint32_t px_i = tile_x * 8 + (pix & 7), py_i = tile_y * 8 + (pix >> 3);
@@ -174,6 +189,7 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
     }
     [[maybe_unused]] CameraCols cam;
     if constexpr (ABS_GRAD) cam = load_camera_cols(VPM);
+    if (range.x + tid < range.y) request(g_cur);
     __syncthreads();
 
     // ---- batches of NT instances; the (Gaussian, pixel) candidate pairs of a batch are split EVENLY over the
@@ -188,20 +204,6 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
     __shared__ uint32_t s_warp_total[NT / 32];
     const float x0 = float(tile_x * 8), y0 = float(tile_y * 8);
     const uint32_t lane = tid & 31, warp = tid >> 5;
-    // Software pipeline of the staging loads: the record and outline of the instance a thread stages in batch b + 1 are
-    // requested while batch b is processed (its index was requested one batch earlier still), so that their latency
-    // overlaps the pair loop instead of sitting between two barriers.
-    uint32_t g_cur = 0, g_nxt = 0;
-    float4 pT1 = make_float4(0, 0, 0, 0), pT2 = pT1, pT4 = pT1, pRGBA = pT1, pc0 = pT1;
-    float pcc = 0.0f;
-    auto request = [&](uint32_t g) {
-        const float* rec = reinterpret_cast<const float*>(eval + g);
-        pT1 = ldg4(rec); pT2 = ldg4(rec + 4); pT4 = ldg4(rec + 8); pRGBA = ldg4(rec + 16);
-        pc0 = ldg4(reinterpret_cast<const float*>(cull + g));
-        pcc = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
-    };
-    if (range.x + tid < range.y) { g_cur = __ldg(prims_sorted + range.x + tid); request(g_cur); }
-    if (range.x + NT + tid < range.y) g_nxt = __ldg(prims_sorted + range.x + NT + tid);
     for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += NT) {
         __syncthreads();                  // previous batch fully consumed
         const uint32_t inst = batch_begin + tid;
