@@ -37,8 +37,18 @@ namespace htgs {
 
 namespace {
 
+// Pixels one CTA blends.  The binning tile of GLOBAL_ORDERING is 16x16 (its lists have to be the reference's), but its
+// blend walks a list with per-pixel early termination and no state shared between pixels, so each binning tile is blended
+// by split_x * split_y independent CTAs that read the same list: more and shorter-lived CTAs, a tighter outline test per
+// CTA, and a CTA stops as soon as ITS pixels are opaque.
+#ifndef HTGS_GO_BLEND_W
+#define HTGS_GO_BLEND_W 8
+#define HTGS_GO_BLEND_H 8
+#endif
 template <int MODE> struct TileShape {
-    static constexpr int tw = ModeTraits<MODE>::tile_w, th = ModeTraits<MODE>::tile_h;
+    static constexpr bool split = MODE == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING;
+    static constexpr int tw = split ? HTGS_GO_BLEND_W : ModeTraits<MODE>::tile_w, th = split ? HTGS_GO_BLEND_H : ModeTraits<MODE>::tile_h;
+    static constexpr int split_x = ModeTraits<MODE>::tile_w / tw, split_y = ModeTraits<MODE>::tile_h / th;
     static constexpr int threads = tw * th;
     static constexpr int warps = threads / 32;
     static constexpr int rows_per_warp = 32 / tw;
@@ -180,7 +190,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
     float transmittance = 1.0f;                          // HB: tail; OIT / GO: pixel
     bool done = !inside;
 
-    const uint2 range = tile_ranges[tile_y * grid_w + tile_x];
+    const uint2 range = tile_ranges[(tile_y / TS::split_y) * grid_w + tile_x / TS::split_x];   // grid_w counts binning tiles
     uint32_t phase = 0;
     bool wait_failed = false;
     [[maybe_unused]] uint32_t stat_candidates = 0, stat_accepted = 0;
@@ -615,8 +625,9 @@ cudaError_t launch_blend_t(const FrameGeometry& geo, const PrimBuffers& prim, co
         if (err != cudaSuccess) return err;
         configured[device] = true;
     }
-    const dim3 grid(geo.grid_w, geo.grid_h, 1);
-    kernel<<<grid, TileShape<MODE>::threads, SL::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, out.image, out.depth, out.alpha, tout,
+    using TS = TileShape<MODE>;
+    const dim3 grid((geo.width + TS::tw - 1) / TS::tw, (geo.height + TS::th - 1) / TS::th, 1);
+    kernel<<<grid, TS::threads, SL::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, out.image, out.depth, out.alpha, tout,
                                                                   uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), out.to_chw,
                                                                   out.use_median_depth, status);
     return cudaGetLastError();
