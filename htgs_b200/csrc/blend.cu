@@ -20,7 +20,7 @@
 //     can touch pixel p.  No divergence, no shared-memory queue.
 //  3. Exact pass.  After the mbarrier completes, every lane walks the set bits of its own mask, so
 //     (almost) every iteration of every lane is an accepted fragment: the expensive part (IEEE divide,
-//     expf, depth, K-buffer insertion) runs converged instead of once per Gaussian per warp.  HYBRID_BLEND
+//     expf, depth, K-buffer insertion) runs converged instead of once per Gaussian per warp.  Every mode
 //     evaluates two candidates per trip for instruction-level parallelism and commits them in list order.
 //  4. K-buffer.  Registers hold only (depth, slot) pairs; the payloads live in a shared-memory pool of
 //     K+1 slots per pixel, so an insertion moves 2 registers per level instead of 5-6.  The buffer
