@@ -16,10 +16,13 @@
 //    per-Gaussian kernel turns the record into the six output gradients (the reference repeats the
 //    scale / rotation chain rule per fragment in two of its modes);
 //  * HYBRID / FIRST_K / OIT: one thread per Gaussian of a tile batch first builds the 64-bit mask of
-//    tile pixels its conservative outline can touch (3 flops per pixel), then only walks those pixels;
-//  * GLOBAL_ORDERING needs the running transmittance per pixel, so it stays pixel-parallel; the 32
-//    pixel contributions of a warp to one Gaussian are reduced with shuffles into a shared-memory
-//    record per staged Gaussian and flushed with vector reductions once per batch.
+//    tile pixels its conservative outline can touch (3 flops per pixel); the (Gaussian, pixel) pairs of the
+//    batch are then split evenly over the threads.  The forward pass saves core entries as positions in the
+//    tile's list, so which pairs are core entries is a table filled once per batch, not a search per pair;
+//  * GLOBAL_ORDERING needs the running transmittance per pixel, so it stays pixel-parallel, in independent
+//    8x8-pixel CTAs; a warp only walks the staged Gaussians whose outline reaches its pixels, and the 32
+//    pixel contributions to one Gaussian are summed with a transposing shuffle reduction into a
+//    shared-memory record per staged Gaussian, flushed with vector reductions once per batch.
 #include "kernels.h"
 
 namespace htgs {
@@ -204,6 +207,27 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
     __shared__ uint32_t s_warp_total[NT / 32];
     const float x0 = float(tile_x * 8), y0 = float(tile_y * 8);
     const uint32_t lane = tid & 31, warp = tid >> 5;
+    // The training forward saved, per pixel and core entry, the POSITION of the entry's Gaussian in the tile's list, so the
+    // entries that belong to a batch are those within NT of its start, and position - start is the staged slot.
+    // FIRST_K gives gradient to stored fragments only: there the entries also set the pixel masks of the staged instances.
+    [[maybe_unused]] auto scatter_core_entries = [&](uint32_t batch_pos) {
+        const uint4* row = reinterpret_cast<const uint4*>(s_idx + pix * SM::idx_stride);
+        auto put = [&](uint32_t j, int k) {
+            s_core[j * 64 + pix] = (signed char)k;
+            if constexpr (kFirstK) atomicOr(reinterpret_cast<uint32_t*>(s_mask + j) + (pix >> 5), 1u << (pix & 31));
+        };
+        #pragma unroll
+        for (int k4 = 0; k4 < (K + 3) / 4; k4 += int(NT / 64)) {
+            const int q = k4 + int(part);
+            if (q >= (K + 3) / 4) break;
+            const uint4 v = row[q];
+            const uint32_t j0 = v.x - batch_pos, j1 = v.y - batch_pos, j2 = v.z - batch_pos, j3 = v.w - batch_pos;
+            if (j0 < NT) put(j0, 4 * q);
+            if (4 * q + 1 < K && j1 < NT) put(j1, 4 * q + 1);
+            if (4 * q + 2 < K && j2 < NT) put(j2, 4 * q + 2);
+            if (4 * q + 3 < K && j3 < NT) put(j3, 4 * q + 3);
+        }
+    };
     for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += NT) {
         __syncthreads();                  // previous batch fully consumed
         const uint32_t inst = batch_begin + tid;
@@ -224,7 +248,13 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
         g_cur = g_nxt;
         if (inst + NT < range.y) request(g_cur);
         if (inst + 2 * NT < range.y) g_nxt = __ldg(prims_sorted + inst + 2 * NT);
-        if (valid) {
+        if constexpr (kFirstK) {
+            s_mask[tid] = 0;
+            __syncthreads();
+            scatter_core_entries(batch_begin - range.x);
+            __syncthreads();
+            my_mask = s_mask[tid];
+        } else if (valid) {
             const float dx0 = x0 - c0.x, dy0 = y0 - c0.y;
             #pragma unroll
             for (int r = 0; r < 8; ++r) {
@@ -239,7 +269,7 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
             }
             my_mask &= inside_mask;
         }
-        s_mask[tid] = my_mask;
+        if constexpr (!kFirstK) s_mask[tid] = my_mask;
         const uint32_t cnt = __popcll(my_mask);
         uint32_t inc = cnt;
         #pragma unroll
@@ -255,23 +285,7 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
         }
         s_off[tid] = excl;
         if (tid == 0) s_off[NT] = total_pairs;
-        if constexpr (SM::has_core) {
-            // The training forward saved, per pixel and core entry, the POSITION of the entry's Gaussian in the tile's list,
-            // so the entries that belong to this batch are those within NT of its start, and position - start is the staged slot.
-            const uint32_t batch_pos = batch_begin - range.x;
-            const uint4* row = reinterpret_cast<const uint4*>(s_idx + pix * SM::idx_stride);
-            #pragma unroll
-            for (int k4 = 0; k4 < (K + 3) / 4; k4 += int(NT / 64)) {
-                const int q = k4 + int(part);
-                if (q >= (K + 3) / 4) break;
-                const uint4 v = row[q];
-                const uint32_t j0 = v.x - batch_pos, j1 = v.y - batch_pos, j2 = v.z - batch_pos, j3 = v.w - batch_pos;
-                if (j0 < NT) s_core[j0 * 64 + pix] = (signed char)(4 * q);
-                if (4 * q + 1 < K && j1 < NT) s_core[j1 * 64 + pix] = (signed char)(4 * q + 1);
-                if (4 * q + 2 < K && j2 < NT) s_core[j2 * 64 + pix] = (signed char)(4 * q + 2);
-                if (4 * q + 3 < K && j3 < NT) s_core[j3 * 64 + pix] = (signed char)(4 * q + 3);
-            }
-        }
+        if constexpr (SM::has_core && !kFirstK) scatter_core_entries(batch_begin - range.x);
         __syncthreads();
         if (total_pairs == 0) continue;
         // my share of the pairs
@@ -360,23 +374,50 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
     }
 }
 
+// Sum of 16 per-lane values over the warp in 16 shuffles instead of 80: at every step a lane keeps one half of its
+// values, hands the other half to its partner and adds what the partner hands over.  After the steps with lane bits
+// 4, 3, 2, 1 a lane holds ONE value summed over the 16 lanes that share its bit 0; the last shuffle completes it.
+// On return the lane holds the warp total of v[transpose_reduce_index(lane)].
+__device__ __forceinline__ uint32_t transpose_reduce_index(uint32_t lane) { return (lane >> 1) & 15u; }   // bit 4 -> 8, bit 3 -> 4, bit 2 -> 2, bit 1 -> 1
+__device__ __forceinline__ float transpose_reduce16(const float (&v)[16], uint32_t lane) {
+    float a8[8], a4[4], a2[2];
+    const bool up16 = lane & 16u, up8 = lane & 8u, up4 = lane & 4u, up2 = lane & 2u;
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) a8[i] = (up16 ? v[i + 8] : v[i]) + __shfl_xor_sync(0xffffffffu, up16 ? v[i] : v[i + 8], 16);
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) a4[i] = (up8 ? a8[i + 4] : a8[i]) + __shfl_xor_sync(0xffffffffu, up8 ? a8[i] : a8[i + 4], 8);
+    #pragma unroll
+    for (int i = 0; i < 2; ++i) a2[i] = (up4 ? a4[i + 2] : a4[i]) + __shfl_xor_sync(0xffffffffu, up4 ? a4[i] : a4[i + 2], 4);
+    float a1 = (up2 ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, up2 ? a2[0] : a2[1], 2);
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+    return a1;
+}
+
 // ALPHA_BLEND_GLOBAL_ORDERING: pixel-parallel, front to back in key order, using the final pixel colour so that
 // "colour behind" = rgb_pixel - rgb_pixel_new (alpha_blend_global_ordering/kernels/backward.cuh:104-161).
-constexpr int kGoBatch = 128;   // Gaussians staged per iteration (two per 256-thread CTA would waste threads; 128 keeps shared memory at 28 KB)
-__global__ void __launch_bounds__(256) backward_global_kernel(
+// One CTA of two warps per 8x8 pixels; the four CTAs of a 16x16 binning tile walk the same list independently (a pixel
+// shares no state with its neighbours) and each stops when ITS pixels are opaque.  Per batch of 64 staged Gaussians a
+// warp first finds, with lane = Gaussian, which of them can touch its 8x4 pixels at all (the conservative outline the
+// forward pass uses) and only walks those; the 16 values a pixel adds to a Gaussian's record are summed over the warp
+// by transpose_reduce16 and added to a shared-memory record per staged Gaussian, flushed once per batch.
+constexpr int kGoBatch = 64;
+constexpr int kGoAccStride = 17;     // 16 values + sum |dL/dposition|; odd stride: rows and columns are both conflict-free
+__global__ void __launch_bounds__(64) backward_global_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
-    const float* __restrict__ grad_image, const float* __restrict__ image, const float* __restrict__ VPM, float4* __restrict__ accum,
-    uint32_t width, uint32_t height, uint32_t grid_w, bool abs_grad_on)
+    const CullRecord* __restrict__ cull, const float* __restrict__ grad_image, const float* __restrict__ image, const float* __restrict__ VPM,
+    float4* __restrict__ accum, uint32_t width, uint32_t height, uint32_t grid_w, bool abs_grad_on)
 {
     using MT = ModeTraits<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING>;
-    __shared__ float4 s_T1[kGoBatch], s_T2[kGoBatch], s_T4[kGoBatch], s_rgba[kGoBatch];
+    __shared__ float4 s_T1[kGoBatch], s_T2[kGoBatch], s_T4[kGoBatch], s_rgba[kGoBatch], s_c0[kGoBatch];
+    __shared__ float s_cc[kGoBatch];
     __shared__ uint32_t s_g[kGoBatch];
-    __shared__ float s_acc[kGoBatch][20];
-    const uint32_t tid = threadIdx.x, lane = tid & 31;
-    const uint32_t tile_x = blockIdx.x, tile_y = blockIdx.y;
-    const uint32_t px_i = tile_x * 16 + (tid & 15), py_i = tile_y * 16 + (tid >> 4);
+    __shared__ float s_acc[kGoBatch * kGoAccStride];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t tile_x = blockIdx.x, tile_y = blockIdx.y;                 // in units of 8 pixels
+    const uint32_t px_i = tile_x * 8 + (tid & 7), py_i = tile_y * 8 + (tid >> 3);
     const bool inside = px_i < width && py_i < height;
     const float pixel_x = __uint2float_rn(px_i), pixel_y = __uint2float_rn(py_i);
+    const float rect_x0 = float(tile_x * 8), rect_y0 = float(tile_y * 8 + warp * 4);
     const uint32_t n_pixels = width * height;
     float3 grad_pixel = make_float3(0, 0, 0), rgb_pixel = make_float3(0, 0, 0);
     if (inside) {
@@ -388,23 +429,54 @@ __global__ void __launch_bounds__(256) backward_global_kernel(
     float3 rgb_pixel_new = make_float3(0, 0, 0);
     float transmittance = 1.0f;
     bool done = !inside;
-    const uint2 range = tile_ranges[tile_y * grid_w + tile_x];
+    constexpr uint32_t kSplit = MT::tile_w / 8;                               // 8-pixel CTAs per binning tile edge
+    const uint2 range = tile_ranges[(tile_y / kSplit) * grid_w + tile_x / kSplit];
+    const uint32_t out_index = transpose_reduce_index(lane);
     for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += kGoBatch) {
-        if (__syncthreads_count(done) == 256) break;
+        if (__syncthreads_count(done) == 64) break;
         const uint32_t batch = min(uint32_t(kGoBatch), range.y - batch_begin);
         if (tid < batch) {
             const uint32_t g = __ldg(prims_sorted + batch_begin + tid);
             const float* rec = reinterpret_cast<const float*>(eval + g);
             s_g[tid] = g;
             s_T1[tid] = ldg4(rec); s_T2[tid] = ldg4(rec + 4); s_T4[tid] = ldg4(rec + 8); s_rgba[tid] = ldg4(rec + 16);
+            s_c0[tid] = ldg4(reinterpret_cast<const float*>(cull + g));
+            s_cc[tid] = __ldg(reinterpret_cast<const float*>(cull + g) + 4);
+        } else {
+            s_c0[tid] = make_float4(__int_as_float(0x7f800000), 0.0f, 0.0f, 0.0f);   // an outline nothing is inside of
+            s_cc[tid] = 0.0f;
         }
-        for (uint32_t i = tid; i < kGoBatch * 20; i += 256) (&s_acc[0][0])[i] = 0.0f;
+        for (uint32_t i = tid; i < kGoBatch * kGoAccStride; i += 64) s_acc[i] = 0.0f;
         __syncthreads();
-        for (uint32_t j = 0; j < batch; ++j) {
-            if (__all_sync(0xffffffffu, done)) break;
-            float v[17];
+        // which staged Gaussians can touch this warp's 8x4 pixels (lane = Gaussian)
+        uint64_t todo = 0;
+        #pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const float4 c0 = s_c0[half * 32 + lane];
+            const float cc = s_cc[half * 32 + lane];
+            const float dx0 = rect_x0 - c0.x, dy0 = rect_y0 - c0.y;
+            bool touches = false;
             #pragma unroll
-            for (int c = 0; c < 17; ++c) v[c] = 0.0f;
+            for (int r = 0; r < 4; ++r) {
+                const float dy = dy0 + float(r);
+                const float b2dy = c0.w * dy, cdy2 = cc * dy * dy;
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float dx = dx0 + float(i);
+                    const float q = dx * (c0.z * dx + b2dy) + cdy2;
+                    touches |= q <= 1.0f;
+                }
+            }
+            todo |= uint64_t(__ballot_sync(0xffffffffu, touches)) << (32 * half);
+        }
+        while (todo != 0) {
+            if (__all_sync(0xffffffffu, done)) break;
+            const uint32_t j = uint32_t(__ffsll((long long)todo) - 1);
+            todo &= todo - 1;
+            float v[16];
+            #pragma unroll
+            for (int c = 0; c < 16; ++c) v[c] = 0.0f;
+            float v_abs = 0.0f;
             bool contributes = false;
             if (!done) {
                 const float4 T1 = s_T1[j], T2 = s_T2[j], T4 = s_T4[j];
@@ -441,7 +513,7 @@ __global__ void __launch_bounds__(256) backward_global_kernel(
                             v[8] = pg.dT4.x; v[9] = pg.dT4.y; v[10] = pg.dT4.z; v[11] = pg.dT4.w;
                             if (abs_grad_on) {
                                 const float3 c4 = make_float3(pg.dT1.w, pg.dT2.w, pg.dT4.w);
-                                v[16] = fabsf(dot(cam.c1, c4)) + fabsf(dot(cam.c2, c4)) + fabsf(dot(cam.c3, c4));
+                                v_abs = fabsf(dot(cam.c1, c4)) + fabsf(dot(cam.c2, c4)) + fabsf(dot(cam.c3, c4));
                             }
                         }
                         transmittance *= one_minus_alpha;
@@ -449,19 +521,19 @@ __global__ void __launch_bounds__(256) backward_global_kernel(
                     }
                 }
             }
-            if (__any_sync(0xffffffffu, contributes)) {      // warp-aggregated: one shared-memory add per value and warp
-                #pragma unroll
-                for (int c = 0; c < 17; ++c) {
-                    float x = v[c];
+            if (__any_sync(0xffffffffu, contributes)) {
+                const float total = transpose_reduce16(v, lane);
+                if ((lane & 1u) == 0 && total != 0.0f) atomicAdd(&s_acc[j * kGoAccStride + out_index], total);
+                if (abs_grad_on) {
                     #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-                    if (lane == 0 && x != 0.0f) atomicAdd(&s_acc[j][c], x);
+                    for (int o = 16; o > 0; o >>= 1) v_abs += __shfl_xor_sync(0xffffffffu, v_abs, o);
+                    if (lane == 0 && v_abs != 0.0f) atomicAdd(&s_acc[j * kGoAccStride + 16], v_abs);
                 }
             }
         }
         __syncthreads();
         if (tid < batch) {
-            const float* a = s_acc[tid];
+            const float* a = s_acc + tid * kGoAccStride;
             bool any = false;
             #pragma unroll
             for (int c = 0; c < 17; ++c) any |= a[c] != 0.0f;
@@ -474,7 +546,6 @@ __global__ void __launch_bounds__(256) backward_global_kernel(
                 if (abs_grad_on) red_add_v4(rec + 4, make_float4(a[16], 0.0f, 0.0f, 0.0f));
             }
         }
-        __syncthreads();
     }
 }
 
@@ -668,8 +739,8 @@ cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsV
         case HTGS_MODE_OIT_BLEND:
             err = launch_tile_backward<HTGS_MODE_OIT_BLEND, 1>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, stream); break;
         case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: {
-            const dim3 grid(geo.grid_w, geo.grid_h, 1);
-            backward_global_kernel<<<grid, 256, 0, stream>>>(tile_ranges, prims_sorted, prim.eval, grad_image, image, view.VPM, acc.accum,
+            const dim3 grid((geo.width + 7) / 8, (geo.height + 7) / 8, 1);
+            backward_global_kernel<<<grid, 64, 0, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, grad_image, image, view.VPM, acc.accum,
                                                              uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), abs_grad);
             err = cudaGetLastError();
             break;
