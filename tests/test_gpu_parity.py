@@ -210,6 +210,24 @@ def test_bit_exact_against_reference_extension(mode, K):
             assert torch.equal(depth, rdepth), f"max depth diff {(depth - rdepth).abs().max().item():.3e}"
 
 
+@pytest.mark.parametrize("mode,K", [(0, 16), (2, 1)])
+def test_benchmark_scene_bit_exact_against_reference_extension(mode, K):
+    """The benchmark's own scene and orbit at full size (3 M Gaussians, 1297x840): image and depth of views spread over the
+    orbit equal the reference's bit for bit, mean and median depth."""
+    import torch
+    ref = harness.reference()
+    if ref is None:
+        pytest.skip("reference extension not built under baseline/_ref")
+    scene = scenes.outdoor_scene(n=3_000_000, n_views=200)
+    tensors = harness.scene_tensors(scene)
+    for vi in (0, 37, 74, 111, 148, 199):
+        view = scene.views[vi]
+        median = vi % 2 == 1
+        img, depth = harness.ours().rasterize(*tensors, harness.settings_for(harness.ours(), scene, view, mode, K), True, median)
+        rimg, rdepth = ref.rasterize(*tensors, harness.settings_for(ref, scene, view, mode, K), True, median)
+        assert torch.equal(img, rimg) and torch.equal(depth, rdepth), f"view {vi}"
+
+
 @pytest.mark.parametrize("mode,K,width,height", [(0, 32, 3840, 2160), (3, 1, 3840, 2160), (2, 1, 3000, 2400)])
 def test_large_images_use_wider_sort_keys(mode, K, width, height):
     """More than 65 536 tiles (4K images with 8x8 tiles): 32-bit tile keys, 17 bits in two radix passes; GLOBAL_ORDERING with
