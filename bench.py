@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--n-gaussians", type=int, default=3_000_000, help="scale the workload down for quick checks (invalid as a benchmark)")
     ap.add_argument("--workload", default="render", choices=["render", "render_fast", "train"],
                     help="render: configuration 1 (default, the headline metric); train: configuration 2 (fwd+bwd, L1 loss, one view per GPU, gradient all-reduce)")
+    ap.add_argument("--exchange", default="rows", choices=["rows", "dense"],
+                    help="train at N > 1: sum only the gradient rows of Gaussians some rank kept (default) or the dense tensors")
     ap.add_argument("--reference-kind", default="auto", choices=["auto", "cuda", "cpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-views", type=int, default=12)
@@ -174,6 +176,14 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
         from htgs_b200 import glue
         activate = glue.activate
 
+    # Exchange: this library's arm sums only the gradient rows of Gaussians some rank's view kept (the others are zero on
+    # every rank); the reference has no multi-GPU path and no such list, its arm all-reduces the dense tensors.
+    sparse = dist is not None and not is_reference and args.exchange == "rows"
+    if sparse:
+        from htgs_b200.torch_bindings import rasterization
+        rasterization.track_training_visibility(True)
+    exchanged_rows = []
+
     def step(s):
         vi = parallel.step_view_indices(s, 1, rank, world, n_views)[0]
         for l in leaves:
@@ -182,7 +192,9 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
         image = mod.diff_rasterize(leaves[0], act_scales, act_rotations, act_opacities, leaves[4], leaves[5], empty, settings(cams_dev[vi]), False)
         loss = (image - target).abs().mean()
         loss.backward()
-        if dist is not None:
+        if sparse:
+            exchanged_rows.append(parallel.allreduce_gradients_rows([l.grad for l in leaves], rasterization.last_training_visibility(device)))
+        elif dist is not None:
             parallel.allreduce_gradients([l.grad for l in leaves])
         return loss
 
@@ -208,11 +220,14 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
     clocks = sampler.stop(t0, t1)
     ms = parallel.max_over_ranks(e0.elapsed_time(e1), device)
     n = scene.n
-    grad_bytes = n * (3 + 3 + 4 + 1 + 3 + 3 * scene.sh_rest.shape[1]) * 4
+    row_bytes = (3 + 3 + 4 + 1 + 3 + 3 * scene.sh_rest.shape[1]) * 4
+    grad_bytes = int(np.mean(exchanged_rows[args.warmup:])) * row_bytes if sparse else n * row_bytes
     line = {"metric": "train-steps/s", "value": args.steps / (ms / 1000.0), "unit": "steps/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name.replace("config1", "config2 (fwd+bwd, L1, one view per GPU)"), "views_per_step": world,
-                       "allreduce_bytes_per_rank": grad_bytes if world > 1 else 0, "parallelism": f"view-partitioned x{world} + gradient all-reduce"},
+                       "allreduce_bytes_per_rank": grad_bytes if world > 1 else 0,
+                       "gradient_exchange": ("none" if world == 1 else "rows of the union of the ranks' visible Gaussians" if sparse else "dense tensors"),
+                       "views_per_s": world * args.steps / (ms / 1000.0), "parallelism": f"view-partitioned x{world} + gradient all-reduce"},
             "clocks": clocks, "final_loss": float(loss.item())}
     if is_reference:
         line["impl"] = "reference"

@@ -129,6 +129,7 @@ def lib():
                 l.htgs_backward.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(HtgsTrainBlobs),
                                             ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(HtgsGradients), ctypes.c_void_p]
                 l.htgs_backward_static.argtypes = l.htgs_backward.argtypes
+                l.htgs_forward_visibility.argtypes = [ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsTrainBlobs), ctypes.c_void_p, ctypes.c_void_p]
                 l.htgs_update_max_weights.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_float,
                                                       ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.POINTER(HtgsFrameInfo)]
                 l.htgs_render_fast.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_int,

@@ -571,6 +571,16 @@ int htgs_context_device(const HtgsContext* ctx) { return ctx ? ctx->device : -1;
 
 void htgs_set_last_error(const char* message) { g_last_error = message ? message : ""; }
 
+int htgs_forward_visibility(const HtgsScene* scene, const HtgsTrainBlobs* blobs, uint8_t* visible, void* stream_ptr) {
+    if (!scene || !blobs || (!visible && scene->n_primitives > 0)) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    if (scene->n_primitives < 0) return fail(HTGS_ERR_INVALID_ARGUMENT, "negative primitive count");
+    const PrimLayout P = carve_primitive_blob(blobs->per_primitive, scene->n_primitives);
+    if (!blobs->per_primitive || blobs->per_primitive_bytes < P.bytes) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "the per-Gaussian forward blob is missing or too small");
+    const cudaError_t err = launch_visibility(P.prim.n_touched, visible, uint32_t(scene->n_primitives), static_cast<cudaStream_t>(stream_ptr));
+    if (err != cudaSuccess) return fail_cuda(err, "forward visibility");
+    return HTGS_OK;
+}
+
 int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                   const float* grad_image, const float* image, const HtgsGradients* grads, void* stream_ptr) {
     if (!grads) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");

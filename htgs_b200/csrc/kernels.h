@@ -108,6 +108,7 @@ struct BackwardOutputs {
     int densification_rows;      // 0, 2 or 3
     bool use_distance_scaling;
 };
+cudaError_t launch_visibility(const uint32_t* n_touched, uint8_t* visible, uint32_t n, cudaStream_t stream);
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
                             const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
                             const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, int sm_count, cudaStream_t stream);

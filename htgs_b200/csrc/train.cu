@@ -720,6 +720,19 @@ cudaError_t launch_tile_backward_k(int K, bool abs_grad, const FrameGeometry& ge
 
 }  // namespace
 
+namespace {
+__global__ void __launch_bounds__(256) visibility_kernel(const uint32_t* __restrict__ n_touched, uint8_t* __restrict__ visible, uint32_t n) {
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i < n) visible[i] = n_touched[i] != 0;
+}
+}  // namespace
+
+cudaError_t launch_visibility(const uint32_t* n_touched, uint8_t* visible, uint32_t n, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    visibility_kernel<<<(n + 255) / 256, 256, 0, stream>>>(n_touched, visible, n);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
                             const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
                             const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, int sm_count, cudaStream_t stream) {

@@ -51,6 +51,37 @@ def allreduce_gradients(grads: Sequence, group=None, async_op: bool = False):
     return handles
 
 
+def allreduce_gradients_rows(grads: Sequence, rows, group=None) -> int:
+    """Sums per-Gaussian gradient tensors over the ranks, in place, exchanging only the rows some rank can have touched.
+
+    `rows` is a bool tensor [N]: the rows of this rank's tensors that may be non-zero (the Gaussians its view kept,
+    `torch_bindings.rasterization.last_training_visibility`); all other rows MUST be zero on this rank.  The union of the
+    ranks' row sets is formed with one small all-reduce, the union's rows are gathered into dense buffers, summed, and
+    written back; rows outside the union are zero on every rank and stay untouched.  A view keeps a sixth of a scene's
+    Gaussians, so the exchange moves the union's share of the 236 bytes per Gaussian instead of all of them.
+    One host synchronisation (the size of the union).  Returns the number of rows exchanged."""
+    import torch
+    import torch.distributed as dist
+    tensors = [g for g in grads if g is not None]
+    if not tensors:
+        return 0
+    n = rows.shape[0]
+    union = rows.to(torch.int32)
+    dist.all_reduce(union, op=dist.ReduceOp.MAX, group=group)
+    index = torch.nonzero(union, as_tuple=False).squeeze(1)
+    count = int(index.numel())
+    if count == 0:
+        return 0
+    for g in tensors:
+        if g.shape[0] != n:
+            raise ValueError("every gradient tensor needs one leading row per Gaussian")
+        flat = g.view(n, -1)
+        packed = flat.index_select(0, index)
+        dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+        flat.index_copy_(0, index, packed)
+    return count
+
+
 def max_over_ranks(value: float, device=None) -> float:
     """Maximum of a host scalar over all ranks (timings are reported as the slowest rank's)."""
     import torch

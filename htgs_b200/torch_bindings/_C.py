@@ -111,6 +111,20 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
     return image, per_primitive, per_tile, per_instance, per_pixel, int(n_inst.value), 0
 
 
+def forward_visibility(per_primitive_buffers, n_primitives: int):
+    """Bool tensor [N]: the Gaussians the training forward that filled `per_primitive_buffers` kept (the only rows of the
+    gradient tensors its backward pass can make non-zero).  No counterpart in the reference."""
+    device = per_primitive_buffers.device
+    visible = torch.empty(n_primitives, dtype=torch.uint8, device=device)
+    scene = _native.HtgsScene()
+    scene.n_primitives = n_primitives
+    blobs = _native.HtgsTrainBlobs(per_primitive_buffers.data_ptr(), per_primitive_buffers.numel(), None, 0, None, 0, None, 0)
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        _native.check(_native.lib().htgs_forward_visibility(ctypes.byref(scene), ctypes.byref(blobs), visible.data_ptr(), stream))
+    return visible.view(torch.bool)
+
+
 def backward(densification_info, grad_image, image, positions, scales, rotations, opacities, sh_rest, per_primitive_buffers, per_tile_buffers,
              per_instance_buffers, per_pixel_buffers, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases, width, height, near_plane,
              far_plane, scale_modifier, n_instances, instance_primitive_indices_selector, use_distance_scaling):

@@ -184,6 +184,12 @@ size_t htgs_backward_scratch_bytes(const HtgsScene* scene);
 int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                   const float* grad_image, const float* image, const HtgsGradients* grads, void* stream);
 
+/* Which Gaussians the training forward kept: visible[i] = 1 when Gaussian i passed culling and touches a tile (these are
+ * the only rows of the six gradient tensors the backward pass can make non-zero), else 0.  Reads the per-Gaussian blob
+ * htgs_forward_begin filled.  No counterpart in the reference; multi-GPU training uses it to exchange only the rows some
+ * rank can have touched.  Stream-ordered, no host synchronisation. */
+int htgs_forward_visibility(const HtgsScene* scene, const HtgsTrainBlobs* blobs, uint8_t* visible, void* stream);
+
 /*
  * Backward pass that allocates nothing.  No counterpart in the reference.
  *

@@ -127,3 +127,29 @@ def test_random_training_cases_against_reference_extension(seed):
     if c["rows"]:
         scale = r_dens.abs().max().item()
         assert (dens - r_dens).abs().max().item() <= 1e-3 * max(scale, 1e-12), c
+
+
+@pytest.mark.parametrize("mode,K", [(0, 8), (2, 1)])
+def test_training_visibility_covers_every_nonzero_gradient_row(mode, K):
+    """`last_training_visibility` is what multi-GPU training exchanges gradient rows by: it must equal the forward's own
+    per-Gaussian tile counts, and no gradient row outside it may be non-zero."""
+    import torch
+    from htgs_b200.torch_bindings import rasterization
+    scene = scenes.outdoor_scene(n=20_000, n_views=3, seed=5, width=200, height=120, focal=180.0)   # part of the scene is outside the view
+    view = scene.views[1]
+    rasterization.track_training_visibility(True)
+    try:
+        image, grads, _ = run_training_step(harness.ours(), scene, view, mode, K)
+        visible = rasterization.last_training_visibility("cuda")
+    finally:
+        rasterization.track_training_visibility(False)
+    assert visible.dtype == torch.bool and visible.shape == (scene.n,)
+    harness.ours().rasterize(*harness.scene_tensors(scene), harness.settings_for(harness.ours(), scene, view, mode, K), True, False)
+    from htgs_b200.torch_bindings import _C
+    inter = harness.our_intermediates(0, scene.n, _C.last_frame_info.n_instances)
+    assert np.array_equal(visible.cpu().numpy(), inter["n_touched"] > 0)
+    assert 0 < int(visible.sum()) < scene.n
+    for g in grads:
+        assert float(g[~visible].abs().max()) == 0.0
+    with pytest.raises(RuntimeError):
+        rasterization.last_training_visibility("cuda")

@@ -44,6 +44,43 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
+def _rows_worker(rank, world, port, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist = parallel.init_process_group("gloo")
+    n = 500
+    gen = torch.Generator().manual_seed(77)             # the same draws on both ranks: every rank can rebuild the other's data
+    keep = [torch.rand(n, generator=gen) < 0.2 for _ in range(world)]
+    data = [[torch.randn((n, 3), generator=gen), torch.randn((n, 5, 3), generator=gen), torch.randn((n, 1), generator=gen)] for _ in range(world)]
+    for r in range(world):
+        for t in data[r]:
+            t[~keep[r]] = 0.0                            # rows a rank's view did not keep are zero on that rank
+    mine = [t.clone() for t in data[rank]] + [None]
+    count = parallel.allreduce_gradients_rows(mine, keep[rank])
+    expected = [sum(data[r][i] for r in range(world)) for i in range(3)]
+    union = torch.stack(keep).any(0)
+    ok = count == int(union.sum()) and all(torch.equal(a, b) for a, b in zip(mine[:3], expected))
+    empty = parallel.allreduce_gradients_rows([torch.zeros((n, 3))], torch.zeros(n, dtype=torch.bool))
+    out.put((rank, ok, empty))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_row_exchange_equals_dense_sum_two_gloo_ranks():
+    """Summing only the rows of the union of the ranks' kept Gaussians gives exactly the dense all-reduce's result."""
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rows_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok, empty in results:
+        assert ok and empty == 0
+
+
 def test_allreduce_and_timing_reduction_two_gloo_ranks():
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
