@@ -190,10 +190,13 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
             l.grad = None
         act_scales, act_rotations, act_opacities = activate(leaves[1], leaves[2], leaves[3])
         image = mod.diff_rasterize(leaves[0], act_scales, act_rotations, act_opacities, leaves[4], leaves[5], empty, settings(cams_dev[vi]), False)
+        if sparse:     # the union of the ranks' visible sets is formed on a side stream while the forward still blends
+            visible, ready = rasterization.last_training_visibility(device, with_event=True)
+            exchange = parallel.begin_row_exchange(visible, ready=ready)
         loss = (image - target).abs().mean()
         loss.backward()
         if sparse:
-            exchanged_rows.append(parallel.allreduce_gradients_rows([l.grad for l in leaves], rasterization.last_training_visibility(device)))
+            exchanged_rows.append(parallel.finish_row_exchange([l.grad for l in leaves], exchange))
         elif dist is not None:
             parallel.allreduce_gradients([l.grad for l in leaves])
         return loss

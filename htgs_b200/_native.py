@@ -29,6 +29,10 @@ class HtgsScene(ctypes.Structure):
     ]
 
 
+class HtgsRowTensors(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p * 8), ("width", ctypes.c_int32 * 8), ("n_tensors", ctypes.c_int32)]
+
+
 class HtgsView(ctypes.Structure):
     _fields_ = [
         ("M", ctypes.c_void_p), ("VPM", ctypes.c_void_p), ("cam_position", ctypes.c_void_p),
@@ -129,6 +133,8 @@ def lib():
                 l.htgs_backward.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(HtgsTrainBlobs),
                                             ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(HtgsGradients), ctypes.c_void_p]
                 l.htgs_backward_static.argtypes = l.htgs_backward.argtypes
+                l.htgs_gather_rows.argtypes = [ctypes.POINTER(HtgsRowTensors), ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+                l.htgs_scatter_rows.argtypes = l.htgs_gather_rows.argtypes
                 l.htgs_forward_visibility.argtypes = [ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsTrainBlobs), ctypes.c_void_p, ctypes.c_void_p]
                 l.htgs_update_max_weights.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_float,
                                                       ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.POINTER(HtgsFrameInfo)]

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libhtgs_b200.so")
-SOURCES = ["api.cu", "preprocess.cu", "binning.cu", "binning_unordered.cu", "blend.cu", "blend_fast.cu", "train.cu", "noalloc.cu", "filter3d.cu", "weights.cu", "activation.cu"]
+SOURCES = ["api.cu", "preprocess.cu", "binning.cu", "binning_unordered.cu", "blend.cu", "blend_fast.cu", "train.cu", "noalloc.cu", "filter3d.cu", "weights.cu", "activation.cu", "exchange.cu"]
 HEADERS = ["common.cuh", "kernels.h", os.path.join("..", "..", "include", "htgs_b200.h")]
 
 # IEEE division / sqrt and no fast-math: the per-fragment arithmetic has to round exactly like

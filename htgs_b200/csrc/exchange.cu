@@ -1,0 +1,84 @@
+// Packing of per-Gaussian rows for the multi-GPU gradient exchange.  No counterpart in the reference (it is single-GPU).
+//
+// A training view keeps about a sixth of a scene's Gaussians and its backward pass leaves every other row of the six
+// gradient tensors zero, so the ranks only have to sum the rows of Gaussians SOME rank kept.  htgs_gather_rows copies
+// those rows of up to 8 row-major float tensors (widths 3, 3, 4, 1, 3, 3 B for the rasterizer's inputs) into one dense
+// [count, sum of widths] buffer, which one all-reduce sums; htgs_scatter_rows writes the sums back.  Both are pure
+// streaming kernels (one element per thread, consecutive threads on consecutive floats of a packed row): the packed side
+// is fully coalesced, the tensor side moves whole rows of 4 to 540 bytes.
+#include "kernels.h"
+
+extern "C" void htgs_set_last_error(const char* message);   // api.cu
+
+namespace htgs {
+
+namespace {
+
+constexpr int kRowBlock = 256;
+
+struct RowTable {
+    float* ptr[HTGS_MAX_ROW_TENSORS];
+    int32_t width[HTGS_MAX_ROW_TENSORS];
+    int32_t begin[HTGS_MAX_ROW_TENSORS + 1];   // first packed column of tensor k; begin[n_tensors] = packed row width
+    int32_t n_tensors;
+};
+
+template <bool GATHER>
+__global__ void __launch_bounds__(kRowBlock) move_rows_kernel(const __grid_constant__ RowTable table, const int64_t* __restrict__ index,
+                                                              uint64_t n_elements, float* __restrict__ packed) {
+    const uint32_t row_width = uint32_t(table.begin[table.n_tensors]);
+    for (uint64_t e = uint64_t(blockIdx.x) * kRowBlock + threadIdx.x; e < n_elements; e += uint64_t(gridDim.x) * kRowBlock) {
+        const uint64_t r = e / row_width;
+        const uint32_t c = uint32_t(e - r * row_width);
+        int k = 0;
+        #pragma unroll
+        for (int t = 1; t < HTGS_MAX_ROW_TENSORS; ++t) k += (t < table.n_tensors && c >= uint32_t(table.begin[t])) ? 1 : 0;
+        float* cell = table.ptr[k] + size_t(index[r]) * size_t(table.width[k]) + (c - uint32_t(table.begin[k]));
+        if (GATHER) packed[e] = *cell;
+        else *cell = packed[e];
+    }
+}
+
+int exchange_fail(int code, const char* message) { htgs_set_last_error(message); return code; }
+
+int move_rows(bool gather, const HtgsRowTensors* tensors, const int64_t* index, int64_t count, float* packed, void* stream) {
+    if (!tensors || count < 0 || tensors->n_tensors < 1 || tensors->n_tensors > HTGS_MAX_ROW_TENSORS)
+        return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "row exchange: null argument, negative count or too many tensors");
+    if (count == 0) return HTGS_OK;
+    if (!index || !packed) return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "row exchange: null index or packed buffer");
+    RowTable table{};
+    table.n_tensors = tensors->n_tensors;
+    int32_t begin = 0;
+    for (int k = 0; k < tensors->n_tensors; ++k) {
+        if (!tensors->data[k] || tensors->width[k] < 1) return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "row exchange: a tensor is null or has no columns");
+        table.ptr[k] = tensors->data[k];
+        table.width[k] = tensors->width[k];
+        table.begin[k] = begin;
+        begin += tensors->width[k];
+    }
+    table.begin[tensors->n_tensors] = begin;
+    const uint64_t n_elements = uint64_t(count) * uint64_t(begin);
+    const uint64_t blocks = (n_elements + kRowBlock - 1) / kRowBlock;
+    const uint32_t grid = uint32_t(blocks < (1u << 20) ? blocks : (1u << 20));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (gather) move_rows_kernel<true><<<grid, kRowBlock, 0, s>>>(table, index, n_elements, packed);
+    else move_rows_kernel<false><<<grid, kRowBlock, 0, s>>>(table, index, n_elements, packed);
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HTGS_OK : exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
+}
+
+}  // namespace
+
+}  // namespace htgs
+
+extern "C" {
+
+int htgs_gather_rows(const HtgsRowTensors* tensors, const int64_t* index, int64_t count, float* packed, void* stream) {
+    return htgs::move_rows(true, tensors, index, count, packed, stream);
+}
+
+int htgs_scatter_rows(const HtgsRowTensors* tensors, const int64_t* index, int64_t count, const float* packed, void* stream) {
+    return htgs::move_rows(false, tensors, index, count, const_cast<float*>(packed), stream);
+}
+
+}  // extern "C"

@@ -101,6 +101,13 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
         n_inst = ctypes.c_uint32()
         _native.check(lib.htgs_forward_begin(ctx, ctypes.byref(scene), ctypes.byref(view), per_primitive.data_ptr(), per_primitive.numel(), stream,
                                              ctypes.byref(n_inst)))
+        if track_visibility:     # before the rest of the forward is enqueued: the list is final and the stream is idle here
+            visible = torch.empty(n, dtype=torch.uint8, device=device)
+            head = _native.HtgsTrainBlobs(per_primitive.data_ptr(), per_primitive.numel(), None, 0, None, 0, None, 0)
+            _native.check(lib.htgs_forward_visibility(ctypes.byref(scene), ctypes.byref(head), visible.data_ptr(), stream))
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(device))
+            last_visibility[torch.device(device)] = (visible.view(torch.bool), ready)
         per_instance = torch.empty(lib.htgs_forward_instance_bytes(ctypes.byref(view), n_inst.value), **byte)
         blobs = _native.HtgsTrainBlobs(per_primitive.data_ptr(), per_primitive.numel(), per_tile.data_ptr(), per_tile.numel(),
                                        per_instance.data_ptr(), per_instance.numel(), per_pixel.data_ptr(), per_pixel.numel())
@@ -109,6 +116,12 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
                                               ctypes.byref(info)))
     last_frame_info = info
     return image, per_primitive, per_tile, per_instance, per_pixel, int(n_inst.value), 0
+
+
+# When set, every training forward leaves (bool tensor [N] of the Gaussians it kept, event recorded after the tensor was
+# written) here, per device; see torch_bindings.rasterization.track_training_visibility.
+track_visibility = False
+last_visibility: dict = {}
 
 
 def forward_visibility(per_primitive_buffers, n_primitives: int):

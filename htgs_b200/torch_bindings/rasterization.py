@@ -41,25 +41,23 @@ class RasterizerSettings(NamedTuple):
 
 
 # Multi-GPU training exchanges only the gradient rows some rank can have touched (htgs_b200.parallel): when tracking is on,
-# every training forward leaves the visibility of its Gaussians here, per device.  No counterpart in the reference.
-_track_visibility = False
-_last_visibility: dict = {}
-
-
+# every training forward leaves the visibility of its Gaussians, per device.  No counterpart in the reference.
 def track_training_visibility(enable: bool) -> None:
-    global _track_visibility
-    _track_visibility = bool(enable)
+    _C.track_visibility = bool(enable)
     if not enable:
-        _last_visibility.clear()
+        _C.last_visibility.clear()
 
 
-def last_training_visibility(device) -> torch.Tensor:
-    """Bool tensor [N] of the last `diff_rasterize` forward on `device` (needs track_training_visibility(True))."""
+def last_training_visibility(device, with_event: bool = False):
+    """Bool tensor [N] of the Gaussians the last `diff_rasterize` forward on `device` kept (needs
+    track_training_visibility(True)); with `with_event` also the CUDA event recorded once the tensor was written, which is
+    early in the forward (after the preprocess pass), so that a side stream can use it while the forward still runs."""
     key = torch.device(device)
     key = torch.device("cuda", torch.cuda.current_device()) if key.type == "cuda" and key.index is None else key
-    if key not in _last_visibility:
+    if key not in _C.last_visibility:
         raise RuntimeError("no training forward was tracked on this device: call track_training_visibility(True) first")
-    return _last_visibility[key]
+    visible, ready = _C.last_visibility[key]
+    return (visible, ready) if with_event else visible
 
 
 class _Rasterize(torch.autograd.Function):
@@ -68,8 +66,6 @@ class _Rasterize(torch.autograd.Function):
                 rasterizer_settings: RasterizerSettings, use_distance_scaling: bool) -> torch.Tensor:
         image, per_primitive_buffers, per_tile_buffers, per_instance_buffers, per_pixel_buffers, n_instances, selector = _C.forward(
             positions, scales, rotations, opacities, sh_0, sh_rest, *rasterizer_settings.as_tuple())
-        if _track_visibility:
-            _last_visibility[positions.device] = _C.forward_visibility(per_primitive_buffers, positions.shape[0])
         ctx.rasterizer_settings = rasterizer_settings
         ctx.n_instances = n_instances
         ctx.instance_primitive_indices_selector = selector

@@ -190,6 +190,20 @@ int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view
  * rank can have touched.  Stream-ordered, no host synchronisation. */
 int htgs_forward_visibility(const HtgsScene* scene, const HtgsTrainBlobs* blobs, uint8_t* visible, void* stream);
 
+/* Packing of per-Gaussian rows for the multi-GPU gradient exchange.  No counterpart in the reference.
+ * `tensors` are row-major float tensors with one row per Gaussian (e.g. the six gradients, widths 3, 3, 4, 1, 3, 3 B);
+ * htgs_gather_rows copies rows index[0..count) of all of them into packed[count][sum of widths] (tensor after tensor inside
+ * a packed row), htgs_scatter_rows copies packed rows back.  `index` (device memory) must hold distinct rows for the
+ * scatter.  Stream-ordered, no host synchronisation. */
+#define HTGS_MAX_ROW_TENSORS 8
+typedef struct HtgsRowTensors {
+    float* data[HTGS_MAX_ROW_TENSORS];
+    int32_t width[HTGS_MAX_ROW_TENSORS];
+    int32_t n_tensors;
+} HtgsRowTensors;
+int htgs_gather_rows(const HtgsRowTensors* tensors, const int64_t* index, int64_t count, float* packed, void* stream);
+int htgs_scatter_rows(const HtgsRowTensors* tensors, const int64_t* index, int64_t count, const float* packed, void* stream);
+
 /*
  * Backward pass that allocates nothing.  No counterpart in the reference.
  *

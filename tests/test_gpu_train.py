@@ -153,3 +153,39 @@ def test_training_visibility_covers_every_nonzero_gradient_row(mode, K):
         assert float(g[~visible].abs().max()) == 0.0
     with pytest.raises(RuntimeError):
         rasterization.last_training_visibility("cuda")
+
+
+def test_row_gather_and_scatter_kernels_match_index_select():
+    """htgs_gather_rows / htgs_scatter_rows (the packing of the multi-GPU gradient exchange) against torch indexing."""
+    import ctypes
+    import torch
+    from htgs_b200 import _native
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    n = 10_000
+    shapes = [(n, 3), (n, 3), (n, 4), (n, 1), (n, 1, 3), (n, 15, 3)]
+    tensors = [torch.randn(s, generator=gen).cuda() for s in shapes]
+    index = torch.nonzero(torch.rand(n, generator=gen) < 0.2).squeeze(1).cuda()
+    count = int(index.numel())
+    table = _native.HtgsRowTensors()
+    table.n_tensors = len(tensors)
+    for k, t in enumerate(tensors):
+        table.data[k] = t.data_ptr()
+        table.width[k] = t[0].numel()
+    width = sum(t[0].numel() for t in tensors)
+    packed = torch.full((count, width), float("nan"), device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    _native.check(_native.lib().htgs_gather_rows(ctypes.byref(table), index.data_ptr(), count, packed.data_ptr(), stream))
+    expected = torch.cat([t.view(n, -1).index_select(0, index) for t in tensors], dim=1)
+    assert torch.equal(packed, expected)
+    before = [t.clone() for t in tensors]
+    packed.mul_(2.0)
+    _native.check(_native.lib().htgs_scatter_rows(ctypes.byref(table), index.data_ptr(), count, packed.data_ptr(), stream))
+    torch.cuda.synchronize()
+    for t, b in zip(tensors, before):
+        want = b.clone()
+        want[index] = 2.0 * b[index]
+        assert torch.equal(t, want)
+    # nothing to move, and argument errors
+    assert _native.lib().htgs_gather_rows(ctypes.byref(table), None, 0, None, stream) == 0
+    table.n_tensors = 9
+    assert _native.lib().htgs_gather_rows(ctypes.byref(table), index.data_ptr(), count, packed.data_ptr(), stream) != 0
