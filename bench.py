@@ -185,7 +185,7 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
     exchanged_rows = []
 
     def step(s):
-        vi = parallel.step_view_indices(s, 1, rank, world, n_views)[0]
+        vi = (s + rank * (n_views // world)) % n_views      # the views of a step are spread evenly over the orbit, as a random batch would be
         for l in leaves:
             l.grad = None
         act_scales, act_rotations, act_opacities = activate(leaves[1], leaves[2], leaves[3])
@@ -230,7 +230,7 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
             "config": {"workload": workload_name.replace("config1", "config2 (fwd+bwd, L1, one view per GPU)"), "views_per_step": world,
                        "allreduce_bytes_per_rank": grad_bytes if world > 1 else 0,
                        "gradient_exchange": ("none" if world == 1 else "rows of the union of the ranks' visible Gaussians" if sparse else "dense tensors"),
-                       "views_per_s": world * args.steps / (ms / 1000.0), "parallelism": f"view-partitioned x{world} + gradient all-reduce"},
+                       "views_per_s": world * args.steps / (ms / 1000.0), "views_of_a_step": "spread evenly over the orbit", "parallelism": f"view-partitioned x{world} + gradient all-reduce"},
             "clocks": clocks, "final_loss": float(loss.item())}
     if is_reference:
         line["impl"] = "reference"

@@ -60,6 +60,12 @@ def _rows_worker(rank, world, port, out):
     union = torch.stack(keep).any(0)
     ok = count == int(union.sum()) and all(torch.equal(a, b) for a, b in zip(mine[:3], expected))
     empty = parallel.allreduce_gradients_rows([torch.zeros((n, 3))], torch.zeros(n, dtype=torch.bool))
+    # a union above parallel.kDenseAbove of the rows switches to the dense all-reduce: same result
+    wide = torch.rand(n, generator=gen) < 0.9
+    full = [torch.full((n, 2), float(r + 1)) * wide[:, None] for r in range(world)]
+    mine = full[rank].clone()
+    moved = parallel.allreduce_gradients_rows([mine], wide)
+    ok = ok and moved == n and torch.equal(mine, sum(full))
     out.put((rank, ok, empty))
     dist.barrier()
     dist.destroy_process_group()
