@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--streams", type=int, default=0,
                     help="frames in flight per GPU on this library's arm (host threads, one CUDA stream each); 0 = 2 if the host has at least 3 hardware threads per rank, else 1")
     ap.add_argument("--n-gaussians", type=int, default=3_000_000, help="scale the workload down for quick checks (invalid as a benchmark)")
+    ap.add_argument("--blend-mode", type=int, default=0, choices=[0, 1, 2, 3], help="0 HYBRID_BLEND (the benchmark), 1 FIRST_K, 2 GLOBAL_ORDERING, 3 OIT: for profiling the other modes' kernels")
+    ap.add_argument("--k", type=int, default=16, choices=[1, 2, 4, 8, 16, 32], help="K of HYBRID_BLEND / FIRST_K (16 is the benchmark)")
     ap.add_argument("--workload", default="render", choices=["render", "render_fast", "train"],
                     help="render: configuration 1 (default, the headline metric); train: configuration 2 (fwd+bwd, L1 loss, one view per GPU, gradient all-reduce)")
     ap.add_argument("--exchange", default="rows", choices=["rows", "dense"],
@@ -115,10 +117,14 @@ def load_measured_peaks():
     return 6650.0, "fallback"
 
 
+MODE_NAMES = ["HYBRID_BLEND", "ALPHA_BLEND_FIRST_K", "ALPHA_BLEND_GLOBAL_ORDERING", "OIT_BLEND"]
+
+
 def make_workload(args):
-    scene = scenes.outdoor_scene(n=args.n_gaussians, n_views=200)
-    name = "config1: 3M Gaussians SH3, 1297x840, HYBRID_BLEND K=16, 200 orbit views" if args.n_gaussians == 3_000_000 else \
-        f"REDUCED config1 ({args.n_gaussians} Gaussians) - not a benchmark number"
+    scene = scenes.outdoor_scene(n=args.n_gaussians, n_views=200, mode=args.blend_mode, K=args.k)
+    headline = args.n_gaussians == 3_000_000 and args.blend_mode == 0 and args.k == 16
+    name = "config1: 3M Gaussians SH3, 1297x840, HYBRID_BLEND K=16, 200 orbit views" if headline else \
+        f"VARIANT of config1 ({args.n_gaussians} Gaussians, {MODE_NAMES[args.blend_mode]} K={args.k}) - not the benchmark number"
     return scene, name
 
 
@@ -538,7 +544,7 @@ def main():
     blend_ms = stage_ms[5]
     bin_ms = stage_ms[1] + stage_ms[2] + stage_ms[3] + stage_ms[4]
     line["roofline"] = {
-        "kernel": "blend_fast_kernel<16>" if fast else "blend_kernel<HYBRID_BLEND,16>", "bound": "fp32",
+        "kernel": f"blend_fast_kernel<{MODE_NAMES[scene.mode]},{scene.K}>" if fast else f"blend_kernel<{MODE_NAMES[scene.mode]},{scene.K}>", "bound": "fp32",
         "achieved": blend_flops / (blend_ms * 1e-3) / 1e12, "peak": fp32_peak_tflops, "unit": "TFLOP/s",
         "frac": blend_flops / (blend_ms * 1e-3) / 1e12 / fp32_peak_tflops,
         "peak_source": f"{sm_count} SMs x 128 FP32 lanes x 2 x {sm_mhz:.0f} MHz (SM clock sampled during the timed region); no tensor-core work on this path",
