@@ -149,6 +149,7 @@ def lib():
                 l.htgs_set_profiling.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_set_collect_stats.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_set_fast_deterministic.argtypes = [ctypes.c_void_p, ctypes.c_int]
+                l.htgs_set_front_priority.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_get_stage_ms.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]
                 l.htgs_memcpy_d2h.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
                 l.htgs_memcpy_h2d.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]

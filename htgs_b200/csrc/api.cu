@@ -129,6 +129,12 @@ struct HtgsContext {
     bool fast_deterministic = false;        // htgs_render_fast: ordered (radix sort) instead of unordered (atomic) binning
     cudaEvent_t events[8] = {};
     bool events_created = false;
+    // With several frames in flight on one GPU (one context and stream per host thread), the short kernels at the front of a
+    // frame (preprocess, scans, sort) go to a stream of the highest priority, so that the block scheduler places them ahead of
+    // the queued CTAs of ANOTHER frame's blend kernel instead of behind all of them; the blend stays on the caller's stream.
+    bool front_priority = true;             // htgs_set_front_priority
+    cudaStream_t front_stream = nullptr;
+    cudaEvent_t front_begin = nullptr, front_end = nullptr;
     float stage_ms[HTGS_N_STAGES] = {};
 };
 
@@ -165,6 +171,9 @@ void htgs_destroy(HtgsContext* ctx) {
     if (ctx->host_path_stream) cudaStreamDestroy(ctx->host_path_stream);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
     if (ctx->events_created) for (auto& e : ctx->events) cudaEventDestroy(e);
+    if (ctx->front_stream) cudaStreamDestroy(ctx->front_stream);
+    if (ctx->front_begin) cudaEventDestroy(ctx->front_begin);
+    if (ctx->front_end) cudaEventDestroy(ctx->front_end);
     delete ctx;
 }
 
@@ -186,6 +195,21 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
     }
     cudaEvent_t* ev = ctx->events;   // 0 start, 1 preprocess, 2 scan, 3 emit, 4 sort, 5 ranges, 6 blend
     out.collect_stats = ctx->collect_stats;
+    cudaStream_t const caller_stream = stream;
+    const bool front_priority = ctx->front_priority;
+    if (front_priority) {
+        if (!ctx->front_stream) {
+            int least = 0, greatest = 0;
+            if ((err = cudaDeviceGetStreamPriorityRange(&least, &greatest)) != cudaSuccess) return fail_cuda(err, "stream priority range");
+            if ((err = cudaStreamCreateWithPriority(&ctx->front_stream, cudaStreamNonBlocking, greatest)) != cudaSuccess) return fail_cuda(err, "front stream");
+            if ((err = cudaEventCreateWithFlags(&ctx->front_begin, cudaEventDisableTiming)) != cudaSuccess) return fail_cuda(err, "front event");
+            if ((err = cudaEventCreateWithFlags(&ctx->front_end, cudaEventDisableTiming)) != cudaSuccess) return fail_cuda(err, "front event");
+        }
+        // everything the caller queued before this call (camera upload, the previous frame) comes first
+        if ((err = cudaEventRecord(ctx->front_begin, caller_stream)) != cudaSuccess) return fail_cuda(err, "front event record");
+        if ((err = cudaStreamWaitEvent(ctx->front_stream, ctx->front_begin, 0)) != cudaSuccess) return fail_cuda(err, "front stream wait");
+        stream = ctx->front_stream;
+    }
     if ((err = cudaMemsetAsync(L.status, 0, sizeof(FrameStatus), stream)) != cudaSuccess) return fail_cuda(err, "status reset");
     if (prof) cudaEventRecord(ev[0], stream);
     if ((err = launch_preprocess(view.mode, false, scene, view, geo, L.prim, L.status, stream, fast)) != cudaSuccess) return fail_cuda(err, "preprocess");
@@ -199,6 +223,11 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
                                         stream, prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "unordered binning");
     } else if ((err = launch_emit_sort_ranges(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream,
                                               prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "binning");
+    if (front_priority) {
+        if ((err = cudaEventRecord(ctx->front_end, stream)) != cudaSuccess) return fail_cuda(err, "front event record");
+        if ((err = cudaStreamWaitEvent(caller_stream, ctx->front_end, 0)) != cudaSuccess) return fail_cuda(err, "caller stream wait");
+        stream = caller_stream;
+    }
     if (max_weights) {
         if ((err = launch_max_weights(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, max_weights, weight_threshold, stream)) != cudaSuccess) return fail_cuda(err, "max weights");
     } else if (fast) {
@@ -341,6 +370,12 @@ int htgs_set_profiling(HtgsContext* ctx, int enable) {
 int htgs_get_stage_ms(HtgsContext* ctx, float* out_ms) {
     if (!ctx || !out_ms) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     for (int i = 0; i < HTGS_N_STAGES; ++i) out_ms[i] = ctx->stage_ms[i];
+    return HTGS_OK;
+}
+
+int htgs_set_front_priority(HtgsContext* ctx, int enable) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    ctx->front_priority = enable != 0;
     return HTGS_OK;
 }
 

@@ -297,6 +297,11 @@ enum HtgsStage {
     HTGS_STAGE_PREPROCESS = 0, HTGS_STAGE_SCAN = 1, HTGS_STAGE_EMIT = 2, HTGS_STAGE_SORT = 3,
     HTGS_STAGE_RANGES = 4, HTGS_STAGE_BLEND = 5, HTGS_STAGE_TOTAL = 6, HTGS_N_STAGES = 7
 };
+/* Frames of several contexts in flight on one GPU: by default the short kernels at the front of a frame (preprocess, scans,
+ * sort) run on a context-owned stream of the highest priority, ordered after everything queued on the caller's stream
+ * before the call and before the blend kernel, which stays on the caller's stream; the block scheduler then places them
+ * ahead of the queued CTAs of another frame's blend kernel.  Results do not change.  0 keeps every kernel on the caller's stream. */
+int htgs_set_front_priority(HtgsContext* ctx, int enable);
 int htgs_set_profiling(HtgsContext* ctx, int enable);
 int htgs_get_stage_ms(HtgsContext* ctx, float* out_ms);
 int htgs_set_collect_stats(HtgsContext* ctx, int enable);

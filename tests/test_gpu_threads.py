@@ -65,3 +65,27 @@ def test_contexts_are_per_thread():
         t.join()
     assert seen["a"] != seen["b"] != _native.context(0)
     assert _native.context(0) == _native.context(0)
+
+
+def test_front_priority_switch_leaves_results_unchanged():
+    """htgs_set_front_priority only moves the front of a frame to another stream: same image and depth, bit for bit, also
+    when the caller's stream has unfinished work queued ahead of the frame (the scene upload here)."""
+    import torch
+    from htgs_b200 import _native
+    scene = scenes.tiny_scene(n=20_000, size=160, seed=12, sh_degree=2)
+    view = scene.views[0]
+    results = []
+    ctx = _native.context(0)
+    try:
+        for enable in (1, 0, 1):
+            _native.check(_native.lib().htgs_set_front_priority(ctx, enable))
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                tensors = [torch.from_numpy(np.ascontiguousarray(a)).pin_memory().to("cuda", non_blocking=True) for a in scene.arrays()]
+                img, depth = harness.ours().rasterize(*tensors, harness.settings_for(harness.ours(), scene, view, 0, 16), True, False)
+            side.synchronize()
+            results.append((img.clone(), depth.clone()))
+    finally:
+        _native.check(_native.lib().htgs_set_front_priority(ctx, 1))
+    for img, depth in results[1:]:
+        assert torch.equal(img, results[0][0]) and torch.equal(depth, results[0][1])
