@@ -276,7 +276,19 @@ def main():
     device = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
-        dist = parallel.init_process_group("nccl")
+        # NCCL announces its version on standard output when its communicator is created (NCCL_DEBUG=VERSION and above):
+        # create it here, with descriptor 1 pointed at standard error, so that the JSON line is the only line on stdout.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist = parallel.init_process_group("nccl")
+            dist.all_reduce(torch.zeros(1, device=device))
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     if ref_mod is not None:
         mod = ref_mod
