@@ -111,6 +111,8 @@ struct BackwardOutputs {
 cudaError_t launch_visibility(const uint32_t* n_touched, uint8_t* visible, uint32_t n, cudaStream_t stream);
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
                             const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
-                            const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, int sm_count, cudaStream_t stream);
+                            const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, cudaEvent_t outputs_cleared, int sm_count,
+                            cudaStream_t stream);   // `outputs_cleared`: event after which the six tensors are zero, or null to clear them here
+cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs& out, cudaStream_t stream);
 
 }  // namespace htgs

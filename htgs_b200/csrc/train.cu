@@ -733,21 +733,29 @@ cudaError_t launch_visibility(const uint32_t* n_touched, uint8_t* visible, uint3
     return cudaGetLastError();
 }
 
+cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs& out, cudaStream_t stream) {
+    const size_t n = size_t(scene.n_primitives), B = size_t(scene.total_sh_bases);
+    if (n == 0) return cudaSuccess;
+    cudaError_t err;
+    if ((err = cudaMemsetAsync(out.grad_positions, 0, n * 3 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_scales, 0, n * 3 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_rotations, 0, n * 4 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_opacities, 0, n * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_sh_0, 0, n * 3 * 4, stream)) != cudaSuccess) return err;
+    if (B && (err = cudaMemsetAsync(out.grad_sh_rest, 0, n * B * 3 * 4, stream)) != cudaSuccess) return err;
+    return cudaSuccess;
+}
+
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
                             const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
-                            const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, int sm_count, cudaStream_t stream) {
+                            const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, cudaEvent_t outputs_cleared, int sm_count,
+                            cudaStream_t stream) {
     (void)sm_count;
     const uint32_t n = uint32_t(scene.n_primitives);
     if (n == 0) return cudaSuccess;
     cudaError_t err = cudaMemsetAsync(acc.accum, 0, size_t(n) * 5 * sizeof(float4), stream);
     if (err != cudaSuccess) return err;
-    const size_t B = size_t(scene.total_sh_bases);
-    if ((err = cudaMemsetAsync(out.grad_positions, 0, size_t(n) * 3 * 4, stream)) != cudaSuccess) return err;
-    if ((err = cudaMemsetAsync(out.grad_scales, 0, size_t(n) * 3 * 4, stream)) != cudaSuccess) return err;
-    if ((err = cudaMemsetAsync(out.grad_rotations, 0, size_t(n) * 4 * 4, stream)) != cudaSuccess) return err;
-    if ((err = cudaMemsetAsync(out.grad_opacities, 0, size_t(n) * 4, stream)) != cudaSuccess) return err;
-    if ((err = cudaMemsetAsync(out.grad_sh_0, 0, size_t(n) * 3 * 4, stream)) != cudaSuccess) return err;
-    if (B && (err = cudaMemsetAsync(out.grad_sh_rest, 0, size_t(n) * B * 3 * 4, stream)) != cudaSuccess) return err;
+    if (outputs_cleared == nullptr && (err = clear_backward_outputs(scene, out, stream)) != cudaSuccess) return err;
     const bool abs_grad = out.densification_info != nullptr && out.densification_rows == 3;
     const int k = effective_k(mode, K);
     switch (mode) {
@@ -767,6 +775,7 @@ cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsV
         default: return cudaErrorInvalidValue;
     }
     if (err != cudaSuccess) return err;
+    if (outputs_cleared != nullptr && (err = cudaStreamWaitEvent(stream, outputs_cleared, 0)) != cudaSuccess) return err;
     preprocess_backward_kernel<<<(n + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
                                                                     view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
                                                                     view.active_sh_bases, scene.total_sh_bases);
