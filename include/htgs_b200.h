@@ -193,8 +193,9 @@ int htgs_forward_visibility(const HtgsScene* scene, const HtgsTrainBlobs* blobs,
 /* Packing of per-Gaussian rows for the multi-GPU gradient exchange.  No counterpart in the reference.
  * `tensors` are row-major float tensors with one row per Gaussian (e.g. the six gradients, widths 3, 3, 4, 1, 3, 3 B);
  * htgs_gather_rows copies rows index[0..count) of all of them into packed[count][sum of widths] (tensor after tensor inside
- * a packed row), htgs_scatter_rows copies packed rows back.  `index` (device memory) must hold distinct rows for the
- * scatter.  Stream-ordered, no host synchronisation. */
+ * a packed row), htgs_scatter_rows copies packed rows back.  `index` (device memory) must hold row numbers inside the
+ * tensors (they live on the device and are not checked) and distinct ones for the scatter.  Stream-ordered, no host
+ * synchronisation. */
 #define HTGS_MAX_ROW_TENSORS 8
 typedef struct HtgsRowTensors {
     float* data[HTGS_MAX_ROW_TENSORS];
