@@ -30,7 +30,7 @@
 #include "kernels.h"
 
 #ifndef HTGS_EXPERIMENT
-#define HTGS_EXPERIMENT 0   // timing experiments only (wrong images): 1 no insertion, 2 / 4 no exact pass (4 keeps the masks), 3 staging only
+#define HTGS_EXPERIMENT 0   // timing experiments only (1-4 give wrong images): 1 no insertion, 2 / 4 no exact pass (4 keeps the masks), 3 staging only; -1 shared-memory padding (right images)
 #endif
 
 namespace htgs {
@@ -76,7 +76,7 @@ template <int MODE, int K, bool TRAIN> struct SmemLayout {
     static constexpr size_t pool_bytes = has_kbuffer ? size_t(K + 1) * TS::threads * pool_elem : 0;
     static constexpr size_t pool_idx_off = pool_off + pool_bytes;
     static constexpr size_t pool_idx_bytes = has_pool_idx ? size_t(K + 1) * TS::threads * 4 : 0;
-    static constexpr size_t total = pool_idx_off + pool_idx_bytes;
+    static constexpr size_t total = pool_idx_off + pool_idx_bytes + (HTGS_EXPERIMENT == -1 ? 6400 : 0);   // -1: padding that costs two resident CTAs per SM (HYBRID K=16)
 };
 
 // The shared per-fragment front end (hybrid_blend/kernels/inference.cuh:137-148).
