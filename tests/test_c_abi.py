@@ -48,3 +48,12 @@ def test_wrong_dtype_is_rejected():
     bad = [torch.zeros(n, 3, dtype=torch.float64), torch.ones(n, 3), torch.zeros(n, 4), torch.ones(n, 1), torch.zeros(n, 1, 3), torch.zeros(n, 0, 3)]
     with pytest.raises((TypeError, ValueError)):
         _C._check_inputs(*bad, torch.eye(4), torch.eye(4), torch.zeros(3))
+
+
+def test_training_visibility_needs_tracking():
+    """Asking for the visibility of a training forward that was never tracked is an error, not an empty answer."""
+    import pytest
+    from htgs_b200.torch_bindings import rasterization
+    rasterization.track_training_visibility(False)
+    with pytest.raises(RuntimeError):
+        rasterization.last_training_visibility("cuda:0")
