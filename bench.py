@@ -42,7 +42,12 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--views-per-step", type=int, default=8)
+    ap.add_argument("--views-per-step", type=int, default=24)
+    ap.add_argument("--driver", default="auto", choices=["auto", "async", "threads"],
+                    help="how this library's arm keeps two frames in flight: async = ONE host thread queueing frames on two CUDA streams without "
+                         "waiting (deferred status checks); threads = two host threads with blocking calls; auto = async")
+    ap.add_argument("--train-steps", type=int, default=0, help="steps of the training leg appended to the default workload (0 = --steps)")
+    ap.add_argument("--no-train-leg", action="store_true", help="default workload: skip the configuration-2 training leg")
     ap.add_argument("--streams", type=int, default=0,
                     help="frames in flight per GPU on this library's arm (host threads, one CUDA stream each); 0 = 2 if the host has at least 3 hardware threads per rank, else 1")
     ap.add_argument("--n-gaussians", type=int, default=3_000_000, help="scale the workload down for quick checks (invalid as a benchmark)")
@@ -160,10 +165,12 @@ def run_reference_cpu(args, scene, workload_name, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, device, dist, rank, world, workload_name):
+def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, device, dist, rank, world, workload_name, steps=None, warmup=None):
     """Configuration 2: one view per GPU per step, forward + backward through `diff_rasterize` with an L1 loss against a
     seeded uniform target, gradients of the six rasterizer inputs all-reduced over the ranks (NCCL)."""
     import torch
+    steps = args.steps if steps is None else steps
+    warmup = args.warmup if warmup is None else warmup
     n_views = len(scene.views)
     v0 = scene.views[0]
     gen = torch.Generator(device="cpu").manual_seed(1234)
@@ -207,7 +214,7 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
             parallel.allreduce_gradients([l.grad for l in leaves])
         return loss
 
-    for s in range(args.warmup):
+    for s in range(warmup):
         step(s)
     torch.cuda.synchronize()
     if dist is not None:
@@ -219,7 +226,7 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.time()
     e0.record()
-    for s in range(args.warmup, args.warmup + args.steps):
+    for s in range(warmup, warmup + steps):
         loss = step(s)
     e1.record()
     torch.cuda.synchronize()
@@ -228,23 +235,32 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
         dist.barrier()
     clocks = sampler.stop(t0, t1)
     ms = parallel.max_over_ranks(e0.elapsed_time(e1), device)
+    if sparse:
+        rasterization.track_training_visibility(False)
     n = scene.n
     row_bytes = (3 + 3 + 4 + 1 + 3 + 3 * scene.sh_rest.shape[1]) * 4
-    grad_bytes = int(np.mean(exchanged_rows[args.warmup:])) * row_bytes if sparse else n * row_bytes
-    line = {"metric": "train-steps/s", "value": args.steps / (ms / 1000.0), "unit": "steps/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+    grad_bytes = int(np.mean(exchanged_rows[warmup:])) * row_bytes if sparse else n * row_bytes
+    line = {"metric": "train-steps/s", "value": steps / (ms / 1000.0), "unit": "steps/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name.replace("config1", "config2 (fwd+bwd, L1, one view per GPU)"), "views_per_step": world,
                        "allreduce_bytes_per_rank": grad_bytes if world > 1 else 0,
                        "gradient_exchange": ("none" if world == 1 else "rows of the union of the ranks' visible Gaussians" if sparse else "dense tensors"),
-                       "views_per_s": world * args.steps / (ms / 1000.0), "views_of_a_step": "spread evenly over the orbit", "parallelism": f"view-partitioned x{world} + gradient all-reduce"},
+                       "views_per_s": world * steps / (ms / 1000.0), "views_of_a_step": "spread evenly over the orbit", "parallelism": f"view-partitioned x{world} + gradient all-reduce"},
             "clocks": clocks, "final_loss": float(loss.item())}
     if is_reference:
         line["impl"] = "reference"
-    if rank == 0:
-        print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    for l in leaves:
+        l.grad = None
+    return line
+
+
+def train_leg_summary(line):
+    """The training line folded into the `train` object of the default workload's JSON line."""
+    cfg = line["config"]
+    return {"metric": "train-steps/s", "steps_per_s": line["value"], "ms_per_step": line["ms_per_step"], "views_per_s": cfg["views_per_s"],
+            "exchange": {"none": "none", "dense tensors": "dense"}.get(cfg["gradient_exchange"], "rows"),
+            "allreduce_bytes_per_rank": cfg["allreduce_bytes_per_rank"], "n_gpus": line["n_gpus"], "steps": line["steps"], "warmup": line["warmup"],
+            "workload": cfg["workload"], "clocks": line["clocks"], "final_loss": line["final_loss"]}
 
 
 def main():
@@ -311,26 +327,49 @@ def main():
                                       width=v0.width, height=v0.height, near_plane=v0.near_plane, far_plane=v0.far_plane, scale_modifier=1.0)
 
     if args.workload == "train":
-        run_training(args, mod, ref_mod is not None, scene, tensors, cams_dev, settings, device, dist, rank, world, workload_name)
+        line = run_training(args, mod, ref_mod is not None, scene, tensors, cams_dev, settings, device, dist, rank, world, workload_name)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
         return
+
+    def train_leg():
+        """Configuration 2 behind the render timing of the default workload: the other half of the metric (train-steps/s)."""
+        if args.workload != "render" or args.no_train_leg:
+            return None
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        tl = run_training(args, mod, ref_mod is not None, scene, tensors, cams_dev, settings, device, dist, rank, world, workload_name,
+                          steps=args.train_steps or args.steps, warmup=max(args.warmup, 3))
+        return train_leg_summary(tl)
 
     fast = args.workload == "render_fast"   # the relaxed-precision RGB-only entry point (`fast_rasterize`) of either implementation
     if fast:
         workload_name = workload_name.replace("config1", "config1 via fast_rasterize (relaxed precision, RGB only)")
-    # Frames in flight.  This library's contexts are re-entrant (one per host thread, no global device state), so the job
-    # is driven by `--streams` host threads, each with its own CUDA stream, rendering alternate views: the small kernels and
-    # the tail of one frame overlap the next frame's work.  The reference keeps per-call state in module-global constant
-    # memory and a function-static stream (rasterization/include/kernel_utils.cuh:10-12), so its arm runs one frame at a time.
-    if args.streams > 0:
-        n_lanes = args.streams
+    # Frames in flight.  This library's contexts are re-entrant (no global device state), so two frames can be in flight on
+    # one GPU: the small kernels and the tail of one frame overlap the next frame's work.  Driver "async" (default): ONE host
+    # thread queues frames on two CUDA streams through the non-blocking path (`set_deferred_checks`: htgs_render_async, status
+    # checked one frame later).  Driver "threads": `--streams` host threads with blocking calls, one CUDA stream each.  The
+    # reference keeps per-call state in module-global constant memory and a function-static stream
+    # (rasterization/include/kernel_utils.cuh:10-12) and blocks in mid-frame, so its arm runs one frame at a time.
+    driver = "async" if args.driver == "auto" else args.driver
+    if driver == "threads":
+        if args.streams > 0:
+            n_lanes = args.streams
+        else:
+            try:
+                host_threads = len(os.sched_getaffinity(0))
+            except AttributeError:
+                host_threads = os.cpu_count() or 1
+            n_lanes = 2 if host_threads >= 3 * world else 1   # a lane's thread busy-waits on its stream: do not oversubscribe the host
     else:
-        try:
-            host_threads = len(os.sched_getaffinity(0))
-        except AttributeError:
-            host_threads = os.cpu_count() or 1
-        n_lanes = 2 if host_threads >= 3 * world else 1   # a lane's thread busy-waits on its stream: do not oversubscribe the host
+        n_lanes = args.streams if args.streams > 0 else 2
     if ref_mod is not None:
         n_lanes = 1
+    if n_lanes == 1:
+        driver = "single"
 
     def render_any(cam):
         if fast:
@@ -352,7 +391,7 @@ def main():
 
         def resident(self, view_idx):
             render_any(cams_dev[view_idx])
-            if ref_mod is None:
+            if ref_mod is None and not our_C.deferred_checks:
                 self.launches += our_C.last_frame_info.kernel_launches
 
         def e2e(self, view_idx):
@@ -374,15 +413,17 @@ def main():
             if depth is not None:
                 depth.record_stream(self.copy_stream)
 
-    lanes = [Lane(own_stream=n_lanes > 1) for _ in range(n_lanes)]
+    # the reference launches on the legacy default stream whatever torch's current stream is: its arm is timed on that stream
+    lanes = [Lane(own_stream=ref_mod is None) for _ in range(n_lanes)]
     launches = [0]
 
-    def timed(kind, steps, warmup, sample_clocks=False, n_lanes=n_lanes, frame_marks=None):
+    def timed(kind, steps, warmup, sample_clocks=False, driver=driver, frame_marks=None):
         import threading
+        n_lanes_used = 1 if driver == "single" else n_lanes
         timed_views = [vi for s in range(warmup, warmup + steps) for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views)]
         warm_views = [vi for s in range(warmup) for vi in parallel.step_view_indices(s, args.views_per_step, rank, world, n_views)]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        gate = threading.Barrier(n_lanes + 1)
+        gate = threading.Barrier(n_lanes_used + 1)
         errors = []
         for lane in lanes:
             lane.launches = 0
@@ -394,22 +435,20 @@ def main():
                 torch.cuda.set_device(device)
                 with torch.cuda.stream(lane.stream):
                     # untimed: the views of the timed region once (either implementation grows its buffers / allocator pools), then the warm-up steps
-                    for vi in timed_views[k::n_lanes] + warm_views[k::n_lanes]:
+                    for vi in timed_views[k::n_lanes_used] + warm_views[k::n_lanes_used]:
                         fn(vi)
                     lane.stream.synchronize()
                     lane.copy_stream.synchronize()
-                    if n_lanes > 1:
-                        gate.wait()          # everybody is warm
-                        gate.wait()          # the main thread has recorded the start event
-                        lane.stream.wait_event(e0)
+                    gate.wait()          # everybody is warm
+                    gate.wait()          # the main thread has recorded the start event
+                    lane.stream.wait_event(e0)
                     lane.launches = 0
-                    for vi in timed_views[k::n_lanes]:
+                    for vi in timed_views[k::n_lanes_used]:
                         fn(vi)
                     lane.stream.wait_stream(lane.copy_stream)   # outstanding copies back belong to the timed region
             except Exception as exc:  # noqa: BLE001 - reported by the main thread
                 errors.append(exc)
-                if n_lanes > 1:
-                    gate.abort()
+                gate.abort()
 
         def prepare():
             torch.cuda.synchronize()
@@ -423,28 +462,68 @@ def main():
             return sampler
 
         main_stream = torch.cuda.current_stream(device)
-        if n_lanes == 1:
+        if driver == "single":
             lane = lanes[0]
             fn = lane.resident if kind == "resident" else lane.e2e
-            for vi in timed_views + warm_views:
-                fn(vi)
+            with torch.cuda.stream(lane.stream):
+                for vi in timed_views + warm_views:
+                    fn(vi)
             sampler = prepare()
             lane.launches = 0
             t0 = time.time()
-            e0.record()
+            e0.record(main_stream)
+            lane.stream.wait_event(e0)
             marks = []
-            for vi in timed_views:
-                fn(vi)
-                if frame_marks is not None:
-                    marks.append(torch.cuda.Event(enable_timing=True))
-                    marks[-1].record()
+            with torch.cuda.stream(lane.stream):
+                for vi in timed_views:
+                    fn(vi)
+                    if frame_marks is not None:
+                        marks.append(torch.cuda.Event(enable_timing=True))
+                        marks[-1].record()
+            main_stream.wait_stream(lane.stream)
             main_stream.wait_stream(lane.copy_stream)   # outstanding copies back belong to the timed region
-            e1.record()
+            e1.record(main_stream)
             if frame_marks is not None:
                 torch.cuda.synchronize()
                 frame_marks.extend(a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks))
+        elif driver == "async":
+            # one host thread, frames alternate between the lanes' streams; no call waits for the GPU, a frame's status is
+            # checked when its stream is used again (two frames later) and, for the last ones, by frame_results()
+            def sweep(views, count_launches):
+                for i, vi in enumerate(views):
+                    lane = lanes[i % n_lanes_used]
+                    with torch.cuda.stream(lane.stream):
+                        (lane.resident if kind == "resident" else lane.e2e)(vi)
+                infos = mod.rasterization.frame_results(device)
+                if count_launches:
+                    # every frame of the sweep launches the same kernels: count one frame's and scale
+                    per_frame = max((fi.kernel_launches for fi in infos), default=0)
+                    lanes[0].launches = per_frame * len(views)
+                return infos
+
+            for lane in lanes[:n_lanes_used]:      # first pass with blocking calls: buffers grow to what these views need
+                with torch.cuda.stream(lane.stream):
+                    for vi in timed_views + warm_views:
+                        (lane.resident if kind == "resident" else lane.e2e)(vi)
+            mod.rasterization.set_deferred_checks(True)
+            try:
+                sweep(warm_views + timed_views[: 2 * n_lanes_used], False)
+                sampler = prepare()
+                t0 = time.time()
+                e0.record(main_stream)
+                for lane in lanes[:n_lanes_used]:
+                    lane.stream.wait_event(e0)
+                infos = sweep(timed_views, True)
+                for lane in lanes[:n_lanes_used]:
+                    main_stream.wait_stream(lane.stream)
+                    main_stream.wait_stream(lane.copy_stream)
+                e1.record(main_stream)
+                if any(fi.reruns for fi in infos):
+                    raise RuntimeError("a frame of the timed region was re-rendered by its deferred check")
+            finally:
+                mod.rasterization.set_deferred_checks(False)
         else:
-            threads = [threading.Thread(target=lane_body, args=(k,)) for k in range(n_lanes)]
+            threads = [threading.Thread(target=lane_body, args=(k,)) for k in range(n_lanes_used)]
             for th in threads:
                 th.start()
             try:
@@ -488,7 +567,8 @@ def main():
         "config": {"workload": workload_name, "views_per_step_per_gpu": args.views_per_step, "parallelism": f"view-partitioned x{world}",
                    "l2": "per-frame working set (708 MB scene + >300 MB per-Gaussian records) exceeds the 126 MB L2; no explicit flush",
                    "scene_residency": "scene resident in HBM; per-frame inputs are the camera matrices",
-                   "frames_in_flight": n_lanes},
+                   "frames_in_flight": n_lanes, "frame_driver": {"async": "one host thread, two CUDA streams, non-blocking calls (deferred status checks)",
+                                                                    "threads": f"{n_lanes} host threads with blocking calls", "single": "one host thread, blocking calls"}[driver]},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": args.views_per_step * (16 + 16 + 3) * 4,
                 "d2h_bytes_per_step": args.views_per_step * n_pix * 4 * (3 if fast else 4), "ms_per_step": ms_e2e / args.steps},
@@ -496,13 +576,22 @@ def main():
     }
 
     if ref_mod is None and n_lanes > 1:
-        # the same job with one frame in flight (one host thread, one stream), for comparison
+        # the same job with one frame in flight (one host thread, one stream, blocking calls), and with the other two-frame driver
         per_frame = []
-        ms_1, _ = timed("resident", args.steps, args.warmup, n_lanes=1, frame_marks=per_frame)
-        ms_1e, _ = timed("e2e", args.steps, args.warmup, n_lanes=1)
+        ms_1, _ = timed("resident", args.steps, args.warmup, driver="single", frame_marks=per_frame)
+        ms_1e, _ = timed("e2e", args.steps, args.warmup, driver="single")
         line["one_frame_in_flight"] = {"value": frames_total / (ms_1 / 1000.0), "e2e": frames_total / (ms_1e / 1000.0), "unit": "frames/s",
                                        "frame_ms": {"p10": float(np.percentile(per_frame, 10)), "p50": float(np.percentile(per_frame, 50)),
                                                     "p90": float(np.percentile(per_frame, 90)), "frames": len(per_frame)}}
+        other = "threads" if driver == "async" else "async"
+        try:
+            host_threads = len(os.sched_getaffinity(0))
+        except AttributeError:
+            host_threads = os.cpu_count() or 1
+        if other == "async" or host_threads >= 3 * world:
+            ms_o, _ = timed("resident", args.steps, args.warmup, driver=other)
+            ms_oe, _ = timed("e2e", args.steps, args.warmup, driver=other)
+            line["other_driver"] = {"driver": other, "value": frames_total / (ms_o / 1000.0), "e2e": frames_total / (ms_oe / 1000.0), "unit": "frames/s"}
 
     if ref_mod is not None:
         line["frame_ms"] = {"p10": float(np.percentile(ref_frames, 10)), "p50": float(np.percentile(ref_frames, 50)),
@@ -511,8 +600,12 @@ def main():
                      "gpu_launches": 0,
                      "cpu_baseline": {"value": None, "unit": "frames/s", "cores": 0, "kind": "reference",
                                       "sample": "not a CPU run: this arm executed the reference's CUDA extension (it has no CPU path)"}})
+        line["train"] = train_leg()
         if rank == 0:
             print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
         return
 
     # ---- per-stage device times, statistics and rooflines (outside the timed regions) ---------------
@@ -580,6 +673,7 @@ def main():
     line["stages_ms"] = {k: float(v) for k, v in zip(names, stage_ms)}
     line["frame_stats"] = {"n_instances": I, "n_visible": n_vis, "key_bytes": key_bytes, "end_bit": end_bit}
 
+    line["train"] = train_leg()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         fps, cores, sample = cpu_port_fps(scene, args.cpu_sample_views)
         line["cpu_baseline"] = {"value": fps, "unit": "frames/s", "cores": cores, "kind": "port", "sample": sample}

@@ -115,6 +115,13 @@ def lib():
                 l.htgs_render.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_void_p,
                                           ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
                                           ctypes.POINTER(HtgsFrameInfo)]
+                l.htgs_render_async.restype = ctypes.c_int
+                l.htgs_render_async.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_void_p,
+                                                ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+                l.htgs_render_fast_async.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_int,
+                                                     ctypes.c_void_p]
+                l.htgs_frame_result.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsFrameInfo)]
+                l.htgs_set_max_weights_tail_credit.argtypes = [ctypes.c_void_p, ctypes.c_int]
                 l.htgs_render_host.restype = ctypes.c_int
                 l.htgs_render_host.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_void_p,
                                                ctypes.c_int, ctypes.c_int, ctypes.POINTER(HtgsFrameInfo)]
@@ -170,15 +177,17 @@ def check(code: int) -> None:
         raise HtgsError(code, f"htgs_b200 error {code}: {msg}")
 
 
-_contexts: Dict[int, int] = {}
+_contexts: Dict[tuple, int] = {}
 _ctx_lock = threading.Lock()
 
 
-def context(device_index: int) -> int:
-    """One library context per (CUDA device, host thread) of this process, created on first use.  A context owns its
-    workspace and its pinned status word, so two host threads that render concurrently (each on its own CUDA stream)
-    must not share one; giving every thread its own makes the Python surface safe to call from several threads."""
-    key = (int(device_index), threading.get_ident())
+def context(device_index: int, stream: int = 0) -> int:
+    """One library context per (CUDA device, host thread, stream key) of this process, created on first use.  A context owns
+    its workspace and its pinned status word, so two frames that are in flight at once - two host threads rendering
+    concurrently, or one thread queueing frames on two CUDA streams without waiting (`htgs_render_async`) - must not share
+    one.  Blocking calls pass no stream key and share the thread's context; the non-blocking path passes the handle of the
+    stream it queues on."""
+    key = (int(device_index), threading.get_ident(), int(stream))
     ctx = _contexts.get(key)
     if ctx is None:
         with _ctx_lock:
@@ -189,6 +198,13 @@ def context(device_index: int) -> int:
                     raise RuntimeError(f"htgs_create({device_index}) failed: {last_error()}")
                 _contexts[key] = ctx
     return ctx
+
+
+def contexts_of_thread(device_index: Optional[int] = None):
+    """Contexts the calling host thread has created (on one device, or on all)."""
+    me = threading.get_ident()
+    with _ctx_lock:
+        return [ctx for (dev, thread, _), ctx in _contexts.items() if thread == me and (device_index is None or dev == int(device_index))]
 
 
 def exported_symbols():

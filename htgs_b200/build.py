@@ -49,8 +49,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(CSRC, src.replace(".cu", ".o"))
         objs.append(obj)
         if force or _stale(obj, [src_path] + headers):
-            extra = ["-DHTGS_EXPERIMENT=" + os.environ["HTGS_EXPERIMENT"]] if os.environ.get("HTGS_EXPERIMENT") else []
-            cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src_path, "-o", obj]
+            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src_path, "-o", obj]
             jobs.append((src, cmd))
 
     def run(job):

@@ -92,9 +92,8 @@ __global__ void __launch_bounds__(kActBlock) activate_backward_kernel(
 
 extern "C" {
 
-void htgs_set_last_error(const char* message);   // api.cu
 
-static int activation_fail(int code, const char* message) { htgs_set_last_error(message); return code; }
+static int activation_fail(int code, const char* message) { htgs::set_last_error(message); return code; }
 
 int htgs_activate(const float* raw_scales, const float* raw_rotations, const float* raw_opacities, const float* filter_3d, float* scales,
                   float* rotations, float* opacities, int32_t n_primitives, void* stream) {

@@ -28,6 +28,20 @@ int fail_cuda(cudaError_t err, const char* what) {
     return HTGS_ERR_CUDA;
 }
 
+// Makes the context's device current for the duration of a call and puts the caller's device back afterwards.
+struct DeviceGuard {
+    int previous = -1;
+    cudaError_t status = cudaSuccess;
+    explicit DeviceGuard(int device) {
+        status = cudaGetDevice(&previous);
+        if (status == cudaSuccess && previous != device) status = cudaSetDevice(device);
+        else previous = -1;   // nothing to restore
+    }
+    ~DeviceGuard() { if (previous >= 0) cudaSetDevice(previous); }
+    DeviceGuard(const DeviceGuard&) = delete;
+    DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+
 constexpr size_t kAlign = 256;
 inline size_t align_up(size_t v) { return (v + kAlign - 1) & ~(kAlign - 1); }
 
@@ -106,6 +120,26 @@ int validate(const HtgsScene* scene, const HtgsView* view, bool needs_colour = t
 
 }  // namespace
 
+// What htgs_render_async queued and htgs_frame_result (or the next call on the context) still has to check.
+struct PendingFrame {
+    bool active = false;
+    HtgsScene scene{};
+    HtgsView view{};
+    BlendOutputs out{};
+    void* workspace = nullptr;          // caller's workspace, or null for the context's own
+    size_t workspace_bytes = 0;
+    cudaStream_t stream = nullptr;
+    float* max_weights = nullptr;
+    float weight_threshold = 0.0f;
+    bool fast = false;
+    FrameGeometry geo{};
+    SortPlan plan{};
+    FrameLayout layout{};
+    uint64_t capacity = 0;
+    uint32_t reruns = 0, launches = 0;
+    bool profiled = false;              // stage events were recorded for this frame
+};
+
 struct HtgsContext {
     int device = 0;
     int sm_count = 0;
@@ -123,24 +157,45 @@ struct HtgsContext {
     FrameGeometry last_geo{};
     uint32_t last_n_instances = 0;
     bool has_last = false;
+    HtgsFrameInfo last_info{};
+    // the frame whose status has not been read yet (htgs_render_async)
+    PendingFrame pending{};
+    cudaEvent_t frame_done = nullptr;       // recorded after the status copy of a frame
     // measurement aids
     bool profiling = false;
     bool collect_stats = false;
     bool fast_deterministic = false;        // htgs_render_fast: ordered (radix sort) instead of unordered (atomic) binning
+    bool max_weights_tail_credit = false;   // htgs_set_max_weights_tail_credit
     cudaEvent_t events[8] = {};
     bool events_created = false;
-    // With several frames in flight on one GPU (one context and stream per host thread), the short kernels at the front of a
+    // With several frames in flight on one GPU (one context and stream each), the short kernels at the front of a
     // frame (preprocess, scans, sort) go to a stream of the highest priority, so that the block scheduler places them ahead of
     // the queued CTAs of ANOTHER frame's blend kernel instead of behind all of them; the blend stays on the caller's stream.
+    // The stream and its two events are created with the context, so that no later call has to create driver objects.
     bool front_priority = true;             // htgs_set_front_priority
     cudaStream_t front_stream = nullptr;
     cudaEvent_t front_begin = nullptr, front_end = nullptr;
     float stage_ms[HTGS_N_STAGES] = {};
 };
 
+namespace htgs {
+int context_device(const HtgsContext* ctx) { return ctx ? ctx->device : -1; }
+void set_last_error(const char* message) { g_last_error = message ? message : ""; }
+}  // namespace htgs
+
+static int finish_frame(HtgsContext* ctx, HtgsFrameInfo* info);
+
+// A call on a context whose previous frame was queued with htgs_render_async checks that frame first.
+static int settle_pending(HtgsContext* ctx) {
+    if (!ctx->pending.active) return HTGS_OK;
+    const int rc = finish_frame(ctx, nullptr);
+    if (rc != HTGS_OK) g_last_error = "deferred check of the previous frame: " + g_last_error;
+    return rc;
+}
+
 extern "C" {
 
-int htgs_version(void) { return 100; }
+int htgs_version(void) { return 110; }
 
 const char* htgs_last_error(void) { return g_last_error.c_str(); }
 
@@ -149,15 +204,24 @@ HtgsContext* htgs_create(int device) {
     cudaError_t err = cudaGetDeviceCount(&count);
     if (err != cudaSuccess || count == 0) { fail_cuda(err != cudaSuccess ? err : cudaErrorNoDevice, "htgs_create: no CUDA device"); return nullptr; }
     if (device < 0 || device >= count) { fail(HTGS_ERR_INVALID_ARGUMENT, "htgs_create: bad device index"); return nullptr; }
-    if ((err = cudaSetDevice(device)) != cudaSuccess) { fail_cuda(err, "cudaSetDevice"); return nullptr; }
+    DeviceGuard guard(device);
+    if (guard.status != cudaSuccess) { fail_cuda(guard.status, "cudaSetDevice"); return nullptr; }
     cudaDeviceProp prop;
     if ((err = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) { fail_cuda(err, "cudaGetDeviceProperties"); return nullptr; }
     if (prop.major != 10) { fail(HTGS_ERR_INVALID_ARGUMENT, "htgs_create: this library is built for sm_100a (B200) only"); return nullptr; }
     HtgsContext* ctx = new HtgsContext();
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
-    if ((err = cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_status), sizeof(FrameStatus), cudaHostAllocDefault)) != cudaSuccess) {
-        fail_cuda(err, "cudaHostAlloc"); delete ctx; return nullptr;
+    int least = 0, greatest = 0;
+    if ((err = cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_status), sizeof(FrameStatus), cudaHostAllocDefault)) != cudaSuccess ||
+        (err = cudaDeviceGetStreamPriorityRange(&least, &greatest)) != cudaSuccess ||
+        (err = cudaStreamCreateWithPriority(&ctx->front_stream, cudaStreamNonBlocking, greatest)) != cudaSuccess ||
+        (err = cudaEventCreateWithFlags(&ctx->front_begin, cudaEventDisableTiming)) != cudaSuccess ||
+        (err = cudaEventCreateWithFlags(&ctx->front_end, cudaEventDisableTiming)) != cudaSuccess ||
+        (err = cudaEventCreateWithFlags(&ctx->frame_done, cudaEventDisableTiming)) != cudaSuccess) {
+        fail_cuda(err, "htgs_create: pinned status word, side stream and events");
+        htgs_destroy(ctx);
+        return nullptr;
     }
     std::memset(ctx->host_status, 0, sizeof(FrameStatus));
     return ctx;
@@ -165,7 +229,8 @@ HtgsContext* htgs_create(int device) {
 
 void htgs_destroy(HtgsContext* ctx) {
     if (!ctx) return;
-    cudaSetDevice(ctx->device);
+    DeviceGuard guard(ctx->device);
+    if (ctx->pending.active) cudaEventSynchronize(ctx->frame_done);
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->host_path_buf) cudaFree(ctx->host_path_buf);
     if (ctx->host_path_stream) cudaStreamDestroy(ctx->host_path_stream);
@@ -174,6 +239,7 @@ void htgs_destroy(HtgsContext* ctx) {
     if (ctx->front_stream) cudaStreamDestroy(ctx->front_stream);
     if (ctx->front_begin) cudaEventDestroy(ctx->front_begin);
     if (ctx->front_end) cudaEventDestroy(ctx->front_end);
+    if (ctx->frame_done) cudaEventDestroy(ctx->frame_done);
     delete ctx;
 }
 
@@ -184,23 +250,22 @@ size_t htgs_render_workspace_bytes(const HtgsScene* scene, const HtgsView* view,
     return carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, instance_capacity, false).bytes;
 }
 
-// The context's side stream (highest priority) and the two events that order it against a caller's stream.
-static int ensure_front_stream(HtgsContext* ctx) {
-    if (ctx->front_stream) return HTGS_OK;
-    cudaError_t err;
-    int least = 0, greatest = 0;
-    if ((err = cudaDeviceGetStreamPriorityRange(&least, &greatest)) != cudaSuccess) return fail_cuda(err, "stream priority range");
-    if ((err = cudaStreamCreateWithPriority(&ctx->front_stream, cudaStreamNonBlocking, greatest)) != cudaSuccess) return fail_cuda(err, "front stream");
-    if ((err = cudaEventCreateWithFlags(&ctx->front_begin, cudaEventDisableTiming)) != cudaSuccess) return fail_cuda(err, "front event");
-    if ((err = cudaEventCreateWithFlags(&ctx->front_end, cudaEventDisableTiming)) != cudaSuccess) return fail_cuda(err, "front event");
-    return HTGS_OK;
-}
+}  // extern "C"
 
-static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const SortPlan& plan,
-                     const FrameLayout& L, BlendOutputs out, cudaStream_t stream, uint32_t* launches, float* max_weights = nullptr,
-                     float weight_threshold = 0.0f, bool fast = false) {
+// Queues one frame (all kernels, the copy of the 64-byte status to pinned memory and the `frame_done` event) on the
+// frame's stream; does not wait for anything.
+static int enqueue_frame(HtgsContext* ctx, PendingFrame& f) {
     cudaError_t err;
+    const HtgsScene& scene = f.scene;
+    const HtgsView& view = f.view;
+    const FrameGeometry& geo = f.geo;
+    const SortPlan& plan = f.plan;
+    const FrameLayout& L = f.layout;
+    BlendOutputs out = f.out;
+    uint32_t* launches = &f.launches;
+    cudaStream_t stream = f.stream;
     const bool prof = ctx->profiling;
+    f.profiled = prof;
     if (prof && !ctx->events_created) {
         for (auto& e : ctx->events) if ((err = cudaEventCreate(&e)) != cudaSuccess) return fail_cuda(err, "cudaEventCreate");
         ctx->events_created = true;
@@ -210,8 +275,6 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
     cudaStream_t const caller_stream = stream;
     const bool front_priority = ctx->front_priority;
     if (front_priority) {
-        const int rc = ensure_front_stream(ctx);
-        if (rc != HTGS_OK) return rc;
         // everything the caller queued before this call (camera upload, the previous frame) comes first
         if ((err = cudaEventRecord(ctx->front_begin, caller_stream)) != cudaSuccess) return fail_cuda(err, "front event record");
         if ((err = cudaStreamWaitEvent(ctx->front_stream, ctx->front_begin, 0)) != cudaSuccess) return fail_cuda(err, "front stream wait");
@@ -219,13 +282,13 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
     }
     if ((err = cudaMemsetAsync(L.status, 0, sizeof(FrameStatus), stream)) != cudaSuccess) return fail_cuda(err, "status reset");
     if (prof) cudaEventRecord(ev[0], stream);
-    if ((err = launch_preprocess(view.mode, false, scene, view, geo, L.prim, L.status, stream, fast)) != cudaSuccess) return fail_cuda(err, "preprocess");
+    if ((err = launch_preprocess(view.mode, false, scene, view, geo, L.prim, L.status, stream, f.fast)) != cudaSuccess) return fail_cuda(err, "preprocess");
     if (prof) cudaEventRecord(ev[1], stream);
     if ((err = launch_scan_only(scene, L.prim, L.inst.capacity, L.status, stream)) != cudaSuccess) return fail_cuda(err, "scan");
     if (prof) cudaEventRecord(ev[2], stream);
     *launches += (scene.n_primitives > 0 ? 2 : 0) + 1;
     const uint32_t* prims_sorted = L.inst.prims[plan.final_buffer];
-    if (fast && !ctx->fast_deterministic) {
+    if (f.fast && !ctx->fast_deterministic) {
         if ((err = launch_bin_unordered(scene, geo, L.prim, L.inst.prims[plan.final_buffer], L.inst.capacity, L.tile_ranges, L.status, ctx->sm_count,
                                         stream, prof ? ev + 3 : nullptr, launches)) != cudaSuccess) return fail_cuda(err, "unordered binning");
     } else if ((err = launch_emit_sort_ranges(view.mode, scene, geo, plan, L.prim, L.inst, L.tile_ranges, L.status, ctx->sm_count, stream,
@@ -235,119 +298,175 @@ static int run_frame(HtgsContext* ctx, const HtgsScene& scene, const HtgsView& v
         if ((err = cudaStreamWaitEvent(caller_stream, ctx->front_end, 0)) != cudaSuccess) return fail_cuda(err, "caller stream wait");
         stream = caller_stream;
     }
-    if (max_weights) {
-        if ((err = launch_max_weights(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, max_weights, weight_threshold, stream)) != cudaSuccess) return fail_cuda(err, "max weights");
-    } else if (fast) {
+    if (f.max_weights) {
+        if ((err = launch_max_weights(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, f.max_weights, f.weight_threshold, ctx->max_weights_tail_credit,
+                                      stream)) != cudaSuccess) return fail_cuda(err, "max weights");
+    } else if (f.fast) {
         if ((err = launch_blend_fast(view.mode, view.K, geo, L.prim, prims_sorted, L.tile_ranges, out.image, out.to_chw, L.status, stream)) != cudaSuccess) return fail_cuda(err, "fast blend");
     } else if ((err = launch_blend(view.mode, view.K, false, geo, L.prim, prims_sorted, L.tile_ranges, out, TrainPixelBuffers{}, L.status, stream)) != cudaSuccess) return fail_cuda(err, "blend");
     *launches += 1;
     if (prof) cudaEventRecord(ev[6], stream);
     if ((err = cudaMemcpyAsync(ctx->host_status, L.status, sizeof(FrameStatus), cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return fail_cuda(err, "status copy");
-    if ((err = cudaStreamSynchronize(stream)) != cudaSuccess) return fail_cuda(err, "frame synchronisation");
-    if (prof) {
-        for (int i = 0; i < 6; ++i) cudaEventElapsedTime(&ctx->stage_ms[i], ev[i], ev[i + 1]);
-        cudaEventElapsedTime(&ctx->stage_ms[HTGS_STAGE_TOTAL], ev[0], ev[6]);
-    }
+    if ((err = cudaEventRecord(ctx->frame_done, stream)) != cudaSuccess) return fail_cuda(err, "frame event record");
     return HTGS_OK;
+}
+
+// Carves the frame's buffers for `f.capacity` instances (growing the context's workspace if it is the one in use) and queues the frame.
+static int carve_and_enqueue(HtgsContext* ctx, PendingFrame& f) {
+    const bool internal = f.workspace == nullptr;
+    if (internal) {
+        const size_t need = carve_frame(nullptr, f.scene.n_primitives, f.geo.n_tiles, f.plan, f.capacity, false).bytes;
+        if (need > ctx->workspace_bytes) {
+            cudaError_t err;
+            // the old workspace may still be in use by frames queued earlier (on this stream or the side stream)
+            if ((err = cudaStreamSynchronize(f.stream)) != cudaSuccess) return fail_cuda(err, "synchronise before growing the workspace");
+            if ((err = cudaStreamSynchronize(ctx->front_stream)) != cudaSuccess) return fail_cuda(err, "synchronise before growing the workspace");
+            if (ctx->workspace) cudaFree(ctx->workspace);
+            ctx->workspace = nullptr; ctx->workspace_bytes = 0;
+            const size_t grow = need + need / 8;
+            if ((err = cudaMalloc(&ctx->workspace, grow)) != cudaSuccess) return fail_cuda(err, "workspace allocation");
+            ctx->workspace_bytes = grow;
+        }
+        ctx->instance_capacity = f.capacity;
+        f.layout = carve_frame(ctx->workspace, f.scene.n_primitives, f.geo.n_tiles, f.plan, f.capacity, false);
+    } else {
+        f.layout = carve_frame(f.workspace, f.scene.n_primitives, f.geo.n_tiles, f.plan, f.capacity, false);
+    }
+    return enqueue_frame(ctx, f);
+}
+
+// First half of a render call: validation, sizing and queueing.  On success the frame is `ctx->pending`.
+static int begin_frame(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
+                       int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info,
+                       float* max_weights, float weight_threshold, bool fast) {
+    int rc = validate(scene, view, max_weights == nullptr);
+    if (rc != HTGS_OK) return rc;
+    if ((rc = settle_pending(ctx)) != HTGS_OK) return rc;
+    PendingFrame& f = ctx->pending;
+    f = PendingFrame{};
+    f.scene = *scene; f.view = *view;
+    f.stream = static_cast<cudaStream_t>(stream_ptr);
+    f.geo = make_geometry(view->mode, view->width, view->height);
+    f.fast = fast && !max_weights && blend_fast_supports(view->mode, view->K);   // other modes / K: the exact kernels serve the fast entry point
+    f.plan = make_sort_plan(view->mode, f.geo.n_tiles);
+    f.out = BlendOutputs{image, depth, alpha, to_chw != 0, use_median_depth != 0, false};
+    f.workspace = workspace; f.workspace_bytes = workspace_bytes;
+    f.max_weights = max_weights; f.weight_threshold = weight_threshold;
+    if (workspace == nullptr) {
+        f.capacity = ctx->instance_capacity ? ctx->instance_capacity : std::max<uint64_t>(uint64_t(scene->n_primitives) * 4, 1u << 20);
+    } else {
+        // largest capacity that fits the caller's workspace (the layout is monotone in capacity)
+        const size_t fixed = carve_frame(nullptr, scene->n_primitives, f.geo.n_tiles, f.plan, 0, false).bytes;
+        if (workspace_bytes < fixed + 4096) {
+            if (info) { std::memset(info, 0, sizeof(*info)); info->workspace_bytes = fixed + 4096; }
+            return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "workspace too small for the per-Gaussian buffers");
+        }
+        const size_t per_inst = size_t(f.plan.key_bytes) * 2 + 8 + (size_t(kMaxRadixBins) * 4 + kSortTile - 1) / kSortTile;
+        uint64_t capacity = (workspace_bytes - fixed - 8 * kAlign) / per_inst;
+        while (capacity > 0 && carve_frame(nullptr, scene->n_primitives, f.geo.n_tiles, f.plan, capacity, false).bytes > workspace_bytes) capacity -= std::min<uint64_t>(capacity, 4096);
+        f.capacity = capacity;
+    }
+    if ((rc = carve_and_enqueue(ctx, f)) != HTGS_OK) return rc;
+    f.active = true;
+    return HTGS_OK;
+}
+
+// Second half: waits for the pending frame, reads its status, re-runs it after growing the workspace when its instance
+// buffers were too small, and fills `info`.
+static int finish_frame(HtgsContext* ctx, HtgsFrameInfo* info) {
+    PendingFrame& f = ctx->pending;
+    if (!f.active) {
+        if (info) *info = ctx->last_info;
+        return HTGS_OK;
+    }
+    const bool internal = f.workspace == nullptr;
+    for (;;) {
+        cudaError_t err;
+        if ((err = cudaEventSynchronize(ctx->frame_done)) != cudaSuccess) { f.active = false; return fail_cuda(err, "frame synchronisation"); }
+        if (f.profiled) {
+            for (int i = 0; i < 6; ++i) cudaEventElapsedTime(&ctx->stage_ms[i], ctx->events[i], ctx->events[i + 1]);
+            cudaEventElapsedTime(&ctx->stage_ms[HTGS_STAGE_TOTAL], ctx->events[0], ctx->events[6]);
+        }
+        const FrameStatus st = *ctx->host_status;
+        ctx->last_layout = f.layout; ctx->last_plan = f.plan; ctx->last_geo = f.geo; ctx->last_n_instances = st.overflow ? 0 : st.n_instances; ctx->has_last = true;
+        const uint64_t needed_capacity = uint64_t(st.n_instances) + uint64_t(st.n_instances) / 4 + 4096;
+        HtgsFrameInfo& li = ctx->last_info;
+        li.n_instances = st.n_instances; li.n_visible = st.n_visible; li.key_bytes = uint32_t(f.plan.key_bytes);
+        li.end_bit = uint32_t(f.plan.end_bit); li.reruns = f.reruns; li.device_error = st.error;
+        li.kernel_launches = f.launches; li.reserved = 0;
+        li.candidate_pairs = st.candidate_pairs; li.accepted_fragments = st.accepted_fragments;
+        li.workspace_bytes = carve_frame(nullptr, f.scene.n_primitives, f.geo.n_tiles, f.plan, st.overflow ? needed_capacity : f.capacity, false).bytes;
+        if (info) *info = li;
+        if (st.error) { f.active = false; return fail(HTGS_ERR_DEVICE_FLAG, "a kernel reported an internal error (bounded wait gave up)"); }
+        if (!st.overflow) { f.active = false; return HTGS_OK; }
+        f.active = false;
+        if (st.n_instances == 0xffffffffu) return fail(HTGS_ERR_INVALID_ARGUMENT, "instance count does not fit 32 bits");
+        if (!internal) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "workspace too small for the instance buffers of this frame");
+        if (f.reruns >= 2) return fail(HTGS_ERR_CUDA, "frame still overflows after growing the workspace");
+        f.capacity = needed_capacity;
+        ++f.reruns;
+        const int rc = carve_and_enqueue(ctx, f);
+        if (rc != HTGS_OK) return rc;
+        f.active = true;
+    }
 }
 
 static int render_core(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
                        int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info,
-                       float* max_weights, float weight_threshold, bool fast = false);
+                       float* max_weights, float weight_threshold, bool fast, bool wait) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    DeviceGuard guard(ctx->device);
+    if (guard.status != cudaSuccess) return fail_cuda(guard.status, "cudaSetDevice");
+    const int rc = begin_frame(ctx, scene, view, image, depth, alpha, to_chw, use_median_depth, workspace, workspace_bytes, stream_ptr, info, max_weights, weight_threshold, fast);
+    if (rc != HTGS_OK || !wait) return rc;
+    return finish_frame(ctx, info);
+}
+
+extern "C" {
 
 int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
                 int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info) {
     if (!image || !depth) return fail(HTGS_ERR_INVALID_ARGUMENT, "image and depth must not be null");
-    return render_core(ctx, scene, view, image, depth, alpha, to_chw, use_median_depth, workspace, workspace_bytes, stream_ptr, info, nullptr, 0.0f);
+    return render_core(ctx, scene, view, image, depth, alpha, to_chw, use_median_depth, workspace, workspace_bytes, stream_ptr, info, nullptr, 0.0f, false, true);
+}
+
+int htgs_render_async(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
+                      int to_chw, int use_median_depth, void* stream_ptr) {
+    if (!image || !depth) return fail(HTGS_ERR_INVALID_ARGUMENT, "image and depth must not be null");
+    return render_core(ctx, scene, view, image, depth, alpha, to_chw, use_median_depth, nullptr, 0, stream_ptr, nullptr, nullptr, 0.0f, false, false);
+}
+
+int htgs_render_fast_async(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, int to_chw, void* stream_ptr) {
+    if (!image) return fail(HTGS_ERR_INVALID_ARGUMENT, "image must not be null");
+    return render_core(ctx, scene, view, image, nullptr, nullptr, to_chw, 0, nullptr, 0, stream_ptr, nullptr, nullptr, 0.0f, true, false);
+}
+
+int htgs_frame_result(HtgsContext* ctx, HtgsFrameInfo* info) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    DeviceGuard guard(ctx->device);
+    if (guard.status != cudaSuccess) return fail_cuda(guard.status, "cudaSetDevice");
+    return finish_frame(ctx, info);
 }
 
 int htgs_update_max_weights(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* max_weights, float weight_threshold,
                             void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info) {
     if (!max_weights) return fail(HTGS_ERR_INVALID_ARGUMENT, "max_weights must not be null");
-    return render_core(ctx, scene, view, nullptr, nullptr, nullptr, 1, 0, workspace, workspace_bytes, stream_ptr, info, max_weights, weight_threshold);
+    return render_core(ctx, scene, view, nullptr, nullptr, nullptr, 1, 0, workspace, workspace_bytes, stream_ptr, info, max_weights, weight_threshold, false, true);
 }
 
 int htgs_render_fast(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, int to_chw, void* workspace,
                      size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info) {
     if (!image) return fail(HTGS_ERR_INVALID_ARGUMENT, "image must not be null");
-    return render_core(ctx, scene, view, image, nullptr, nullptr, to_chw, 0, workspace, workspace_bytes, stream_ptr, info, nullptr, 0.0f, true);
-}
-
-static int render_core(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
-                       int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream_ptr, HtgsFrameInfo* info,
-                       float* max_weights, float weight_threshold, bool fast) {
-    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
-    int rc = validate(scene, view, max_weights == nullptr);
-    if (rc != HTGS_OK) return rc;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-    cudaError_t err;
-    int current = -1;
-    cudaGetDevice(&current);
-    if (current != ctx->device && (err = cudaSetDevice(ctx->device)) != cudaSuccess) return fail_cuda(err, "cudaSetDevice");
-
-    const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
-    fast = fast && !max_weights && blend_fast_supports(view->mode, view->K);   // other modes / K: the exact kernels serve the fast entry point
-    const SortPlan plan = make_sort_plan(view->mode, geo.n_tiles);
-    const BlendOutputs out{image, depth, alpha, to_chw != 0, use_median_depth != 0, false};
-    const bool internal = workspace == nullptr;
-    uint32_t reruns = 0, launches = 0;
-
-    uint64_t capacity;
-    if (internal) {
-        capacity = ctx->instance_capacity ? ctx->instance_capacity : std::max<uint64_t>(uint64_t(scene->n_primitives) * 4, 1u << 20);
-    } else {
-        // largest capacity that fits the caller's workspace (the layout is monotone in capacity)
-        const size_t fixed = carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, 0, false).bytes;
-        if (workspace_bytes < fixed + 4096) {
-            if (info) { std::memset(info, 0, sizeof(*info)); info->workspace_bytes = fixed + 4096; }
-            return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "workspace too small for the per-Gaussian buffers");
-        }
-        const size_t per_inst = size_t(plan.key_bytes) * 2 + 8 + (size_t(kMaxRadixBins) * 4 + kSortTile - 1) / kSortTile;
-        capacity = (workspace_bytes - fixed - 8 * kAlign) / per_inst;
-        while (capacity > 0 && carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, capacity, false).bytes > workspace_bytes) capacity -= std::min<uint64_t>(capacity, 4096);
-    }
-
-    for (;;) {
-        FrameLayout L;
-        if (internal) {
-            const size_t need = carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, capacity, false).bytes;
-            if (need > ctx->workspace_bytes) {
-                if ((err = cudaStreamSynchronize(stream)) != cudaSuccess) return fail_cuda(err, "synchronise before growing the workspace");
-                if (ctx->workspace) cudaFree(ctx->workspace);
-                ctx->workspace = nullptr; ctx->workspace_bytes = 0;
-                const size_t grow = need + need / 8;
-                if ((err = cudaMalloc(&ctx->workspace, grow)) != cudaSuccess) return fail_cuda(err, "workspace allocation");
-                ctx->workspace_bytes = grow;
-            }
-            ctx->instance_capacity = capacity;
-            L = carve_frame(ctx->workspace, scene->n_primitives, geo.n_tiles, plan, capacity, false);
-        } else {
-            L = carve_frame(workspace, scene->n_primitives, geo.n_tiles, plan, capacity, false);
-        }
-        rc = run_frame(ctx, *scene, *view, geo, plan, L, out, stream, &launches, max_weights, weight_threshold, fast);
-        if (rc != HTGS_OK) return rc;
-        const FrameStatus st = *ctx->host_status;
-        ctx->last_layout = L; ctx->last_plan = plan; ctx->last_geo = geo; ctx->last_n_instances = st.overflow ? 0 : st.n_instances; ctx->has_last = true;
-        const uint64_t needed_capacity = uint64_t(st.n_instances) + uint64_t(st.n_instances) / 4 + 4096;
-        if (info) {
-            info->n_instances = st.n_instances; info->n_visible = st.n_visible; info->key_bytes = uint32_t(plan.key_bytes);
-            info->end_bit = uint32_t(plan.end_bit); info->reruns = reruns; info->device_error = st.error;
-            info->kernel_launches = launches; info->reserved = 0;
-            info->candidate_pairs = st.candidate_pairs; info->accepted_fragments = st.accepted_fragments;
-            info->workspace_bytes = carve_frame(nullptr, scene->n_primitives, geo.n_tiles, plan, st.overflow ? needed_capacity : capacity, false).bytes;
-        }
-        if (st.error) return fail(HTGS_ERR_DEVICE_FLAG, "a kernel reported an internal error (bounded wait gave up)");
-        if (!st.overflow) return HTGS_OK;
-        if (st.n_instances == 0xffffffffu) return fail(HTGS_ERR_INVALID_ARGUMENT, "instance count does not fit 32 bits");
-        if (!internal) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "workspace too small for the instance buffers of this frame");
-        capacity = needed_capacity;
-        ++reruns;
-        if (reruns > 2) return fail(HTGS_ERR_CUDA, "frame still overflows after growing the workspace");
-    }
+    return render_core(ctx, scene, view, image, nullptr, nullptr, to_chw, 0, workspace, workspace_bytes, stream_ptr, info, nullptr, 0.0f, true, true);
 }
 
 int htgs_get_intermediates(HtgsContext* ctx, HtgsIntermediates* out) {
     if (!ctx || !out) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    if (ctx->pending.active) {
+        DeviceGuard guard(ctx->device);
+        const int rc = settle_pending(ctx);
+        if (rc != HTGS_OK) return rc;
+    }
     if (!ctx->has_last) return fail(HTGS_ERR_INVALID_ARGUMENT, "no frame has been rendered on this context");
     const FrameLayout& L = ctx->last_layout;
     const SortPlan& p = ctx->last_plan;
@@ -392,6 +511,12 @@ int htgs_set_fast_deterministic(HtgsContext* ctx, int enable) {
     return HTGS_OK;
 }
 
+int htgs_set_max_weights_tail_credit(HtgsContext* ctx, int enable) {
+    if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
+    ctx->max_weights_tail_credit = enable != 0;
+    return HTGS_OK;
+}
+
 int htgs_set_collect_stats(HtgsContext* ctx, int enable) {
     if (!ctx) return fail(HTGS_ERR_INVALID_ARGUMENT, "context must not be null");
     ctx->collect_stats = enable != 0;
@@ -405,7 +530,8 @@ int htgs_render_host(HtgsContext* ctx, const HtgsScene* hs, const HtgsView* hv, 
     if (rc != HTGS_OK) return rc;
     if (!host_image || !host_depth) return fail(HTGS_ERR_INVALID_ARGUMENT, "image and depth must not be null");
     cudaError_t err;
-    if ((err = cudaSetDevice(ctx->device)) != cudaSuccess) return fail_cuda(err, "cudaSetDevice");
+    DeviceGuard guard(ctx->device);
+    if (guard.status != cudaSuccess) return fail_cuda(guard.status, "cudaSetDevice");
     if (!ctx->host_path_stream && (err = cudaStreamCreateWithFlags(&ctx->host_path_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail_cuda(err, "cudaStreamCreate");
     cudaStream_t stream = ctx->host_path_stream;
     const size_t n = size_t(hs->n_primitives), B = size_t(hs->total_sh_bases), P = size_t(hv->width) * hv->height;
@@ -516,22 +642,9 @@ PixelLayout carve_pixel_blob(void* blob, int mode, int K, const FrameGeometry& g
     return L;
 }
 
-int set_device_of(HtgsContext* ctx) {
-    int current = -1;
-    cudaGetDevice(&current);
-    if (current != ctx->device) {
-        const cudaError_t err = cudaSetDevice(ctx->device);
-        if (err != cudaSuccess) return fail_cuda(err, "cudaSetDevice");
-    }
-    return HTGS_OK;
-}
-
 }  // namespace
 
 extern "C" {
-
-int htgs_backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
-                             const float* grad_image, const float* image, const HtgsGradients* grads, void* accum_ptr, void* stream_ptr);
 
 int htgs_forward_blob_sizes(const HtgsScene* scene, const HtgsView* view, size_t* per_primitive_bytes, size_t* per_tile_bytes, size_t* per_pixel_bytes) {
     const int rc = validate(scene, view);
@@ -554,7 +667,9 @@ int htgs_forward_begin(HtgsContext* ctx, const HtgsScene* scene, const HtgsView*
     if (!ctx || !n_instances) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     int rc = validate(scene, view);
     if (rc != HTGS_OK) return rc;
-    if ((rc = set_device_of(ctx)) != HTGS_OK) return rc;
+    DeviceGuard guard(ctx->device);
+    if (guard.status != cudaSuccess) return fail_cuda(guard.status, "cudaSetDevice");
+    if ((rc = settle_pending(ctx)) != HTGS_OK) return rc;
     const PrimLayout L = carve_primitive_blob(per_primitive, scene->n_primitives);
     if (!per_primitive || per_primitive_bytes < L.bytes) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "per-primitive blob too small");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
@@ -575,7 +690,9 @@ int htgs_forward_finish(HtgsContext* ctx, const HtgsScene* scene, const HtgsView
     if (!ctx || !blobs || !image) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     int rc = validate(scene, view);
     if (rc != HTGS_OK) return rc;
-    if ((rc = set_device_of(ctx)) != HTGS_OK) return rc;
+    DeviceGuard guard(ctx->device);
+    if (guard.status != cudaSuccess) return fail_cuda(guard.status, "cudaSetDevice");
+    if ((rc = settle_pending(ctx)) != HTGS_OK) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);
     const SortPlan plan = make_sort_plan(view->mode, geo.n_tiles);
@@ -609,10 +726,6 @@ size_t htgs_backward_scratch_bytes(const HtgsScene* scene) {
     return scene ? align_up(size_t(scene->n_primitives > 0 ? scene->n_primitives : 0) * 5 * sizeof(float4) + 1) : 0;
 }
 
-int htgs_context_device(const HtgsContext* ctx) { return ctx ? ctx->device : -1; }
-
-void htgs_set_last_error(const char* message) { g_last_error = message ? message : ""; }
-
 int htgs_forward_visibility(const HtgsScene* scene, const HtgsTrainBlobs* blobs, uint8_t* visible, void* stream_ptr) {
     if (!scene || !blobs || (!visible && scene->n_primitives > 0)) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     if (scene->n_primitives < 0) return fail(HTGS_ERR_INVALID_ARGUMENT, "negative primitive count");
@@ -627,15 +740,18 @@ int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view
                   const float* grad_image, const float* image, const HtgsGradients* grads, void* stream_ptr) {
     if (!grads) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     if (!grads->scratch || grads->scratch_bytes < htgs_backward_scratch_bytes(scene)) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "backward scratch too small");
-    return htgs_backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, grads->scratch, stream_ptr);
+    return htgs::backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, grads->scratch, stream_ptr);
 }
 
-int htgs_backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+}  // extern "C"
+
+int htgs::backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                              const float* grad_image, const float* image, const HtgsGradients* grads, void* accum_ptr, void* stream_ptr) {
     if (!ctx || !blobs || !grads || !grad_image || !accum_ptr) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     int rc = validate(scene, view);
     if (rc != HTGS_OK) return rc;
-    if ((rc = set_device_of(ctx)) != HTGS_OK) return rc;
+    DeviceGuard guard(ctx->device);
+    if (guard.status != cudaSuccess) return fail_cuda(guard.status, "cudaSetDevice");
     if (view->mode == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING && !image) return fail(HTGS_ERR_INVALID_ARGUMENT, "ALPHA_BLEND_GLOBAL_ORDERING needs the forward image");
     if (scene->n_primitives > 0 && (!grads->grad_positions || !grads->grad_scales || !grads->grad_rotations || !grads->grad_opacities || !grads->grad_sh_0 ||
                                     (scene->total_sh_bases > 0 && !grads->grad_sh_rest)))
@@ -658,7 +774,6 @@ int htgs_backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const Htg
     // configuration 2) on the context's side stream meanwhile, ordered after whatever the caller queued before this call.
     cudaEvent_t outputs_cleared = nullptr;
     if (ctx->front_priority && scene->n_primitives > 0) {
-        if ((rc = ensure_front_stream(ctx)) != HTGS_OK) return rc;
         cudaError_t e;
         if ((e = cudaEventRecord(ctx->front_begin, stream)) != cudaSuccess) return fail_cuda(e, "front event record");
         if ((e = cudaStreamWaitEvent(ctx->front_stream, ctx->front_begin, 0)) != cudaSuccess) return fail_cuda(e, "front stream wait");
@@ -671,5 +786,3 @@ int htgs_backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const Htg
     if (err != cudaSuccess) return fail_cuda(err, "backward");
     return HTGS_OK;
 }
-
-}  // extern "C"

@@ -114,10 +114,10 @@ template <typename KeyT>
 __global__ void __launch_bounds__(kPreprocessBlock) emit_instances_kernel(
     const uint32_t* __restrict__ n_touched, const ushort4* __restrict__ bounds, const EvalRecord* __restrict__ eval,
     const uint32_t* __restrict__ block_sums, const uint32_t* __restrict__ block_offsets, KeyT* __restrict__ keys, uint32_t* __restrict__ prims,
-    uint32_t n_primitives, uint32_t grid_w, uint32_t capacity)
+    uint32_t n_primitives, uint32_t grid_w, uint32_t capacity, const FrameStatus* __restrict__ status)
 {
     const uint32_t total = block_sums[blockIdx.x];
-    if (total == 0) return;
+    if (total == 0 || status->overflow) return;   // a frame that does not fit its instance buffers is skipped by every later stage
     __shared__ uint32_t excl[kPreprocessBlock + 1];
     __shared__ ushort4 box[kPreprocessBlock];
     __shared__ uint32_t depth_bits[kPreprocessBlock];
@@ -380,18 +380,13 @@ cudaError_t emit_sort_ranges_t(const HtgsScene& scene, const FrameGeometry& geo,
     }
     emit_instances_kernel<KeyT><<<prim_blocks, kPreprocessBlock, 0, stream>>>(
         prim.n_touched, prim.bounds, prim.eval, prim.block_sums, prim.block_offsets, static_cast<KeyT*>(inst.keys[0]), inst.prims[0], n,
-        uint32_t(geo.grid_w), inst.capacity);
+        uint32_t(geo.grid_w), inst.capacity, status);
     if (ev) cudaEventRecord(ev[0], stream);
     if (launches) *launches += 1;
     const uint32_t persistent = uint32_t(sm_count) * 4;
-    static bool configured[64] = {};
-    int device = 0;
-    cudaGetDevice(&device);
-    if (device >= 0 && device < 64 && !configured[device]) {
-        err = cudaFuncSetAttribute(radix_scatter_kernel<KeyT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(scatter_smem_bytes<KeyT>()));
-        if (err != cudaSuccess) return err;
-        configured[device] = true;
-    }
+    static PerDeviceOnce configured;
+    err = configured.run([] { return cudaFuncSetAttribute(radix_scatter_kernel<KeyT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(scatter_smem_bytes<KeyT>())); });
+    if (err != cudaSuccess) return err;
     int cur = 0;
     for (int p = 0; p < plan.n_passes; ++p) {
         KeyT* kin = static_cast<KeyT*>(inst.keys[cur]);

@@ -29,10 +29,6 @@
 //     fragments, and the slot that falls out of the chain becomes the free one.
 #include "kernels.h"
 
-#ifndef HTGS_EXPERIMENT
-#define HTGS_EXPERIMENT 0   // timing experiments only (1-4 give wrong images): 1 no insertion, 2 / 4 no exact pass (4 keeps the masks), 3 staging only; -1 shared-memory padding (right images)
-#endif
-
 namespace htgs {
 
 namespace {
@@ -76,7 +72,7 @@ template <int MODE, int K, bool TRAIN> struct SmemLayout {
     static constexpr size_t pool_bytes = has_kbuffer ? size_t(K + 1) * TS::threads * pool_elem : 0;
     static constexpr size_t pool_idx_off = pool_off + pool_bytes;
     static constexpr size_t pool_idx_bytes = has_pool_idx ? size_t(K + 1) * TS::threads * 4 : 0;
-    static constexpr size_t total = pool_idx_off + pool_idx_bytes + (HTGS_EXPERIMENT == -1 ? 6400 : 0);   // -1: padding that costs two resident CTAs per SM (HYBRID K=16)
+    static constexpr size_t total = pool_idx_off + pool_idx_bytes;
 };
 
 // The shared per-fragment front end (hybrid_blend/kernels/inference.cuh:137-148).
@@ -235,7 +231,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
         for (int chunk = 0; chunk < TS::chunks; ++chunk) {
             // ---- 2. candidate masks: lane = Gaussian, one ballot per pixel of the warp --------------
             uint64_t cand = 0;
-            if (HTGS_EXPERIMENT < 3) {
+            {
                 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     const uint32_t j = chunk * TS::chunk + half * 32 + lane;
@@ -275,7 +271,6 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                 copies_landed = true;
             }
             const uint32_t n_cand = __popcll(cand);
-            if (HTGS_EXPERIMENT == 4) transmittance += float(n_cand);   // keeps the candidate masks alive when the exact pass is disabled
             if constexpr (STATS) stat_candidates += n_cand;
             const uint32_t n_iter = __reduce_max_sync(0xffffffffu, n_cand);
             const uint32_t chunk_base = chunk * TS::chunk;
@@ -310,7 +305,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                 };
                 auto commit = [&](float depth, float4 frag, uint32_t j) {
                     if constexpr (STATS) ++stat_accepted;
-                    if (HTGS_EXPERIMENT != 1 && depth < kd[K - 1] && frag.w >= MT::min_alpha_core) {
+                    if (depth < kd[K - 1] && frag.w >= MT::min_alpha_core) {
                         pool4[free_slot * TS::threads + tid] = frag;
                         if constexpr (TRAIN) pool_idx[free_slot * TS::threads + tid] = batch_begin - range.x + j;   // position in the tile's list: what the backward pass looks up
                         free_slot = slot_index(kbuffer_insert<K>(kd, ks, depth, slot_t(free_slot)));   // the entry that fell out: a real fragment or an empty one
@@ -324,7 +319,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                     }
                     transmittance *= 1.0f - frag.w;
                 };
-                for (uint32_t it = 0; it < (HTGS_EXPERIMENT >= 2 ? 0u : n_iter); it += 2) {
+                for (uint32_t it = 0; it < n_iter; it += 2) {
                     bool v0, v1;
                     const uint32_t j0 = pop_candidate(v0);
                     const uint32_t j1 = pop_candidate(v1);
@@ -617,14 +612,9 @@ cudaError_t launch_blend_t(const FrameGeometry& geo, const PrimBuffers& prim, co
                            const BlendOutputs& out, const TrainPixelBuffers& tout, FrameStatus* status, cudaStream_t stream) {
     using SL = SmemLayout<MODE, K, TRAIN>;
     auto kernel = blend_kernel<MODE, K, TRAIN, STATS>;
-    static bool configured[64] = {};
-    int device = 0;
-    cudaGetDevice(&device);
-    if (device >= 0 && device < 64 && !configured[device]) {
-        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SL::total));
-        if (err != cudaSuccess) return err;
-        configured[device] = true;
-    }
+    static PerDeviceOnce configured;
+    const cudaError_t err = configured.run([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SL::total)); });
+    if (err != cudaSuccess) return err;
     using TS = TileShape<MODE>;
     const dim3 grid((geo.width + TS::tw - 1) / TS::tw, (geo.height + TS::th - 1) / TS::th, 1);
     kernel<<<grid, TS::threads, SL::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, out.image, out.depth, out.alpha, tout,

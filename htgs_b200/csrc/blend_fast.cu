@@ -24,9 +24,6 @@
 
 #include <cuda_fp16.h>
 
-#ifndef HTGS_EXPERIMENT
-#define HTGS_EXPERIMENT 0   // timing experiments only (wrong images): 1 no core insertion, 2 no fragment loop
-#endif
 
 namespace htgs {
 
@@ -268,7 +265,7 @@ __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
         };
         auto commit = [&](uint32_t j, float depth, float4 frag) {
             if constexpr (kHybrid) {
-                if (HTGS_EXPERIMENT != 1 && depth < depth_max && frag.w >= MT::min_alpha_core) {
+                if (depth < depth_max && frag.w >= MT::min_alpha_core) {
                     frag = unpack_half4(core_replace<K>(keys, pay, tid, depth, pack_half4(frag.x, frag.y, frag.z, frag.w), row_max, kmax));
                     depth_max = KeyCodec<K>::decode(kmax);
                 }
@@ -284,7 +281,7 @@ __global__ void __launch_bounds__(kFastThreads) blend_fast_kernel(
                 transmittance_tail *= 1.0f - frag.w;
             }
         };
-        for (uint32_t it = 0; it < (HTGS_EXPERIMENT >= 2 ? 0u : n_iter); it += 2) {
+        for (uint32_t it = 0; it < n_iter; it += 2) {
             bool v0, v1;
             const uint32_t j0 = pop_candidate(v0);
             const uint32_t j1 = pop_candidate(v1);
@@ -374,16 +371,13 @@ template <int MODE, int K>
 cudaError_t launch_fast_k(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges, float* image,
                           bool to_chw, FrameStatus* status, cudaStream_t stream) {
     using SL = FastSmem<MODE, K>;
-    static bool configured[64] = {};
-    int device = 0;
-    cudaGetDevice(&device);
-    if (device >= 0 && device < 64 && !configured[device]) {
-        cudaError_t err = cudaFuncSetAttribute(blend_fast_kernel<MODE, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SL::total));
+    static PerDeviceOnce configured;
+    const cudaError_t cfg = configured.run([] {
+        const cudaError_t err = cudaFuncSetAttribute(blend_fast_kernel<MODE, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SL::total));
         if (err != cudaSuccess) return err;
-        err = cudaFuncSetAttribute(blend_fast_kernel<MODE, K>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        if (err != cudaSuccess) return err;
-        configured[device] = true;
-    }
+        return cudaFuncSetAttribute(blend_fast_kernel<MODE, K>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    });
+    if (cfg != cudaSuccess) return cfg;
     if (geo.n_tiles == 0) return cudaSuccess;
     blend_fast_kernel<MODE, K><<<dim3(geo.grid_w, geo.grid_h), kFastThreads, SL::total, stream>>>(
         tile_ranges, prims_sorted, reinterpret_cast<const FastRecord*>(prim.eval), prim.cull, image, uint32_t(geo.width), uint32_t(geo.height),

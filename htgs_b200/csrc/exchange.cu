@@ -8,7 +8,6 @@
 // coalesced, the tensor side moves whole rows of 4 to 540 bytes.
 #include "kernels.h"
 
-extern "C" void htgs_set_last_error(const char* message);   // api.cu
 
 namespace htgs {
 
@@ -57,7 +56,7 @@ __global__ void __launch_bounds__(kRowBlock) move_rows_kernel(const __grid_const
     }
 }
 
-int exchange_fail(int code, const char* message) { htgs_set_last_error(message); return code; }
+int exchange_fail(int code, const char* message) { htgs::set_last_error(message); return code; }
 
 int move_rows(bool gather, const HtgsRowTensors* tensors, const int64_t* index, int64_t count, float* packed, void* stream) {
     if (!tensors || count < 0 || tensors->n_tensors < 1 || tensors->n_tensors > HTGS_MAX_ROW_TENSORS)

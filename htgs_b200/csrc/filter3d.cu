@@ -8,7 +8,6 @@
 
 #include "kernels.h"
 
-extern "C" void htgs_set_last_error(const char* message);
 
 namespace {
 
@@ -91,7 +90,7 @@ void frustum_bounds(int32_t width, int32_t height, float focal_x, float focal_y,
 extern "C" int htgs_update_3d_filter_views(const float* positions, const HtgsFilterView* views, int32_t n_views, float* filter_3d,
                                            uint8_t* visibility_mask, int32_t n_points, float clipping_tolerance, float distance2filter, void* stream) {
     if (n_points < 0 || n_views < 0 || (n_points > 0 && n_views > 0 && (!positions || !views || !filter_3d || !visibility_mask))) {
-        htgs_set_last_error("htgs_update_3d_filter_views: null pointer or negative size");
+        htgs::set_last_error("htgs_update_3d_filter_views: null pointer or negative size");
         return HTGS_ERR_INVALID_ARGUMENT;
     }
     if (n_points == 0 || n_views == 0) return HTGS_OK;
@@ -114,7 +113,7 @@ extern "C" int htgs_update_3d_filter_views(const float* positions, const HtgsFil
                                                                                             distance2filter);
         const cudaError_t err = cudaGetLastError();
         if (err != cudaSuccess) {
-            htgs_set_last_error((std::string("htgs_update_3d_filter_views: ") + cudaGetErrorString(err)).c_str());
+            htgs::set_last_error((std::string("htgs_update_3d_filter_views: ") + cudaGetErrorString(err)).c_str());
             return HTGS_ERR_CUDA;
         }
     }
@@ -125,7 +124,7 @@ extern "C" int htgs_update_3d_filter(const float* positions, const float* w2c, f
                                      int32_t width, int32_t height, float focal_x, float focal_y, float center_x, float center_y, float near_plane,
                                      float clipping_tolerance, float distance2filter, void* stream) {
     if (n_points < 0 || (n_points > 0 && (!positions || !w2c || !filter_3d || !visibility_mask))) {
-        htgs_set_last_error("htgs_update_3d_filter: null pointer or negative size");
+        htgs::set_last_error("htgs_update_3d_filter: null pointer or negative size");
         return HTGS_ERR_INVALID_ARGUMENT;
     }
     if (n_points == 0) return HTGS_OK;
@@ -139,7 +138,7 @@ extern "C" int htgs_update_3d_filter(const float* positions, const float* w2c, f
                                                                                   bottom, near_plane, distance2filter);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) {
-        htgs_set_last_error((std::string("htgs_update_3d_filter: ") + cudaGetErrorString(err)).c_str());
+        htgs::set_last_error((std::string("htgs_update_3d_filter: ") + cudaGetErrorString(err)).c_str());
         return HTGS_ERR_CUDA;
     }
     return HTGS_OK;

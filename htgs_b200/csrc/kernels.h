@@ -4,7 +4,28 @@
 
 #include "common.cuh"
 
+#include <atomic>
+#include <mutex>
+
 namespace htgs {
+
+// One-time, per-device set-up of a kernel instantiation (its dynamic shared-memory limit), safe when several host
+// threads, each with its own context, launch the same kernel at once.  A set-up that fails is retried by the next call.
+struct PerDeviceOnce {
+    std::mutex mutex;
+    std::atomic<bool> done[64] = {};
+    template <typename F> cudaError_t run(F&& setup) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (device < 0 || device >= 64) return setup();
+        if (done[device].load(std::memory_order_acquire)) return cudaSuccess;
+        std::lock_guard<std::mutex> lock(mutex);
+        if (done[device].load(std::memory_order_relaxed)) return cudaSuccess;
+        const cudaError_t err = setup();
+        if (err == cudaSuccess) done[device].store(true, std::memory_order_release);
+        return err;
+    }
+};
 
 struct PrimBuffers {
     uint32_t* n_touched;      // [N]
@@ -95,8 +116,9 @@ cudaError_t launch_blend_fast(int mode, int K, const FrameGeometry& geo, const P
                               float* image, bool to_chw, FrameStatus* status, cudaStream_t stream);
 
 // weights.cu
+// `credit_tail` (HYBRID_BLEND only): also run the second walk that credits `alpha * tail weight` to every fragment.
 cudaError_t launch_max_weights(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
-                               float* max_weights, float weight_threshold, cudaStream_t stream);
+                               float* max_weights, float weight_threshold, bool credit_tail, cudaStream_t stream);
 
 // train.cu: backward pass
 struct GradAccumBuffers {
@@ -114,5 +136,12 @@ cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsV
                             const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, cudaEvent_t outputs_cleared, int sm_count,
                             cudaStream_t stream);   // `outputs_cleared`: event after which the six tensors are zero, or null to clear them here
 cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs& out, cudaStream_t stream);
+
+
+// api.cu: internals shared with the other translation units (C++ linkage: not part of the C-ABI).
+int backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                        const float* grad_image, const float* image, const HtgsGradients* grads, void* accum, void* stream);
+int context_device(const HtgsContext* ctx);
+void set_last_error(const char* message);   // message htgs_last_error() returns on the calling thread
 
 }  // namespace htgs

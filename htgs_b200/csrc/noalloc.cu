@@ -21,24 +21,17 @@ float4* g_static_accum_ptr[kMaxDevices] = {};                     // device addr
 
 }  // namespace
 
-// defined in api.cu
-extern "C" int htgs_backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs,
-                                        uint32_t n_instances, const float* grad_image, const float* image, const HtgsGradients* grads,
-                                        void* accum, void* stream);
-extern "C" int htgs_context_device(const HtgsContext* ctx);
-extern "C" void htgs_set_last_error(const char* message);
-
 extern "C" int htgs_backward_static_max_gaussians(void) { return kStaticMaxGaussians; }
 
 extern "C" int htgs_backward_static(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                                     const float* grad_image, const float* image, const HtgsGradients* grads, void* stream) {
-    if (!ctx || !scene) { htgs_set_last_error("htgs_backward_static: null argument"); return HTGS_ERR_INVALID_ARGUMENT; }
+    if (!ctx || !scene) { htgs::set_last_error("htgs_backward_static: null argument"); return HTGS_ERR_INVALID_ARGUMENT; }
     if (scene->n_primitives > kStaticMaxGaussians) {
-        htgs_set_last_error("htgs_backward_static: scene has more than 131072 Gaussians, the capacity of the built-in scratch; use htgs_backward with a caller-provided scratch buffer");
+        htgs::set_last_error("htgs_backward_static: scene has more than 131072 Gaussians, the capacity of the built-in scratch; use htgs_backward with a caller-provided scratch buffer");
         return HTGS_ERR_INVALID_ARGUMENT;
     }
-    const int device = htgs_context_device(ctx);
-    if (device < 0 || device >= kMaxDevices) { htgs_set_last_error("htgs_backward_static: device index out of range"); return HTGS_ERR_INVALID_ARGUMENT; }
+    const int device = htgs::context_device(ctx);
+    if (device < 0 || device >= kMaxDevices) { htgs::set_last_error("htgs_backward_static: device index out of range"); return HTGS_ERR_INVALID_ARGUMENT; }
     if (!g_static_accum_ptr[device]) {
         // First call on this device: translate the host-side symbol into the device address, with that device current.
         // (The symbol name itself is NOT a device pointer in host code; passing it to a kernel would be wrong.)
@@ -48,10 +41,10 @@ extern "C" int htgs_backward_static(HtgsContext* ctx, const HtgsScene* scene, co
         void* ptr = nullptr;
         if (err == cudaSuccess) err = cudaGetSymbolAddress(&ptr, g_static_accum);
         if (err != cudaSuccess || !ptr) {
-            htgs_set_last_error((std::string("htgs_backward_static: cudaGetSymbolAddress failed: ") + cudaGetErrorString(err)).c_str());
+            htgs::set_last_error((std::string("htgs_backward_static: cudaGetSymbolAddress failed: ") + cudaGetErrorString(err)).c_str());
             return HTGS_ERR_CUDA;
         }
         g_static_accum_ptr[device] = static_cast<float4*>(ptr);
     }
-    return htgs_backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, g_static_accum_ptr[device], stream);
+    return htgs::backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, g_static_accum_ptr[device], stream);
 }

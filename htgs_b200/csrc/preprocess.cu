@@ -312,16 +312,16 @@ __global__ void __launch_bounds__(kFinishBlock) preprocess_finish_kernel(
 }
 
 int sm_count_of_current_device() {
-    static int cached[64] = {};
+    static std::atomic<int> cached[64] = {};
     int device = 0;
     cudaGetDevice(&device);
     if (device < 0 || device >= 64) return 148;
-    if (!cached[device]) {
-        int n = 0;
+    int n = cached[device].load(std::memory_order_relaxed);
+    if (!n) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
-        cached[device] = n;
+        cached[device].store(n, std::memory_order_relaxed);
     }
-    return cached[device];
+    return n;
 }
 
 template <int MODE, bool TRAIN, bool FAST>

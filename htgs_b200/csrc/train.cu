@@ -39,6 +39,20 @@ __device__ __forceinline__ void red_add_v4(float4* addr, const float4& v) {
 __device__ __forceinline__ float rcp_approx(float x) { float y; asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ float exp_approx(float x) { float y; asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f)); return y; }
 
+// Whether the forward pass rejected the fragment for `alpha < min_alpha`.  The forward decides with IEEE arithmetic
+// (1.0f / denominator, expf); the approximate alpha computed here differs from that value by less than 1e-6 of itself
+// (1 ulp reciprocal, 2 ulp exp2, and the rounding of an exponent of magnitude <= 8), so it settles the question unless
+// it lies within 4e-6 of the threshold, and only then is the forward's own arithmetic repeated: the decision is the
+// forward's in every case, the approximations only ever scale gradient terms.
+template <typename MT>
+__device__ __forceinline__ bool rejected_by_forward(float alpha_approx, float opacity, float numerator_rho2, float denominator) {
+    if (fabsf(alpha_approx - MT::min_alpha) < 4e-6f * MT::min_alpha) {
+        const float G = expf(-0.5f * numerator_rho2 * (1.0f / denominator));
+        return fminf(opacity * G, kMaxFragmentAlpha) < MT::min_alpha;
+    }
+    return alpha_approx < MT::min_alpha;
+}
+
 struct PairGrad {      // what one (pixel, Gaussian) pair adds to the Gaussian's record
     float4 dT1, dT2, dT4;
 };
@@ -347,7 +361,7 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
             const float denominator_rcp = rcp_approx(denominator);
             const float G = exp_approx(-0.5f * numerator_rho2 * denominator_rcp);
             const float alpha = fminf(rgba.w * G, kMaxFragmentAlpha);
-            if constexpr (!kFirstK) { if (alpha < MT::min_alpha) continue; }
+            if constexpr (!kFirstK) { if (rejected_by_forward<MT>(alpha, rgba.w, numerator_rho2, denominator)) continue; }
             float3 dL_drgb;
             float dL_dalpha;
             if (core_idx >= 0) {
@@ -499,7 +513,7 @@ __global__ void __launch_bounds__(64) backward_global_kernel(
                     const float4 rgba = s_rgba[j];
                     const float opacity = rgba.w;
                     const float alpha = fminf(opacity * G, kMaxFragmentAlpha);
-                    if (!(alpha < MT::min_alpha)) {
+                    if (!rejected_by_forward<MT>(alpha, opacity, numerator_rho2, denominator)) {
                         const float blending_weight = transmittance * alpha;
                         const float3 dL_drgb = blending_weight * grad_pixel;
                         v[12] = dL_drgb.x; v[13] = dL_drgb.y; v[14] = dL_drgb.z;
@@ -689,13 +703,10 @@ cudaError_t launch_tile_backward(bool abs_grad, const FrameGeometry& geo, const 
     const dim3 grid(geo.grid_w, geo.grid_h, 1);
     auto launch = [&](auto kernel) -> cudaError_t {
         // both instantiations have the same function-pointer type, so this lambda (and a static in it) is shared by them
-        static bool configured[2][64] = {};
-        int device = 0;
-        cudaGetDevice(&device);
-        if (SM::total > 48 * 1024 && device >= 0 && device < 64 && !configured[abs_grad][device]) {
-            const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SM::total));
+        static PerDeviceOnce configured[2];
+        if (SM::total > 48 * 1024) {
+            const cudaError_t err = configured[abs_grad ? 1 : 0].run([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SM::total)); });
             if (err != cudaSuccess) return err;
-            configured[abs_grad][device] = true;
         }
         kernel<<<grid, kBwdThreads, SM::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, tin, grad_image, VPM, accum,
                                                 uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w));

@@ -32,7 +32,7 @@ __device__ __forceinline__ void raise_weight(unsigned int* max_weights, uint32_t
 template <int MODE, int K>
 __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
-    const CullRecord* __restrict__ cull, unsigned int* __restrict__ max_weights, uint32_t width, uint32_t height, uint32_t grid_w, float weight_threshold)
+    const CullRecord* __restrict__ cull, unsigned int* __restrict__ max_weights, uint32_t width, uint32_t height, uint32_t grid_w, float weight_threshold, bool credit_tail)
 {
     using MT = ModeTraits<MODE>;
     using WS = WShape<MODE>;
@@ -62,7 +62,8 @@ __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
     float second_pass_weight = 0.0f;
     const bool outline_in_second_pass = weight_threshold >= MT::min_alpha;
 
-    for (int pass = 0; pass < ((kHybrid || kOit) ? 2 : 1); ++pass) {
+    const int n_passes = (kOit || (kHybrid && credit_tail)) ? 2 : 1;
+    for (int pass = 0; pass < n_passes; ++pass) {
         const bool lane_active = !done && (pass == 0 || second_pass_weight >= weight_threshold);
         if (pass == 1 && __syncthreads_count(lane_active) == 0) break;   // no pixel of the tile has a tail to credit
         for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += WS::threads) {
@@ -220,36 +221,36 @@ __global__ void __launch_bounds__(WShape<MODE>::threads) max_weights_kernel(
 
 template <int MODE, int K>
 cudaError_t launch_w(const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges, float* max_weights,
-                     float weight_threshold, cudaStream_t stream) {
+                     float weight_threshold, bool credit_tail, cudaStream_t stream) {
     const dim3 grid(geo.grid_w, geo.grid_h, 1);
     max_weights_kernel<MODE, K><<<grid, WShape<MODE>::threads, 0, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, reinterpret_cast<unsigned int*>(max_weights),
-                                                                            uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), weight_threshold);
+                                                                            uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), weight_threshold, credit_tail);
     return cudaGetLastError();
 }
 
 template <int MODE>
 cudaError_t launch_w_k(int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges, float* max_weights,
-                       float weight_threshold, cudaStream_t stream) {
+                       float weight_threshold, bool credit_tail, cudaStream_t stream) {
     switch (K) {
-        case 32: return launch_w<MODE, 32>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
-        case 16: return launch_w<MODE, 16>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
-        case 8: return launch_w<MODE, 8>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
-        case 4: return launch_w<MODE, 4>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
-        case 2: return launch_w<MODE, 2>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
-        default: return launch_w<MODE, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        case 32: return launch_w<MODE, 32>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
+        case 16: return launch_w<MODE, 16>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
+        case 8: return launch_w<MODE, 8>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
+        case 4: return launch_w<MODE, 4>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
+        case 2: return launch_w<MODE, 2>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
+        default: return launch_w<MODE, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
     }
 }
 
 }  // namespace
 
 cudaError_t launch_max_weights(int mode, int K, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
-                               float* max_weights, float weight_threshold, cudaStream_t stream) {
+                               float* max_weights, float weight_threshold, bool credit_tail, cudaStream_t stream) {
     const int k = effective_k(mode, K);
     switch (mode) {
-        case HTGS_MODE_HYBRID_BLEND: return launch_w_k<HTGS_MODE_HYBRID_BLEND>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
-        case HTGS_MODE_ALPHA_BLEND_FIRST_K: return launch_w_k<HTGS_MODE_ALPHA_BLEND_FIRST_K>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
-        case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: return launch_w<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
-        case HTGS_MODE_OIT_BLEND: return launch_w<HTGS_MODE_OIT_BLEND, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, stream);
+        case HTGS_MODE_HYBRID_BLEND: return launch_w_k<HTGS_MODE_HYBRID_BLEND>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
+        case HTGS_MODE_ALPHA_BLEND_FIRST_K: return launch_w_k<HTGS_MODE_ALPHA_BLEND_FIRST_K>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
+        case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: return launch_w<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
+        case HTGS_MODE_OIT_BLEND: return launch_w<HTGS_MODE_OIT_BLEND, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -17,6 +17,31 @@ from .._native import HtgsFrameInfo, HtgsScene, HtgsView
 
 last_frame_info = None  # HtgsFrameInfo of the most recent call (diagnostics)
 
+# Deferred checks (torch_bindings.rasterization.set_deferred_checks): `render` and `_C_benchmarking.benchmark` queue the frame
+# with htgs_render_async and return without waiting for the GPU; the frame's status is checked by the next call on the same
+# CUDA stream, or by `frame_results`.  Each CUDA stream gets a context (workspace) of its own, so one host thread can keep
+# frames in flight on several streams.  The tensors of a queued frame are kept alive here until its check.
+deferred_checks = False
+_queued: dict = {}
+
+
+def frame_results(device=None):
+    """Waits for and checks every frame this host thread queued with deferred checks (on `device`, or on all devices);
+    raises what the blocking call would have raised.  Returns the HtgsFrameInfo of each context that was checked."""
+    global last_frame_info
+    index = None if device is None else _device_index(torch.device(device))
+    infos = []
+    for ctx in _native.contexts_of_thread(index):
+        if ctx not in _queued:
+            continue
+        info = HtgsFrameInfo()
+        rc = _native.lib().htgs_frame_result(ctx, ctypes.byref(info))
+        _queued.pop(ctx, None)
+        _native.check(rc)
+        infos.append(info)
+        last_frame_info = info
+    return infos
+
 
 def _check_inputs(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_position):
     n = positions.shape[0] if positions.dim() >= 1 else -1
@@ -65,7 +90,14 @@ def render(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_p
         scene, view = _scene_view(tensors, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases, width, height, near_plane, far_plane, scale_modifier)
         info = HtgsFrameInfo()
         stream = torch.cuda.current_stream(device).cuda_stream
-        rc = _native.lib().htgs_render(_native.context(device.index if device.index is not None else torch.cuda.current_device()),
+        if deferred_checks:
+            ctx = _native.context(_device_index(device), stream)
+            rc = _native.lib().htgs_render_async(ctx, ctypes.byref(scene), ctypes.byref(view), image.data_ptr(), depth.data_ptr(), None,
+                                                 int(bool(to_chw)), int(bool(use_median_depth)), stream)
+            _queued[ctx] = (tensors, M, VPM, cam_position, image, depth)
+            _native.check(rc)
+            return image, depth
+        rc = _native.lib().htgs_render(_native.context(_device_index(device)),
                                        ctypes.byref(scene), ctypes.byref(view), image.data_ptr(), depth.data_ptr(), None, int(bool(to_chw)),
                                        int(bool(use_median_depth)), None, 0, stream, ctypes.byref(info))
     _native.check(rc)

@@ -26,6 +26,12 @@ def benchmark(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, ca
                                      scale_modifier)
         info = HtgsFrameInfo()
         stream = torch.cuda.current_stream(device).cuda_stream
+        if _C.deferred_checks:     # see _C.deferred_checks: queued without a host wait, checked by the next call on this stream
+            ctx = _native.context(_C._device_index(device), stream)
+            rc = _native.lib().htgs_render_fast_async(ctx, ctypes.byref(scene), ctypes.byref(view), image.data_ptr(), int(bool(to_chw)), stream)
+            _C._queued[ctx] = (tensors, M, VPM, cam_position, image)
+            _native.check(rc)
+            return image
         rc = _native.lib().htgs_render_fast(_native.context(_C._device_index(device)), ctypes.byref(scene), ctypes.byref(view), image.data_ptr(),
                                             int(bool(to_chw)), None, 0, stream, ctypes.byref(info))
     _native.check(rc)

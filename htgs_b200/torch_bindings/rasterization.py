@@ -60,6 +60,24 @@ def last_training_visibility(device, with_event: bool = False):
     return (visible, ready) if with_event else visible
 
 
+# Forward renders without a host wait.  No counterpart in the reference (its `rasterize` blocks in mid-frame).
+def set_deferred_checks(enable: bool) -> None:
+    """With deferred checks `rasterize` and `fast_rasterize` queue the frame on the current CUDA stream and return at once;
+    the frame's status (device error flags, instance buffers that were too small) is checked by the next call on that
+    stream or by `frame_results()`.  Each CUDA stream renders with a workspace of its own, so one host thread keeps two
+    frames in flight by alternating between two streams.  Render every kind of view once with the checks on (the default)
+    first: a frame whose instance buffers turn out too small is rendered again when it is checked, i.e. after work queued
+    behind it has already read its image (`HtgsFrameInfo.reruns` of `frame_results()` tells)."""
+    if not enable:
+        _C.frame_results()
+    _C.deferred_checks = bool(enable)
+
+
+def frame_results(device=None):
+    """Waits for and checks the frames queued with deferred checks by this host thread; see `set_deferred_checks`."""
+    return _C.frame_results(device)
+
+
 class _Rasterize(torch.autograd.Function):
     @staticmethod
     def forward(ctx: Any, positions, scales, rotations, opacities, sh_0, sh_rest, densification_info,

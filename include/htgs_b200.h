@@ -11,7 +11,9 @@
  * Threading: a context is bound to one CUDA device and must not be used from
  * two host threads at once.  Calls are stream-ordered on the stream passed in
  * and re-entrant across contexts (camera matrices are read from device memory
- * by the kernels; nothing is uploaded to __constant__ memory).
+ * by the kernels; nothing is uploaded to __constant__ memory).  An entry point
+ * that takes a context makes the context's device current while it runs and
+ * puts the caller's current device back before it returns.
  */
 #ifndef HTGS_B200_H
 #define HTGS_B200_H
@@ -128,6 +130,27 @@ size_t htgs_render_workspace_bytes(const HtgsScene* scene, const HtgsView* view,
 int htgs_render(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
                 int to_chw, int use_median_depth, void* workspace, size_t workspace_bytes, void* stream, HtgsFrameInfo* info);
 
+/*
+ * Forward render without a host wait.  No counterpart in the reference, which blocks in the middle of every frame to
+ * read the instance count (rasterization/src/hybrid_blend/inference.cu:118-119); htgs_render still waits once, at its end.
+ *
+ * htgs_render_async queues the whole frame on `stream` (same arguments and results as htgs_render, always with the
+ * context's own workspace) and returns at once; the 64-byte frame status lands in pinned host memory behind the frame.
+ * htgs_frame_result waits for that status, checks it and fills `info`; the next call of any frame-level entry point on
+ * the same context performs the same check first and reports a failure of the earlier frame as its own.  One host thread
+ * keeps two frames in flight by alternating between two contexts, each with its own stream.
+ *
+ * What the deferred check can find: a device-side error flag, or instance buffers that were too small for the frame
+ * (the context sizes them from the frames it has seen).  In the second case the check grows the workspace and renders
+ * the frame again on the same stream before it returns (info->reruns > 0); work the caller queued on the stream between
+ * htgs_render_async and the check has then read an image without its instances.  A caller that cannot tolerate that
+ * renders each new kind of view once with htgs_render first, or checks info->reruns and repeats the dependent work.
+ * The scene, view and output pointers must stay valid until the check.
+ */
+int htgs_render_async(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, float* depth, float* alpha,
+                      int to_chw, int use_median_depth, void* stream);
+int htgs_frame_result(HtgsContext* ctx, HtgsFrameInfo* info);
+
 /* As htgs_render with HOST buffers: inputs are copied to the device and the image/depth back inside the
  * call (used for end-to-end measurement and by callers without device memory of their own). */
 int htgs_render_host(HtgsContext* ctx, const HtgsScene* host_scene, const HtgsView* host_view, float* host_image, float* host_depth,
@@ -213,7 +236,8 @@ int htgs_scatter_rows(const HtgsRowTensors* tensors, const int64_t* index, int64
  * the library, held until the process exits).  It exists for hosts that cannot hand over a scratch buffer
  * because they may not allocate device memory at the point of the call: a plug-in inside an application that
  * owns all allocations, or a process that has given every free byte to another allocator.  The call performs
- * no cudaMalloc / cudaFree and calls no allocating library routine.
+ * no cudaMalloc / cudaFree and calls no allocating library routine (the side stream and the events a context uses are
+ * created by htgs_create).
  *   - Scenes with more than htgs_backward_static_max_gaussians() (131072) Gaussians are rejected with
  *     HTGS_ERR_INVALID_ARGUMENT; use htgs_backward for those.
  *   - The first call on a device looks up the device address of the array (cudaGetSymbolAddress); make that
@@ -241,6 +265,8 @@ int htgs_backward_static(HtgsContext* ctx, const HtgsScene* scene, const HtgsVie
 int htgs_set_fast_deterministic(HtgsContext* ctx, int enable);
 int htgs_render_fast(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, int to_chw, void* workspace,
                      size_t workspace_bytes, void* stream, HtgsFrameInfo* info);
+/* htgs_render_fast without the host wait; the rules of htgs_render_async apply, htgs_frame_result completes it. */
+int htgs_render_fast_async(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* image, int to_chw, void* stream);
 
 /*
  * Per-Gaussian maximum blending weight over the pixels of one view.  Replaces `_C.update_max_weights` =
@@ -249,6 +275,11 @@ int htgs_render_fast(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* v
  */
 int htgs_update_max_weights(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, float* max_weights, float weight_threshold,
                             void* workspace, size_t workspace_bytes, void* stream, HtgsFrameInfo* info);
+/* HYBRID_BLEND only.  The reference's kernel source has a second walk over each tile's list that credits
+ * `alpha * tail weight` of the pixel to every fragment (rasterization/include/hybrid_blend/kernels/update_max_weights.cuh:170-210).
+ * enable = 1 performs that walk; enable = 0 credits the K-buffer (core) weights only.  See the library's design notes for
+ * which of the two the reference extension's build for this GPU was measured to produce. */
+int htgs_set_max_weights_tail_credit(HtgsContext* ctx, int enable);
 
 /*
  * 3D smoothing-filter update for one view.  Replaces `_C.update_3d_filter_cuda` = update_3d_filter_wrapper

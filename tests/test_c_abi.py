@@ -15,6 +15,20 @@ def test_library_exports_all_declared_symbols():
         assert hasattr(lib, name), f"{name} is declared in include/htgs_b200.h but not exported"
 
 
+def test_library_exports_nothing_the_header_does_not_declare():
+    """The reverse direction: every `htgs_*` C symbol the library exports is declared in include/htgs_b200.h."""
+    import subprocess
+    from htgs_b200 import _native, build
+    build.build()
+    out = subprocess.run(["nm", "-D", "--defined-only", _native.LIB_PATH], stdout=subprocess.PIPE, text=True, check=True).stdout
+    exported = {line.split()[-1] for line in out.splitlines() if len(line.split()) >= 3 and line.split()[-2] in ("T", "W")}
+    c_symbols = {name for name in exported if name.startswith("htgs_")}          # C++ internals are mangled (_ZN4htgs...)
+    declared = set(_native.exported_symbols())
+    assert c_symbols, "nm found no htgs_* symbol: is the library stripped?"
+    assert c_symbols <= declared, f"exported but not declared in the header: {sorted(c_symbols - declared)}"
+    assert declared <= c_symbols, f"declared but not exported: {sorted(declared - c_symbols)}"
+
+
 def test_version_and_error_string():
     from htgs_b200 import _native
     lib = _native.lib()

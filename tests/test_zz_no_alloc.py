@@ -76,3 +76,27 @@ def test_static_scratch_backward_rejects_scenes_above_its_capacity():
     sc = _native.HtgsScene(1, 1, 1, 1, 1, None, cap + 1, 0)   # never dereferenced: the size check comes first
     rc = lib.htgs_backward_static(_native.context(0), ctypes.byref(sc), None, None, 0, None, None, None, None)
     assert rc == _native.HTGS_ERR_INVALID_ARGUMENT and "131072" in _native.last_error()
+
+
+def test_static_scratch_backward_leaves_free_device_memory_unchanged():
+    """After one warm-up call (first launches load kernels and look up the built-in array), a call of
+    htgs_backward_static must not change the amount of free device memory the driver reports: nothing is allocated or freed."""
+    import torch
+    from htgs_b200 import _native
+    scene = scenes.tiny_scene(n=6000, size=128, seed=43, sh_degree=1)
+    view = scene.views[0]
+    sc, vw, blobs, n_inst, image, keep = _forward_state(scene, view, 0, 8)
+    n, total_sh = scene.n, scene.sh_rest.shape[1]
+    lib, ctx = _native.lib(), _native.context(0)
+    grad_image = torch.ones((3, view.height, view.width), device="cuda")
+    outs = [torch.empty(shape, device="cuda") for shape in ((n, 3), (n, 3), (n, 4), (n, 1), (n, 1, 3), (n, total_sh, 3))]
+    grads = _native.HtgsGradients(*(o.data_ptr() for o in outs), None, 0, None, 0, 0)
+    args = (ctx, ctypes.byref(sc), ctypes.byref(vw), ctypes.byref(blobs), n_inst, grad_image.data_ptr(), image.data_ptr(), ctypes.byref(grads), None)
+    assert lib.htgs_backward_static(*args) == _native.HTGS_OK, _native.last_error()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    assert lib.htgs_backward_static(*args) == _native.HTGS_OK, _native.last_error()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    del keep
