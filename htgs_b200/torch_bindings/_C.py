@@ -225,6 +225,12 @@ def backward(densification_info, grad_image, image, positions, scales, rotations
     return grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest
 
 
+# HYBRID_BLEND `update_max_weights`: False (default) reproduces the reference extension's output, which credits K-buffer (core)
+# weights only; True also performs the second walk of the reference's kernel SOURCE that credits `alpha * tail weight` to
+# every fragment (torch_bindings.rasterization.set_max_weights_tail_credit).
+max_weights_tail_credit = False
+
+
 def update_max_weights(max_weights, positions, scales, rotations, opacities, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases,
                        width, height, near_plane, far_plane, scale_modifier, weight_threshold):
     """`_C.update_max_weights` (rasterization/include/rasterization_api.h:79-97): raises `max_weights` [N,1] in place."""
@@ -248,6 +254,7 @@ def update_max_weights(max_weights, positions, scales, rotations, opacities, M, 
         view = HtgsView(M.data_ptr(), VPM.data_ptr(), cam_position.data_ptr(), int(rasterizer_mode), int(K), int(active_sh_bases), int(width), int(height),
                         float(near_plane), float(far_plane), float(scale_modifier))
         info = HtgsFrameInfo()
+        _native.check(_native.lib().htgs_set_max_weights_tail_credit(_native.context(_device_index(device)), int(max_weights_tail_credit)))
         rc = _native.lib().htgs_update_max_weights(_native.context(_device_index(device)), ctypes.byref(scene), ctypes.byref(view), max_weights.data_ptr(),
                                                    float(weight_threshold), None, 0, torch.cuda.current_stream(device).cuda_stream, ctypes.byref(info))
     _native.check(rc)

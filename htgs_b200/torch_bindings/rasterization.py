@@ -123,5 +123,14 @@ def fast_rasterize(positions, scales, rotations, opacities, sh_0, sh_rest, setti
     return _C_benchmarking.benchmark(positions, scales, rotations, opacities, sh_0, sh_rest, *settings.as_tuple(), to_chw)
 
 
+def set_max_weights_tail_credit(enable: bool) -> None:
+    """HYBRID_BLEND `update_max_weights` only.  The reference's kernel source walks every tile's list a second time and
+    credits `alpha * tail weight` to each fragment (hybrid_blend/kernels/update_max_weights.cuh:170-210), but the extension
+    built from it with nvcc 12.9 for sm_100a never does (a Gaussian that only lands in the tail keeps weight 0; the same
+    source compiled without device-code optimisation does credit it).  The default (False) reproduces the extension's
+    output bit for bit; True gives what the source describes.  No counterpart in the reference."""
+    _C.max_weights_tail_credit = bool(enable)
+
+
 def update_max_weights(max_weights, positions, scales, rotations, opacities, settings: RasterizerSettings, weight_threshold: float) -> None:
     return _C.update_max_weights(max_weights, positions, scales, rotations, opacities, *settings.as_tuple(), weight_threshold)
