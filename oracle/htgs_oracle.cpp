@@ -545,9 +545,13 @@ int64_t run_render(const float* positions, const float* scales, const float* rot
 // R/include/hybrid_blend/kernels/update_max_weights.cuh:59-212 (core weights, then a second pass over the
 // tile's list that credits alpha * tail_weight to every fragment inside the cutoff),
 // first_k :60-, global_ordering :59-, oit :57- analogues.  Sequential over tiles (small cases only).
+// `hybrid_tail_credit` = false restates what the reference EXTENSION computes for HYBRID_BLEND: its link keeps
+// alpha_blend_first_k's copy of the dispatcher template both modes define (R/src/hybrid_blend/update_max_weights.cu:15-28,
+// R/src/alpha_blend_first_k/update_max_weights.cu:15-28), so HYBRID's lists are walked by FIRST_K's kernel, which keeps
+// the K nearest fragments with alpha >= 1/20 and has no second pass: HYBRID's core weights and nothing else.
 // ----------------------------------------------------------------------------
 template <typename R>
-void max_weights_image(int mode, const BlendIn<R>& in, R weight_threshold, R* max_weights) {
+void max_weights_image(int mode, const BlendIn<R>& in, R weight_threshold, R* max_weights, bool hybrid_tail_credit) {
     const ModeConstants mc = mode_constants(mode);
     const int K = in.K;
     auto raise = [&](int64_t g, R w) { if (max_weights[g] < w) max_weights[g] = w; };
@@ -598,7 +602,7 @@ void max_weights_image(int mode, const BlendIn<R>& in, R weight_threshold, R* ma
                         if (w < weight_threshold || ki[k] == UINT32_MAX) continue;
                         raise(ki[k], w);
                     }
-                    if (mode == 0 && alpha_sum >= weight_threshold) second = tc * (R(1) - t) * (R(1) / alpha_sum);
+                    if (mode == 0 && hybrid_tail_credit && alpha_sum >= weight_threshold) second = tc * (R(1) - t) * (R(1) / alpha_sum);
                 } else if (alpha_sum >= weight_threshold) {
                     second = (R(1) - t) * (R(1) / alpha_sum);
                 }
@@ -679,18 +683,18 @@ void htgs_oracle_blend_f64(int mode, const uint32_t* ranges, const uint32_t* pri
 }
 
 void htgs_oracle_max_weights_f32(int mode, const uint32_t* ranges, const uint32_t* prim_idx, const float* vpmt1, const float* vpmt2, const float* vpmt4,
-                                 const float* mt3, const float* rgba, int width, int height, int K, float weight_threshold, float* max_weights) {
+                                 const float* mt3, const float* rgba, int width, int height, int K, float weight_threshold, float* max_weights, int hybrid_tail_credit) {
     const ModeConstants mc = mode_constants(mode);
     BlendIn<float> in{ranges, prim_idx, vpmt1, vpmt2, vpmt4, mt3, rgba, width, height, (width + mc.tile_w - 1) / mc.tile_w,
                       (height + mc.tile_h - 1) / mc.tile_h, K, false};
-    max_weights_image<float>(mode, in, weight_threshold, max_weights);
+    max_weights_image<float>(mode, in, weight_threshold, max_weights, hybrid_tail_credit != 0);
 }
 void htgs_oracle_max_weights_f64(int mode, const uint32_t* ranges, const uint32_t* prim_idx, const double* vpmt1, const double* vpmt2, const double* vpmt4,
-                                 const double* mt3, const double* rgba, int width, int height, int K, double weight_threshold, double* max_weights) {
+                                 const double* mt3, const double* rgba, int width, int height, int K, double weight_threshold, double* max_weights, int hybrid_tail_credit) {
     const ModeConstants mc = mode_constants(mode);
     BlendIn<double> in{ranges, prim_idx, vpmt1, vpmt2, vpmt4, mt3, rgba, width, height, (width + mc.tile_w - 1) / mc.tile_w,
                        (height + mc.tile_h - 1) / mc.tile_h, K, false};
-    max_weights_image<double>(mode, in, weight_threshold, max_weights);
+    max_weights_image<double>(mode, in, weight_threshold, max_weights, hybrid_tail_credit != 0);
 }
 
 // whole forward (preprocess -> bin -> blend); returns the instance count

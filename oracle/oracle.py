@@ -119,8 +119,10 @@ def blend(mode: int, ranges, prim_idx, pre: dict, view, K: int, use_median_depth
     return image, depth, alpha
 
 
-def max_weights(mode: int, ranges, prim_idx, pre: dict, view, K: int, weight_threshold: float, start=None):
-    """update_max_weights from preprocess outputs and a sorted instance list (sequential; small cases only)."""
+def max_weights(mode: int, ranges, prim_idx, pre: dict, view, K: int, weight_threshold: float, start=None, hybrid_tail_credit: bool = True):
+    """update_max_weights from preprocess outputs and a sorted instance list (sequential; small cases only).
+    `hybrid_tail_credit`: HYBRID_BLEND as the reference's kernel source describes it (True) or as the reference extension
+    computes it (False: core weights only, see htgs_oracle.cpp)."""
     dtype = pre["vpmt1"].dtype
     n = pre["vpmt1"].shape[0]
     out = np.zeros(n, dtype) if start is None else np.ascontiguousarray(start, dtype).reshape(-1).copy()
@@ -129,7 +131,7 @@ def max_weights(mode: int, ranges, prim_idx, pre: dict, view, K: int, weight_thr
     thr = ctypes.c_double(weight_threshold) if dtype == np.float64 else ctypes.c_float(weight_threshold)
     fn = lib().htgs_oracle_max_weights_f64 if dtype == np.float64 else lib().htgs_oracle_max_weights_f32
     fn(int(mode), _p(ranges), _p(prim_idx), _p(pre["vpmt1"]), _p(pre["vpmt2"]), _p(pre["vpmt4"]), _p(pre["mt3"]), _p(pre["rgba"]),
-       int(view.width), int(view.height), int(K), thr, _p(out))
+       int(view.width), int(view.height), int(K), thr, _p(out), int(bool(hybrid_tail_credit)))
     return out
 
 

@@ -113,3 +113,26 @@ def test_reference_fast_path_stays_near_exact_oracle(oracle_lib, name, mode, K):
     assert d.mean() < 2e-4
     assert np.mean(d > 1e-3) < 2e-3
     assert d.max() < 0.1
+
+
+@pytest.mark.parametrize("name,mode,K", list(all_cases()))
+def test_max_weights_match_reference(oracle_lib, name, mode, K):
+    """`update_max_weights` of the reference extension (golden vectors) against the oracle fed with the reference's own tile
+    lists.  HYBRID_BLEND is pinned in the form the extension computes it (K-buffer weights only: its link resolves HYBRID's
+    kernel dispatcher to FIRST_K's copy); with the tail credit of the kernel source the oracle can only give more."""
+    from golden.make_golden import MAX_WEIGHT_THRESHOLD
+    _, scene, gold = load_case(name)
+    key = f"m{mode}_k{K}_max_weights"
+    if key not in gold.files:
+        pytest.skip("golden file predates the max-weight vectors")
+    view = scene.views[0]
+    tag = f"m{mode}_k{K}"
+    pre = oracle_lib.preprocess(scene, view, mode, dtype=np.float32)
+    pre["rgba"][:, 3] = scene.opacities.reshape(-1)
+    want = gold[key].reshape(-1)
+    got = oracle_lib.max_weights(mode, gold[f"{tag}_ranges"], gold[f"{tag}_sorted_prims"], pre, view, K, MAX_WEIGHT_THRESHOLD, hybrid_tail_credit=False)
+    d = np.abs(got - want)
+    assert np.mean(d > 1e-5) < 5e-3 and d.max() < 0.06, f"{np.mean(d > 1e-5):.2e} of the weights differ, max {d.max():.3e}"
+    if mode == scenes.HYBRID_BLEND:
+        with_tail = oracle_lib.max_weights(mode, gold[f"{tag}_ranges"], gold[f"{tag}_sorted_prims"], pre, view, K, MAX_WEIGHT_THRESHOLD, hybrid_tail_credit=True)
+        assert (with_tail >= got).all() and (with_tail > got + 1e-4).sum() > 0
