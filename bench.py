@@ -391,7 +391,7 @@ def main():
 
         def resident(self, view_idx):
             render_any(cams_dev[view_idx])
-            if ref_mod is None and not our_C.deferred_checks:
+            if ref_mod is None and not mod.rasterization.deferred_checks():
                 self.launches += our_C.last_frame_info.kernel_launches
 
         def e2e(self, view_idx):

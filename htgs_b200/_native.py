@@ -180,6 +180,33 @@ def check(code: int) -> None:
 _contexts: Dict[tuple, int] = {}
 _ctx_lock = threading.Lock()
 
+# Which binding serves the Python surface: the compiled torch extension modules (htgs_b200/pybind, the default when they
+# have been built) or this ctypes binding (no compile step beyond the core library).  HTGS_B200_BINDING=pybind|ctypes|auto.
+_pybind_modules = None
+
+
+def pybind_modules():
+    """(_C, _C_benchmarking) of htgs_b200.pybind when they are the active binding, else None."""
+    global _pybind_modules
+    if _pybind_modules is None:
+        choice = os.environ.get("HTGS_B200_BINDING", "auto").lower()
+        if choice not in ("auto", "pybind", "ctypes"):
+            raise ValueError("HTGS_B200_BINDING must be auto, pybind or ctypes")
+        _pybind_modules = False
+        if choice != "ctypes":
+            try:
+                from . import pybind
+                _pybind_modules = pybind.load()
+            except ImportError:
+                if choice == "pybind":
+                    raise
+    return _pybind_modules or None
+
+
+def active_binding() -> str:
+    return "pybind" if pybind_modules() else "ctypes"
+
+
 
 def context(device_index: int, stream: int = 0) -> int:
     """One library context per (CUDA device, host thread, stream key) of this process, created on first use.  A context owns
@@ -187,6 +214,9 @@ def context(device_index: int, stream: int = 0) -> int:
     concurrently, or one thread queueing frames on two CUDA streams without waiting (`htgs_render_async`) - must not share
     one.  Blocking calls pass no stream key and share the thread's context; the non-blocking path passes the handle of the
     stream it queues on."""
+    mods = pybind_modules()
+    if mods:     # both bindings use one set of contexts: the extension module's (per host thread, like this table)
+        return mods[0].context_handle(int(device_index), int(stream))
     key = (int(device_index), threading.get_ident(), int(stream))
     ctx = _contexts.get(key)
     if ctx is None:
@@ -202,6 +232,9 @@ def context(device_index: int, stream: int = 0) -> int:
 
 def contexts_of_thread(device_index: Optional[int] = None):
     """Contexts the calling host thread has created (on one device, or on all)."""
+    mods = pybind_modules()
+    if mods:
+        return list(mods[0].context_handles(-1 if device_index is None else int(device_index)))
     me = threading.get_ident()
     with _ctx_lock:
         return [ctx for (dev, thread, _), ctx in _contexts.items() if thread == me and (device_index is None or dev == int(device_index))]

@@ -1,7 +1,8 @@
-"""Builds libhtgs_b200.so (the sm_100a rasterizer core) in-tree with nvcc.
+"""Builds libhtgs_b200.so (the sm_100a rasterizer core) in-tree with nvcc, and the two torch extension modules over it.
 
-No torch headers are involved: the core is a plain C-ABI shared library.
-Run `python -m htgs_b200.build` (add `-v` for ptxas resource usage).
+No torch headers are involved in the core: it is a plain C-ABI shared library.  The torch / pybind layer is one host-only
+source (csrc/bindings.cpp) compiled twice with the host compiler into htgs_b200/pybind/_C.*.so and _C_benchmarking.*.so.
+Run `python -m htgs_b200.build` (add `-v` for ptxas resource usage, `--no-bindings` to skip the torch modules).
 """
 from __future__ import annotations
 
@@ -73,5 +74,65 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+PYBIND_DIR = os.path.join(HERE, "pybind")
+BINDINGS_SRC = os.path.join(CSRC, "bindings.cpp")
+
+
+def binding_paths():
+    import sysconfig
+    suffix = sysconfig.get_config_var("EXT_SUFFIX")
+    return os.path.join(PYBIND_DIR, "_C" + suffix), os.path.join(PYBIND_DIR, "_C_benchmarking" + suffix)
+
+
+def build_bindings(force: bool = False) -> tuple:
+    """Compiles csrc/bindings.cpp into the extension modules `_C` and `_C_benchmarking` (same names and signatures as the
+    reference's pybind modules) and links them against libhtgs_b200.so.  Host compiler only; takes a minute or two."""
+    import shutil as _shutil
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    lib = build()
+    cxx = os.environ.get("CXX") or _shutil.which("g++") or _shutil.which("c++")
+    if not cxx:
+        raise RuntimeError("no C++ compiler found; set CXX")
+    try:
+        includes, libdirs = ce.include_paths("cuda"), ce.library_paths("cuda")
+    except TypeError:      # older signature
+        includes, libdirs = ce.include_paths(cuda=True), ce.library_paths(cuda=True)
+    includes = list(includes) + [sysconfig.get_paths()["include"]]
+    flags = ["-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-Wno-unused-variable", "-Wno-unused-function", "-DTORCH_API_INCLUDE_EXTENSION_H",
+             f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    for pname in ("COMPILER_TYPE", "STDLIB", "BUILD_ABI"):      # keeps pybind11's internals compatible with torch's own build
+        pval = getattr(torch._C, f"_PYBIND11_{pname}", None)
+        if pval is not None:
+            flags.append(f'-DPYBIND11_{pname}="{pval}"')
+    link = [f"-L{d}" for d in libdirs] + ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart",
+                                          f"-L{HERE}", "-lhtgs_b200", "-Wl,-rpath,$ORIGIN/.."] + [f"-Wl,-rpath,{d}" for d in libdirs]
+    targets = binding_paths()
+    jobs = []
+    for target, name, extra in ((targets[0], "_C", []), (targets[1], "_C_benchmarking", ["-DHTGS_BINDINGS_BENCHMARKING"])):
+        if force or _stale(target, [BINDINGS_SRC, lib, os.path.normpath(os.path.join(CSRC, "..", "..", "include", "htgs_b200.h"))]):
+            jobs.append((name, [cxx] + flags + extra + [f"-DTORCH_EXTENSION_NAME={name}"] + [f"-I{d}" for d in includes] + [BINDINGS_SRC, "-o", target] + link))
+    if jobs:
+        os.makedirs(PYBIND_DIR, exist_ok=True)
+        init = os.path.join(PYBIND_DIR, "__init__.py")
+        if not os.path.exists(init):
+            raise RuntimeError(f"{init} is missing")
+
+        def run(job):
+            name, cmd = job
+            res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            return name, res.returncode, res.stdout
+
+        with concurrent.futures.ThreadPoolExecutor(max_workers=2) as pool:
+            for name, rc, out in pool.map(run, jobs):
+                if rc != 0:
+                    sys.stdout.write(f"--- bindings {name} ---\n{out}\n")
+                    raise RuntimeError(f"compiling the torch extension module {name} failed")
+    return targets
+
+
 if __name__ == "__main__":
     print(build(force="-f" in sys.argv, verbose="-v" in sys.argv))
+    if "--no-bindings" not in sys.argv:
+        print(*build_bindings(force="-f" in sys.argv), sep="\n")

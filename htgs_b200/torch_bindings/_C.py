@@ -15,7 +15,22 @@ import torch
 from .. import _native
 from .._native import HtgsFrameInfo, HtgsScene, HtgsView
 
-last_frame_info = None  # HtgsFrameInfo of the most recent call (diagnostics)
+_last_frame_info = None     # HtgsFrameInfo of the most recent call through this (ctypes) binding
+_last_source = "ctypes"     # which binding made the most recent call (torch_bindings.rasterization sets "pybind")
+
+
+def __getattr__(name):
+    # `_C.last_frame_info`: statistics of the most recent frame, whichever binding rendered it (diagnostics)
+    if name == "last_frame_info":
+        mods = _native.pybind_modules()
+        return mods[0].frame_info() if (mods and _last_source == "pybind") else _last_frame_info
+    raise AttributeError(name)
+
+
+def _set_info(info):
+    global _last_frame_info, _last_source
+    _last_frame_info = info
+    _last_source = "ctypes"
 
 # Deferred checks (torch_bindings.rasterization.set_deferred_checks): `render` and `_C_benchmarking.benchmark` queue the frame
 # with htgs_render_async and return without waiting for the GPU; the frame's status is checked by the next call on the same
@@ -28,7 +43,6 @@ _queued: dict = {}
 def frame_results(device=None):
     """Waits for and checks every frame this host thread queued with deferred checks (on `device`, or on all devices);
     raises what the blocking call would have raised.  Returns the HtgsFrameInfo of each context that was checked."""
-    global last_frame_info
     index = None if device is None else _device_index(torch.device(device))
     infos = []
     for ctx in _native.contexts_of_thread(index):
@@ -39,7 +53,7 @@ def frame_results(device=None):
         _queued.pop(ctx, None)
         _native.check(rc)
         infos.append(info)
-        last_frame_info = info
+        _set_info(info)
     return infos
 
 
@@ -80,7 +94,6 @@ def _scene_view(tensors, M, VPM, cam_position, mode, K, active_sh_bases, width, 
 def render(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases,
            width, height, near_plane, far_plane, scale_modifier, to_chw, use_median_depth) -> Tuple[torch.Tensor, torch.Tensor]:
     """`_C.render` (rasterization/include/rasterization_api.h:57-77): returns (image, depth)."""
-    global last_frame_info
     n, device = _check_inputs(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_position)
     tensors = [t.contiguous() for t in (positions, scales, rotations, opacities, sh_0, sh_rest)]
     M, VPM, cam_position = M.contiguous(), VPM.contiguous(), cam_position.contiguous()
@@ -101,7 +114,7 @@ def render(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_p
                                        ctypes.byref(scene), ctypes.byref(view), image.data_ptr(), depth.data_ptr(), None, int(bool(to_chw)),
                                        int(bool(use_median_depth)), None, 0, stream, ctypes.byref(info))
     _native.check(rc)
-    last_frame_info = info
+    _set_info(info)
     return image, depth
 
 
@@ -114,7 +127,6 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
     """`_C.forward` (rasterization/include/rasterization_api.h:8-26): returns
     (image, per_primitive_buffers, per_tile_buffers, per_instance_buffers, per_pixel_buffers, n_instances, selector).
     The four byte tensors are opaque to the caller and only meaningful to `backward` of this module."""
-    global last_frame_info
     n, device = _check_inputs(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_position)
     tensors = [t.contiguous() for t in (positions, scales, rotations, opacities, sh_0, sh_rest)]
     M, VPM, cam_position = M.contiguous(), VPM.contiguous(), cam_position.contiguous()
@@ -146,7 +158,7 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
         info = HtgsFrameInfo()
         _native.check(lib.htgs_forward_finish(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), n_inst.value, image.data_ptr(), stream,
                                               ctypes.byref(info)))
-    last_frame_info = info
+    _set_info(info)
     return image, per_primitive, per_tile, per_instance, per_pixel, int(n_inst.value), 0
 
 
@@ -154,6 +166,39 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
 # written) here, per device; see torch_bindings.rasterization.track_training_visibility.
 track_visibility = False
 last_visibility: dict = {}
+
+
+# The extras of the compiled module `htgs_b200.pybind._C` under the same names, so that the surface can use either binding.
+def frame_info():
+    return _last_frame_info
+
+
+def set_deferred_checks(enable: bool) -> None:
+    global deferred_checks
+    if not enable:
+        frame_results()
+    deferred_checks = bool(enable)
+
+
+def set_max_weights_tail_credit(enable: bool) -> None:
+    global max_weights_tail_credit
+    max_weights_tail_credit = bool(enable)
+
+
+def set_track_visibility(enable: bool) -> None:
+    global track_visibility
+    track_visibility = bool(enable)
+    if not enable:
+        last_visibility.clear()
+
+
+def get_last_visibility(device_index: int):
+    return last_visibility.get(torch.device("cuda", int(device_index)))
+
+
+def benchmark(*args):
+    from . import _C_benchmarking
+    return _C_benchmarking.benchmark(*args)
 
 
 def forward_visibility(per_primitive_buffers, n_primitives: int):
@@ -234,7 +279,6 @@ max_weights_tail_credit = False
 def update_max_weights(max_weights, positions, scales, rotations, opacities, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases,
                        width, height, near_plane, far_plane, scale_modifier, weight_threshold):
     """`_C.update_max_weights` (rasterization/include/rasterization_api.h:79-97): raises `max_weights` [N,1] in place."""
-    global last_frame_info
     device = positions.device
     if device.type != "cuda":
         raise ValueError("htgs_b200 rasterizer: tensors must live on a CUDA device")
@@ -258,7 +302,7 @@ def update_max_weights(max_weights, positions, scales, rotations, opacities, M, 
         rc = _native.lib().htgs_update_max_weights(_native.context(_device_index(device)), ctypes.byref(scene), ctypes.byref(view), max_weights.data_ptr(),
                                                    float(weight_threshold), None, 0, torch.cuda.current_stream(device).cuda_stream, ctypes.byref(info))
     _native.check(rc)
-    last_frame_info = info
+    _set_info(info)
 
 
 def update_3d_filter_cuda(positions, w2c, filter_3d, visibility_mask, width, height, focal_x, focal_y, center_x, center_y, near_plane,

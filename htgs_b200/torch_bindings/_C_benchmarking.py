@@ -35,5 +35,5 @@ def benchmark(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, ca
         rc = _native.lib().htgs_render_fast(_native.context(_C._device_index(device)), ctypes.byref(scene), ctypes.byref(view), image.data_ptr(),
                                             int(bool(to_chw)), None, 0, stream, ctypes.byref(info))
     _native.check(rc)
-    _C.last_frame_info = info
+    _C._set_info(info)
     return image

@@ -12,7 +12,25 @@ from typing import Any, NamedTuple
 import torch
 from torch.autograd.function import once_differentiable
 
+from .. import _native
 from . import _C, _C_benchmarking
+
+# The binding behind this surface: the compiled torch extension module `htgs_b200.pybind._C` when it has been built (same
+# entry points as the reference's `_C`, plus this library's extras), else the ctypes binding `_C` of this package.  Both call
+# the same C-ABI library and share one set of library contexts.
+_mods = _native.pybind_modules()
+_impl = _mods[0] if _mods else _C
+_via_pybind = _mods is not None
+
+
+def binding() -> str:
+    """"pybind" or "ctypes": which binding serves this surface (environment variable HTGS_B200_BINDING)."""
+    return "pybind" if _via_pybind else "ctypes"
+
+
+def _mark():
+    if _via_pybind:
+        _C._last_source = "pybind"     # `_C.last_frame_info` then reports the extension module's frame
 
 
 class RasterizerMode(Enum):
@@ -43,9 +61,7 @@ class RasterizerSettings(NamedTuple):
 # Multi-GPU training exchanges only the gradient rows some rank can have touched (htgs_b200.parallel): when tracking is on,
 # every training forward leaves the visibility of its Gaussians, per device.  No counterpart in the reference.
 def track_training_visibility(enable: bool) -> None:
-    _C.track_visibility = bool(enable)
-    if not enable:
-        _C.last_visibility.clear()
+    _impl.set_track_visibility(bool(enable))
 
 
 def last_training_visibility(device, with_event: bool = False):
@@ -53,10 +69,11 @@ def last_training_visibility(device, with_event: bool = False):
     track_training_visibility(True)); with `with_event` also the CUDA event recorded once the tensor was written, which is
     early in the forward (after the preprocess pass), so that a side stream can use it while the forward still runs."""
     key = torch.device(device)
-    key = torch.device("cuda", torch.cuda.current_device()) if key.type == "cuda" and key.index is None else key
-    if key not in _C.last_visibility:
+    index = torch.cuda.current_device() if key.index is None else key.index
+    record = _impl.last_visibility(index) if _via_pybind else _C.get_last_visibility(index)
+    if record is None:
         raise RuntimeError("no training forward was tracked on this device: call track_training_visibility(True) first")
-    visible, ready = _C.last_visibility[key]
+    visible, ready = record
     return (visible, ready) if with_event else visible
 
 
@@ -68,13 +85,20 @@ def set_deferred_checks(enable: bool) -> None:
     frames in flight by alternating between two streams.  Render every kind of view once with the checks on (the default)
     first: a frame whose instance buffers turn out too small is rendered again when it is checked, i.e. after work queued
     behind it has already read its image (`HtgsFrameInfo.reruns` of `frame_results()` tells)."""
-    if not enable:
-        _C.frame_results()
-    _C.deferred_checks = bool(enable)
+    _impl.set_deferred_checks(bool(enable))
+
+
+def deferred_checks() -> bool:
+    return bool(_impl.deferred_checks()) if _via_pybind else bool(_C.deferred_checks)
 
 
 def frame_results(device=None):
-    """Waits for and checks the frames queued with deferred checks by this host thread; see `set_deferred_checks`."""
+    """Waits for and checks the frames queued with deferred checks by this host thread; see `set_deferred_checks`.
+    Returns one frame-statistics object per CUDA stream that had a frame queued."""
+    _mark()
+    if _via_pybind:
+        index = -1 if device is None else (torch.cuda.current_device() if torch.device(device).index is None else torch.device(device).index)
+        return _impl.frame_results(index)
     return _C.frame_results(device)
 
 
@@ -82,7 +106,8 @@ class _Rasterize(torch.autograd.Function):
     @staticmethod
     def forward(ctx: Any, positions, scales, rotations, opacities, sh_0, sh_rest, densification_info,
                 rasterizer_settings: RasterizerSettings, use_distance_scaling: bool) -> torch.Tensor:
-        image, per_primitive_buffers, per_tile_buffers, per_instance_buffers, per_pixel_buffers, n_instances, selector = _C.forward(
+        _mark()
+        image, per_primitive_buffers, per_tile_buffers, per_instance_buffers, per_pixel_buffers, n_instances, selector = _impl.forward(
             positions, scales, rotations, opacities, sh_0, sh_rest, *rasterizer_settings.as_tuple())
         ctx.rasterizer_settings = rasterizer_settings
         ctx.n_instances = n_instances
@@ -100,7 +125,7 @@ class _Rasterize(torch.autograd.Function):
     @staticmethod
     @once_differentiable
     def backward(ctx: Any, grad_image: torch.Tensor):
-        grads = _C.backward(ctx.densification_info, grad_image, *ctx.saved_tensors, *ctx.rasterizer_settings.as_tuple(),
+        grads = _impl.backward(ctx.densification_info, grad_image, *ctx.saved_tensors, *ctx.rasterizer_settings.as_tuple(),
                             ctx.n_instances, ctx.instance_primitive_indices_selector, ctx.use_distance_scaling)
         grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest = grads
         return (grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest, None, None, None)
@@ -113,14 +138,16 @@ def diff_rasterize(positions, scales, rotations, opacities, sh_0, sh_rest, densi
 
 def rasterize(positions, scales, rotations, opacities, sh_0, sh_rest, settings: RasterizerSettings, to_chw: bool,
               use_median_depth: bool) -> tuple[torch.Tensor, torch.Tensor]:
-    image, depth = _C.render(positions, scales, rotations, opacities, sh_0, sh_rest, *settings.as_tuple(), to_chw, use_median_depth)
+    _mark()
+    image, depth = _impl.render(positions, scales, rotations, opacities, sh_0, sh_rest, *settings.as_tuple(), to_chw, use_median_depth)
     depth = depth.unsqueeze(0) if to_chw else depth.unsqueeze(-1)
     return image, depth
 
 
 def fast_rasterize(positions, scales, rotations, opacities, sh_0, sh_rest, settings: RasterizerSettings, to_chw: bool) -> torch.Tensor:
     """The reference's relaxed-precision benchmark path (torch_bindings/rasterization.py:166-186): RGB only."""
-    return _C_benchmarking.benchmark(positions, scales, rotations, opacities, sh_0, sh_rest, *settings.as_tuple(), to_chw)
+    _mark()
+    return _impl.benchmark(positions, scales, rotations, opacities, sh_0, sh_rest, *settings.as_tuple(), to_chw)
 
 
 def set_max_weights_tail_credit(enable: bool) -> None:
@@ -129,8 +156,9 @@ def set_max_weights_tail_credit(enable: bool) -> None:
     built from it with nvcc 12.9 for sm_100a never does (a Gaussian that only lands in the tail keeps weight 0; the same
     source compiled without device-code optimisation does credit it).  The default (False) reproduces the extension's
     output bit for bit; True gives what the source describes.  No counterpart in the reference."""
-    _C.max_weights_tail_credit = bool(enable)
+    _impl.set_max_weights_tail_credit(bool(enable))
 
 
 def update_max_weights(max_weights, positions, scales, rotations, opacities, settings: RasterizerSettings, weight_threshold: float) -> None:
-    return _C.update_max_weights(max_weights, positions, scales, rotations, opacities, *settings.as_tuple(), weight_threshold)
+    _mark()
+    return _impl.update_max_weights(max_weights, positions, scales, rotations, opacities, *settings.as_tuple(), weight_threshold)

@@ -71,3 +71,17 @@ def test_training_visibility_needs_tracking():
     rasterization.track_training_visibility(False)
     with pytest.raises(RuntimeError):
         rasterization.last_training_visibility("cuda:0")
+
+
+def test_extension_modules_expose_the_reference_entry_points():
+    """The compiled torch extension modules import without a GPU and carry the names the reference's pybind modules bind
+    (torch_bindings/bindings.cpp:8-16, bindings_benchmarking.cpp:6-8)."""
+    from htgs_b200 import build
+    build.build_bindings()
+    from htgs_b200 import pybind
+    mod_c, mod_b = pybind.load()
+    for name in ("update_3d_filter_cuda", "forward", "backward", "render", "update_max_weights"):
+        assert callable(getattr(mod_c, name)), name
+    assert callable(mod_b.benchmark)
+    assert [n for n in dir(mod_b) if not n.startswith("_")] == ["benchmark"]
+    assert "arg18: bool) -> tuple[torch.Tensor, torch.Tensor]" in mod_c.render.__doc__      # 17 settings-order arguments + to_chw + use_median_depth
