@@ -92,9 +92,11 @@ def build_bindings(force: bool = False) -> tuple:
     import torch
     from torch.utils import cpp_extension as ce
     lib = build()
-    cxx = os.environ.get("CXX") or _shutil.which("g++") or _shutil.which("c++")
+    # The system compiler, not $CXX: this image exports CXX as a wrapper script around g++ meant for nvcc's -ccbin, and a
+    # module built through it crashed as soon as a C++ exception left libc10 (every failing TORCH_CHECK).  HTGS_B200_CXX overrides.
+    cxx = os.environ.get("HTGS_B200_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else None) or _shutil.which("g++") or _shutil.which("c++")
     if not cxx:
-        raise RuntimeError("no C++ compiler found; set CXX")
+        raise RuntimeError("no C++ compiler found; set HTGS_B200_CXX")
     try:
         includes, libdirs = ce.include_paths("cuda"), ce.library_paths("cuda")
     except TypeError:      # older signature
@@ -129,6 +131,15 @@ def build_bindings(force: bool = False) -> tuple:
                 if rc != 0:
                     sys.stdout.write(f"--- bindings {name} ---\n{out}\n")
                     raise RuntimeError(f"compiling the torch extension module {name} failed")
+        # self-test in a child process: a failing check inside the module must surface as a Python exception, with or without a GPU
+        probe = ("import torch\nfrom htgs_b200.pybind import _C\n"
+                 "try:\n    _C.context_handle(100000)\nexcept RuntimeError:\n    print('exceptions-ok')\n")
+        res = subprocess.run([sys.executable, "-c", probe], cwd=os.path.dirname(HERE), stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if "exceptions-ok" not in res.stdout:
+            for target in targets:
+                if os.path.exists(target):
+                    os.remove(target)
+            raise RuntimeError("the torch extension modules were built but do not survive a C++ exception (removed them again):\n" + res.stdout[-2000:])
     return targets
 
 

@@ -212,7 +212,7 @@ def test_config4_as_specified_is_refused_not_mis_rendered():
     big = [t.clone() for t in tensors]
     big[1] = big[1] * float(np.exp(5.0))      # log-scale mean -5.5 -> -0.5: every Gaussian that survives culling covers a large part of the 4K image
     view = scene.views[5]
-    with pytest.raises(_native.HtgsError) as err:
+    with pytest.raises(RuntimeError) as err:      # _native.HtgsError through the ctypes binding, torch's RuntimeError through the extension module
         harness.ours().rasterize(*big, harness.settings_for(harness.ours(), scene, view, 0, 32), True, False)
     assert "32 bits" in str(err.value)
     torch.cuda.synchronize()
