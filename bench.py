@@ -55,8 +55,10 @@ def parse_args():
     ap.add_argument("--k", type=int, default=16, choices=[1, 2, 4, 8, 16, 32], help="K of HYBRID_BLEND / FIRST_K (16 is the benchmark)")
     ap.add_argument("--workload", default="render", choices=["render", "render_fast", "train"],
                     help="render: configuration 1 (default, the headline metric); train: configuration 2 (fwd+bwd, L1 loss, one view per GPU, gradient all-reduce)")
-    ap.add_argument("--exchange", default="rows", choices=["rows", "dense"],
-                    help="train at N > 1: sum only the gradient rows of Gaussians some rank kept (default) or the dense tensors")
+    ap.add_argument("--exchange", default="overlap", choices=["overlap", "rows", "dense"],
+                    help="train at N > 1: overlap = the backward pass runs in ranges of Gaussians and each finished range's rows are summed while "
+                         "the next is computed (default); rows = the rows some rank kept, after the backward; dense = the dense tensors, after the backward")
+    ap.add_argument("--exchange-chunks", type=int, default=4, help="ranges of Gaussians the backward pass is split into for --exchange overlap")
     ap.add_argument("--reference-kind", default="auto", choices=["auto", "cuda", "cpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-views", type=int, default=12)
@@ -191,10 +193,15 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
 
     # Exchange: this library's arm sums only the gradient rows of Gaussians some rank's view kept (the others are zero on
     # every rank); the reference has no multi-GPU path and no such list, its arm all-reduces the dense tensors.
-    sparse = dist is not None and not is_reference and args.exchange == "rows"
+    sparse = dist is not None and not is_reference and args.exchange in ("rows", "overlap")
+    overlap = sparse and args.exchange == "overlap"
+    xchg = None
     if sparse:
         from htgs_b200.torch_bindings import rasterization
         rasterization.track_training_visibility(True)
+    if overlap:
+        xchg = parallel.BackwardExchange(n_chunks=args.exchange_chunks, measure=True)
+        rasterization.set_backward_hook(xchg)
     exchanged_rows = []
 
     def step(s):
@@ -205,10 +212,15 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
         image = mod.diff_rasterize(leaves[0], act_scales, act_rotations, act_opacities, leaves[4], leaves[5], empty, settings(cams_dev[vi]), False)
         if sparse:     # the union of the ranks' visible sets is formed on a side stream while the forward still blends
             visible, ready = rasterization.last_training_visibility(device, with_event=True)
-            exchange = parallel.begin_row_exchange(visible, ready=ready)
+            if overlap:
+                xchg.begin(visible, ready, mode=scene.mode)
+            else:
+                exchange = parallel.begin_row_exchange(visible, ready=ready)
         loss = (image - target).abs().mean()
-        loss.backward()
-        if sparse:
+        loss.backward()      # with --exchange overlap the rasterizer's backward sums its gradients over the ranks range by range
+        if overlap:
+            exchanged_rows.append(xchg.rows_exchanged)
+        elif sparse:
             exchanged_rows.append(parallel.finish_row_exchange([l.grad for l in leaves], exchange))
         elif dist is not None:
             parallel.allreduce_gradients([l.grad for l in leaves])
@@ -235,6 +247,11 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
         dist.barrier()
     clocks = sampler.stop(t0, t1)
     ms = parallel.max_over_ranks(e0.elapsed_time(e1), device)
+    exposed = None
+    if overlap:
+        rasterization.set_backward_hook(None)
+        waits = xchg.exposed_ms(last=steps)
+        exposed = parallel.max_over_ranks(float(np.mean(waits)) if waits else 0.0, device)
     if sparse:
         rasterization.track_training_visibility(False)
     n = scene.n
@@ -244,7 +261,10 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name.replace("config1", "config2 (fwd+bwd, L1, one view per GPU)"), "views_per_step": world,
                        "allreduce_bytes_per_rank": grad_bytes if world > 1 else 0,
-                       "gradient_exchange": ("none" if world == 1 else "rows of the union of the ranks' visible Gaussians" if sparse else "dense tensors"),
+                       "gradient_exchange": ("none" if world == 1 else
+                                             f"rows of the union of the ranks' visible Gaussians, summed range by range ({args.exchange_chunks} ranges) while the backward pass runs" if overlap else
+                                             "rows of the union of the ranks' visible Gaussians" if sparse else "dense tensors"),
+                       "exchange_exposed_ms": exposed,
                        "views_per_s": world * steps / (ms / 1000.0), "views_of_a_step": "spread evenly over the orbit", "parallelism": f"view-partitioned x{world} + gradient all-reduce"},
             "clocks": clocks, "final_loss": float(loss.item())}
     if is_reference:
@@ -258,7 +278,8 @@ def train_leg_summary(line):
     """The training line folded into the `train` object of the default workload's JSON line."""
     cfg = line["config"]
     return {"metric": "train-steps/s", "steps_per_s": line["value"], "ms_per_step": line["ms_per_step"], "views_per_s": cfg["views_per_s"],
-            "exchange": {"none": "none", "dense tensors": "dense"}.get(cfg["gradient_exchange"], "rows"),
+            "exchange": {"none": "none", "dense tensors": "dense"}.get(cfg["gradient_exchange"], "rows, overlapped with the backward" if "range by range" in cfg["gradient_exchange"] else "rows"),
+            "exchange_exposed_ms": cfg.get("exchange_exposed_ms"),
             "allreduce_bytes_per_rank": cfg["allreduce_bytes_per_rank"], "n_gpus": line["n_gpus"], "steps": line["steps"], "warmup": line["warmup"],
             "workload": cfg["workload"], "clocks": line["clocks"], "final_loss": line["final_loss"]}
 

@@ -134,13 +134,16 @@ cudaError_t launch_visibility(const uint32_t* n_touched, uint8_t* visible, uint3
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
                             const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
                             const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, cudaEvent_t outputs_cleared, int sm_count,
-                            cudaStream_t stream);   // `outputs_cleared`: event after which the six tensors are zero, or null to clear them here
-cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs& out, cudaStream_t stream);
+                            uint32_t first, uint32_t count, cudaStream_t stream);
+// `outputs_cleared`: event after which rows [first, first + count) of the six tensors are zero, or null to clear them here.
+// [first, first + count): the Gaussians whose gradients the call computes (everything else is left untouched); a proper part
+// of the scene is refused (cudaErrorNotSupported) for GLOBAL_ORDERING.
+cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs& out, uint32_t first, uint32_t count, cudaStream_t stream);
 
 
 // api.cu: internals shared with the other translation units (C++ linkage: not part of the C-ABI).
 int backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
-                        const float* grad_image, const float* image, const HtgsGradients* grads, void* accum, void* stream);
+                        const float* grad_image, const float* image, const HtgsGradients* grads, void* accum, uint32_t first, uint32_t count, void* stream);
 int context_device(const HtgsContext* ctx);
 void set_last_error(const char* message);   // message htgs_last_error() returns on the calling thread
 

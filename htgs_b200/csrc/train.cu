@@ -116,7 +116,7 @@ template <int MODE, int K, bool ABS_GRAD>
 __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ prims_sorted, const EvalRecord* __restrict__ eval,
     const CullRecord* __restrict__ cull, TrainPixelBuffers tin, const float* __restrict__ grad_image, const float* __restrict__ VPM,
-    float4* __restrict__ accum, uint32_t width, uint32_t height, uint32_t grid_w)
+    float4* __restrict__ accum, uint32_t width, uint32_t height, uint32_t grid_w, uint32_t g_first, uint32_t g_end)
 {
     using MT = ModeTraits<MODE>;
     using SM = BwdSmem<MODE, K>;
@@ -131,7 +131,18 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
 
     const uint32_t tid = threadIdx.x;
     const uint32_t tile_x = blockIdx.x, tile_y = blockIdx.y;
-    const uint2 range = tile_ranges[tile_y * grid_w + tile_x];
+    const uint2 tile_range = tile_ranges[tile_y * grid_w + tile_x];
+    uint2 range = tile_range;
+    // A pass over the Gaussians [g_first, g_end) only: a tile's list is ascending in Gaussian index for these modes (instances
+    // are emitted in index order and the tile sort is stable), so the pass walks one contiguous piece of it.
+    if (g_first != 0u || g_end != 0xffffffffu) {
+        auto lower_bound = [&](uint32_t lo, uint32_t hi, uint32_t g) {
+            while (lo < hi) { const uint32_t mid = (lo + hi) >> 1; if (__ldg(prims_sorted + mid) < g) lo = mid + 1; else hi = mid; }
+            return lo;
+        };
+        range.x = lower_bound(tile_range.x, tile_range.y, g_first);
+        range.y = lower_bound(range.x, tile_range.y, g_end);
+    }
     if (range.x >= range.y) return;
     const uint32_t n_pixels = width * height;
     const uint32_t PP = tin.padded_pixels;
@@ -271,7 +282,7 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
         if constexpr (kFirstK) {
             s_mask[tid] = 0;
             __syncthreads();
-            scatter_core_entries(batch_begin - range.x);
+            scatter_core_entries(batch_begin - __ldg(&tile_ranges[blockIdx.y * grid_w + blockIdx.x].x));   // the forward's stored core positions count from the start of the tile's list
             __syncthreads();
             my_mask = s_mask[tid];
         } else if (valid) {
@@ -305,7 +316,7 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
         }
         s_off[tid] = excl;
         if (tid == 0) s_off[NT] = total_pairs;
-        if constexpr (SM::has_core && !kFirstK) scatter_core_entries(batch_begin - range.x);
+        if constexpr (SM::has_core && !kFirstK) scatter_core_entries(batch_begin - __ldg(&tile_ranges[blockIdx.y * grid_w + blockIdx.x].x));   // the forward's stored core positions count from the start of the tile's list
         __syncthreads();
         if (total_pairs == 0) continue;
         // my share of the pairs
@@ -589,10 +600,10 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
     const float* __restrict__ positions, const float* __restrict__ scales, const float* __restrict__ rotations, const float* __restrict__ sh_rest,
     const float* __restrict__ M, const float* __restrict__ VPM, const float* __restrict__ cam_position_ptr,
     const uint32_t* __restrict__ n_touched, const uint8_t* __restrict__ clamp, const float4* __restrict__ accum, BackwardOutputs out,
-    uint32_t n_primitives, int active_sh_bases, int total_sh_bases)
+    uint32_t n_primitives, int active_sh_bases, int total_sh_bases, uint32_t g_first, uint32_t g_end)
 {
-    const uint32_t idx = blockIdx.x * 256 + threadIdx.x;
-    if (idx >= n_primitives) return;
+    const uint32_t idx = g_first + blockIdx.x * 256 + threadIdx.x;
+    if (idx >= g_end) return;
     float3* grad_sh_rest = reinterpret_cast<float3*>(out.grad_sh_rest) + size_t(idx) * total_sh_bases;
     if (n_touched[idx] == 0) return;          // outputs were cleared by the launcher
     const float4 dT1 = accum[size_t(idx) * 5], dT2 = accum[size_t(idx) * 5 + 1], dT4 = accum[size_t(idx) * 5 + 2], dC = accum[size_t(idx) * 5 + 3];
@@ -698,7 +709,8 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
 
 template <int MODE, int K>
 cudaError_t launch_tile_backward(bool abs_grad, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted, const uint2* tile_ranges,
-                                 const TrainPixelBuffers& tin, const float* grad_image, const float* VPM, float4* accum, cudaStream_t stream) {
+                                 const TrainPixelBuffers& tin, const float* grad_image, const float* VPM, float4* accum, uint32_t g_first, uint32_t g_end,
+                                 cudaStream_t stream) {
     using SM = BwdSmem<MODE, K>;
     const dim3 grid(geo.grid_w, geo.grid_h, 1);
     auto launch = [&](auto kernel) -> cudaError_t {
@@ -709,7 +721,7 @@ cudaError_t launch_tile_backward(bool abs_grad, const FrameGeometry& geo, const 
             if (err != cudaSuccess) return err;
         }
         kernel<<<grid, kBwdThreads, SM::total, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, tin, grad_image, VPM, accum,
-                                                uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w));
+                                                uint32_t(geo.width), uint32_t(geo.height), uint32_t(geo.grid_w), g_first, g_end);
         return cudaGetLastError();
     };
     return abs_grad ? launch(backward_tile_kernel<MODE, K, true>) : launch(backward_tile_kernel<MODE, K, false>);
@@ -718,14 +730,14 @@ cudaError_t launch_tile_backward(bool abs_grad, const FrameGeometry& geo, const 
 template <int MODE>
 cudaError_t launch_tile_backward_k(int K, bool abs_grad, const FrameGeometry& geo, const PrimBuffers& prim, const uint32_t* prims_sorted,
                                    const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image, const float* VPM, float4* accum,
-                                   cudaStream_t stream) {
+                                   uint32_t g_first, uint32_t g_end, cudaStream_t stream) {
     switch (K) {
-        case 32: return launch_tile_backward<MODE, 32>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
-        case 16: return launch_tile_backward<MODE, 16>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
-        case 8: return launch_tile_backward<MODE, 8>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
-        case 4: return launch_tile_backward<MODE, 4>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
-        case 2: return launch_tile_backward<MODE, 2>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
-        default: return launch_tile_backward<MODE, 1>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, stream);
+        case 32: return launch_tile_backward<MODE, 32>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, g_first, g_end, stream);
+        case 16: return launch_tile_backward<MODE, 16>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, g_first, g_end, stream);
+        case 8: return launch_tile_backward<MODE, 8>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, g_first, g_end, stream);
+        case 4: return launch_tile_backward<MODE, 4>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, g_first, g_end, stream);
+        case 2: return launch_tile_backward<MODE, 2>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, g_first, g_end, stream);
+        default: return launch_tile_backward<MODE, 1>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, VPM, accum, g_first, g_end, stream);
     }
 }
 
@@ -744,38 +756,42 @@ cudaError_t launch_visibility(const uint32_t* n_touched, uint8_t* visible, uint3
     return cudaGetLastError();
 }
 
-cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs& out, cudaStream_t stream) {
-    const size_t n = size_t(scene.n_primitives), B = size_t(scene.total_sh_bases);
+cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs& out, uint32_t first, uint32_t count, cudaStream_t stream) {
+    const size_t n = size_t(count), at = size_t(first), B = size_t(scene.total_sh_bases);
     if (n == 0) return cudaSuccess;
     cudaError_t err;
-    if ((err = cudaMemsetAsync(out.grad_positions, 0, n * 3 * 4, stream)) != cudaSuccess) return err;
-    if ((err = cudaMemsetAsync(out.grad_scales, 0, n * 3 * 4, stream)) != cudaSuccess) return err;
-    if ((err = cudaMemsetAsync(out.grad_rotations, 0, n * 4 * 4, stream)) != cudaSuccess) return err;
-    if ((err = cudaMemsetAsync(out.grad_opacities, 0, n * 4, stream)) != cudaSuccess) return err;
-    if ((err = cudaMemsetAsync(out.grad_sh_0, 0, n * 3 * 4, stream)) != cudaSuccess) return err;
-    if (B && (err = cudaMemsetAsync(out.grad_sh_rest, 0, n * B * 3 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_positions + at * 3, 0, n * 3 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_scales + at * 3, 0, n * 3 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_rotations + at * 4, 0, n * 4 * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_opacities + at, 0, n * 4, stream)) != cudaSuccess) return err;
+    if ((err = cudaMemsetAsync(out.grad_sh_0 + at * 3, 0, n * 3 * 4, stream)) != cudaSuccess) return err;
+    if (B && (err = cudaMemsetAsync(out.grad_sh_rest + at * B * 3, 0, n * B * 3 * 4, stream)) != cudaSuccess) return err;
     return cudaSuccess;
 }
 
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
                             const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
                             const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, cudaEvent_t outputs_cleared, int sm_count,
-                            cudaStream_t stream) {
+                            uint32_t first, uint32_t count, cudaStream_t stream) {
     (void)sm_count;
     const uint32_t n = uint32_t(scene.n_primitives);
-    if (n == 0) return cudaSuccess;
-    cudaError_t err = cudaMemsetAsync(acc.accum, 0, size_t(n) * 5 * sizeof(float4), stream);
+    if (n == 0 || count == 0) return cudaSuccess;
+    const bool whole = first == 0 && count == n;
+    // the pixel-parallel GLOBAL_ORDERING pass needs every fragment in front of a fragment: it cannot run over a part of the Gaussians
+    if (!whole && mode == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) return cudaErrorNotSupported;
+    const uint32_t g_first = whole ? 0u : first, g_end = whole ? 0xffffffffu : first + count;
+    cudaError_t err = cudaMemsetAsync(acc.accum + size_t(first) * 5, 0, size_t(count) * 5 * sizeof(float4), stream);
     if (err != cudaSuccess) return err;
-    if (outputs_cleared == nullptr && (err = clear_backward_outputs(scene, out, stream)) != cudaSuccess) return err;
+    if (outputs_cleared == nullptr && (err = clear_backward_outputs(scene, out, first, count, stream)) != cudaSuccess) return err;
     const bool abs_grad = out.densification_info != nullptr && out.densification_rows == 3;
     const int k = effective_k(mode, K);
     switch (mode) {
         case HTGS_MODE_HYBRID_BLEND:
-            err = launch_tile_backward_k<HTGS_MODE_HYBRID_BLEND>(k, abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, stream); break;
+            err = launch_tile_backward_k<HTGS_MODE_HYBRID_BLEND>(k, abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, g_first, g_end, stream); break;
         case HTGS_MODE_ALPHA_BLEND_FIRST_K:
-            err = launch_tile_backward_k<HTGS_MODE_ALPHA_BLEND_FIRST_K>(k, abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, stream); break;
+            err = launch_tile_backward_k<HTGS_MODE_ALPHA_BLEND_FIRST_K>(k, abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, g_first, g_end, stream); break;
         case HTGS_MODE_OIT_BLEND:
-            err = launch_tile_backward<HTGS_MODE_OIT_BLEND, 1>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, stream); break;
+            err = launch_tile_backward<HTGS_MODE_OIT_BLEND, 1>(abs_grad, geo, prim, prims_sorted, tile_ranges, tin, grad_image, view.VPM, acc.accum, g_first, g_end, stream); break;
         case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: {
             const dim3 grid((geo.width + 7) / 8, (geo.height + 7) / 8, 1);
             backward_global_kernel<<<grid, 64, 0, stream>>>(tile_ranges, prims_sorted, prim.eval, prim.cull, grad_image, image, view.VPM, acc.accum,
@@ -787,9 +803,9 @@ cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsV
     }
     if (err != cudaSuccess) return err;
     if (outputs_cleared != nullptr && (err = cudaStreamWaitEvent(stream, outputs_cleared, 0)) != cudaSuccess) return err;
-    preprocess_backward_kernel<<<(n + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
-                                                                    view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
-                                                                    view.active_sh_bases, scene.total_sh_bases);
+    preprocess_backward_kernel<<<(count + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
+                                                                        view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
+                                                                        view.active_sh_bases, scene.total_sh_bases, first, first + count);
     return cudaGetLastError();
 }
 

@@ -149,6 +149,147 @@ def finish_row_exchange(grads: Sequence, exchange: "RowExchange", group=None) ->
     return exchange.count
 
 
+def _sum_rows(tensors, index, lo: int, hi: int, stream, group) -> None:
+    """Sums rows index[lo:hi] of the tensors over the ranks (gather -> one all-reduce -> scatter), queued on `stream`."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    if hi <= lo:
+        return
+    if tensors[0].is_cuda:
+        from . import _native
+        table = _native.HtgsRowTensors()
+        table.n_tensors = len(tensors)
+        width = 0
+        for k, g in enumerate(tensors):
+            table.data[k] = g.data_ptr()
+            table.width[k] = g[0].numel()
+            width += g[0].numel()
+        packed = torch.empty((hi - lo, width), dtype=torch.float32, device=tensors[0].device)
+        lib = _native.lib()
+        first = index.data_ptr() + 8 * lo
+        _native.check(lib.htgs_gather_rows(ctypes.byref(table), first, hi - lo, packed.data_ptr(), stream.cuda_stream))
+        dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+        _native.check(lib.htgs_scatter_rows(ctypes.byref(table), first, hi - lo, packed.data_ptr(), stream.cuda_stream))
+        return
+    n = tensors[0].shape[0]
+    rows = index[lo:hi]
+    for g in tensors:          # host tensors (the gloo tests of this logic)
+        flat = g.view(n, -1)
+        packed = flat.index_select(0, rows)
+        dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+        flat.index_copy_(0, rows, packed)
+
+
+class BackwardExchange:
+    """Sums the rasterizer's six gradient tensors over the ranks WHILE the backward pass still runs.
+
+    The six tensors become final in the last kernel of the backward pass, so an exchange that starts after `loss.backward()`
+    has nothing to hide behind.  Here the pass runs over `n_chunks` ranges of Gaussian indices, one after the other
+    (`htgs_backward_range`: a tile's list is ascending in Gaussian index, so a range costs its share of the pass), and as
+    soon as a range has been queued its rows are summed on a second stream: gather of the rows some rank's view kept ->
+    one NCCL all-reduce -> scatter, all while the next range is computed.  Only the last range's exchange is exposed.
+    Every rank uses the same ranges (they depend on the scene size alone), so the collectives match.
+
+    Use per training step:
+        xchg.begin(visible, ready)     # right after the forward: union of the ranks' visible sets (overlaps the blend)
+        loss.backward()                # with rasterization.set_backward_hook(xchg) installed
+    after which the gradients autograd received from `diff_rasterize` are sums over the ranks.  What the rasterizer's
+    gradients are chained through on the way to the leaves (the activation functions of the parameters) is the same linear
+    map on every rank, so summing before it equals summing after it; loss terms that reach the parameters by other paths
+    (regularisers, weight decay) are NOT summed by this and stay the caller's to handle.
+    ALPHA_BLEND_GLOBAL_ORDERING cannot run over a part of the Gaussians: it gets one range (no overlap)."""
+
+    def __init__(self, n_chunks: int = 4, group=None, measure: bool = False):
+        self.n_chunks = max(1, int(n_chunks))
+        self.group = group
+        self.measure = measure          # record CUDA events around the wait for the last range's exchange (exposed_ms)
+        self._marks = []
+        self.exchange = None
+        self.bounds = None
+        self.dense = False
+        self.rows_exchanged = 0
+        self._chunk_ranges = None
+        self._comm = None
+
+    def chunk_ranges(self, n: int, mode: int = 0):
+        chunks = 1 if mode == 2 else self.n_chunks
+        edges = [(n * k) // chunks for k in range(chunks + 1)]
+        return [(edges[k], edges[k + 1] - edges[k]) for k in range(chunks)]
+
+    ranges = chunk_ranges       # the name the autograd hook calls
+
+    def begin(self, rows, ready=None, mode: int = 0) -> None:
+        """`rows`: bool tensor [N] of the Gaussians this rank's view kept (`last_training_visibility`); `ready`: the event
+        after which it is valid.  Forms the union over the ranks and finds where each range of Gaussians starts in its
+        (ascending) index list.  One host synchronisation, on the side stream."""
+        import torch
+        n = rows.shape[0]
+        self.exchange = begin_row_exchange(rows, self.group, ready)
+        self._chunk_ranges = self.chunk_ranges(n, mode)
+        index = self.exchange.index
+        self.dense = self.exchange.count > kDenseAbove * n
+        edges = [first for first, _ in self._chunk_ranges] + [n]
+        if self.dense or self.exchange.count == 0:
+            self.bounds = None
+        elif index.is_cuda:
+            with torch.cuda.stream(self.exchange.side_stream):
+                self.bounds = torch.searchsorted(index, torch.tensor(edges, dtype=index.dtype, device=index.device)).tolist()
+        else:
+            self.bounds = torch.searchsorted(index, torch.tensor(edges, dtype=index.dtype)).tolist()
+        self.rows_exchanged = n if self.dense else self.exchange.count
+
+    def after_range(self, k: int, first: int, count: int, grads) -> None:
+        import torch
+        import torch.distributed as dist
+        tensors = [g for g in grads if g is not None and g.numel() > 0]
+        if not tensors or count == 0 or self.exchange is None:
+            return
+        cuda = tensors[0].is_cuda
+        if cuda:
+            device = tensors[0].device
+            comm = self.exchange.side_stream
+            if comm is None:
+                comm = _side_streams.get(device) or _side_streams.setdefault(device, torch.cuda.Stream(device=device))
+            self._comm = comm
+            done = torch.cuda.Event()
+            done.record(torch.cuda.current_stream(device))
+            comm.wait_event(done)
+            context = torch.cuda.stream(comm)
+        else:
+            import contextlib
+            comm, context = None, contextlib.nullcontext()
+        with context:
+            if self.dense:
+                for g in tensors:
+                    dist.all_reduce(g[first:first + count], op=dist.ReduceOp.SUM, group=self.group)
+            elif self.bounds is not None:
+                _sum_rows(tensors, self.exchange.index, self.bounds[k], self.bounds[k + 1], comm, self.group)
+
+    def finish(self, grads) -> None:
+        import torch
+        if self._comm is not None:
+            current = torch.cuda.current_stream(self._comm.device)
+            if self.measure:
+                before, after = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                before.record(current)
+            current.wait_stream(self._comm)
+            if self.measure:
+                after.record(current)
+                self._marks.append((before, after))
+            for g in grads:
+                if g is not None and g.is_cuda:
+                    g.record_stream(self._comm)
+            self.exchange.index.record_stream(self._comm)
+
+
+    def exposed_ms(self, last: int = 0):
+        """With `measure`: per step, the time the compute stream waited for the exchange after its own last kernel of the
+        backward pass (call after a device synchronisation).  `last` > 0 keeps the most recent steps only."""
+        marks = self._marks[-last:] if last else self._marks
+        return [a.elapsed_time(b) for a, b in marks]
+
+
 def allreduce_gradients_rows(grads: Sequence, rows, group=None) -> int:
     """Sums per-Gaussian gradient tensors over the ranks, in place, exchanging only the rows some rank can have touched:
     `begin_row_exchange` and `finish_row_exchange` in one call (the host then waits for the backward pass before it can

@@ -102,6 +102,18 @@ def frame_results(device=None):
     return _C.frame_results(device)
 
 
+# Multi-GPU training (htgs_b200.parallel.BackwardExchange): when set, the backward pass of `diff_rasterize` runs in ranges of
+# Gaussians and hands every finished range to the hook, which sums it over the ranks while the next range is computed; the
+# gradients autograd receives are then already the sums.  No counterpart in the reference (it is single-GPU).
+_backward_hook = None
+
+
+def set_backward_hook(hook) -> None:
+    """`hook` needs ranges(n_primitives, mode) -> [(first, count), ...], after_range(k, first, count, grads) and finish(grads)."""
+    global _backward_hook
+    _backward_hook = hook
+
+
 class _Rasterize(torch.autograd.Function):
     @staticmethod
     def forward(ctx: Any, positions, scales, rotations, opacities, sh_0, sh_rest, densification_info,
@@ -125,8 +137,16 @@ class _Rasterize(torch.autograd.Function):
     @staticmethod
     @once_differentiable
     def backward(ctx: Any, grad_image: torch.Tensor):
-        grads = _impl.backward(ctx.densification_info, grad_image, *ctx.saved_tensors, *ctx.rasterizer_settings.as_tuple(),
-                            ctx.n_instances, ctx.instance_primitive_indices_selector, ctx.use_distance_scaling)
+        hook = _backward_hook
+        if hook is None:
+            grads = _impl.backward(ctx.densification_info, grad_image, *ctx.saved_tensors, *ctx.rasterizer_settings.as_tuple(),
+                                   ctx.n_instances, ctx.instance_primitive_indices_selector, ctx.use_distance_scaling)
+        else:      # range by range over the C-ABI (the ctypes binding drives the loop; both bindings share the library contexts)
+            n = ctx.saved_tensors[1].shape[0]
+            grads = _C.backward(ctx.densification_info, grad_image, *ctx.saved_tensors, *ctx.rasterizer_settings.as_tuple(),
+                                ctx.n_instances, ctx.instance_primitive_indices_selector, ctx.use_distance_scaling,
+                                ranges=hook.ranges(n, ctx.rasterizer_settings.mode.value), after_range=hook.after_range)
+            hook.finish(grads)
         grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest = grads
         return (grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest, None, None, None)
 

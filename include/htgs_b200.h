@@ -207,6 +207,17 @@ size_t htgs_backward_scratch_bytes(const HtgsScene* scene);
 int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                   const float* grad_image, const float* image, const HtgsGradients* grads, void* stream);
 
+/* The backward pass over the Gaussians [first_gaussian, first_gaussian + n_gaussians) only: rows of the six gradient tensors
+ * (and of densification_info) inside the range are computed exactly as htgs_backward computes them, everything outside is
+ * left untouched.  No counterpart in the reference.  A multi-GPU trainer calls it for one range after the other and starts
+ * summing a finished range over the ranks while the next one is computed (a tile's list is ascending in Gaussian index, so a
+ * range costs its share of the pass).  ALPHA_BLEND_GLOBAL_ORDERING, whose pass needs every fragment in front of a fragment,
+ * accepts the whole scene only (HTGS_ERR_UNSUPPORTED_MODE otherwise).  `grads->scratch` as for htgs_backward; the call
+ * clears the scratch rows of its range.  Stream-ordered, no host synchronisation. */
+int htgs_backward_range(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                        const float* grad_image, const float* image, const HtgsGradients* grads, uint32_t first_gaussian, uint32_t n_gaussians,
+                        void* stream);
+
 /* Which Gaussians the training forward kept: visible[i] = 1 when Gaussian i passed culling and touches a tile (these are
  * the only rows of the six gradient tensors the backward pass can make non-zero), else 0.  Reads the per-Gaussian blob
  * htgs_forward_begin filled.  No counterpart in the reference; multi-GPU training uses it to exchange only the rows some

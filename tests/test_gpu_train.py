@@ -189,3 +189,60 @@ def test_row_gather_and_scatter_kernels_match_index_select():
     assert _native.lib().htgs_gather_rows(ctypes.byref(table), None, 0, None, stream) == 0
     table.n_tensors = 9
     assert _native.lib().htgs_gather_rows(ctypes.byref(table), index.data_ptr(), count, packed.data_ptr(), stream) != 0
+
+
+@pytest.mark.parametrize("mode,K", [(0, 16), (1, 8), (3, 1)])
+def test_backward_in_ranges_of_gaussians_equals_the_whole_pass(mode, K):
+    """`htgs_backward_range`: the pass split into ranges of Gaussian indices gives the gradients of the whole pass (sums
+    of float atomics, so equal to rounding), the callback sees every range once in order, and rows of a range are final
+    when its callback runs (checked by snapshotting them there)."""
+    import torch
+    from htgs_b200.torch_bindings import _C
+    scene = scenes.outdoor_scene(n=150_000, n_views=2, seed=37, width=640, height=360, focal=500.0)
+    view = scene.views[0]
+    tensors = harness.scene_tensors(scene)
+    st = harness.settings_for(harness.ours(), scene, view, mode, K)
+    fwd = _C.forward(*tensors, *st.as_tuple())
+    image, blobs, n_inst, sel = fwd[0], fwd[1:5], fwd[5], fwd[6]
+    grad_image = torch.from_numpy(target_image(view.height, view.width, 77)).cuda() - 0.5
+    empty = torch.empty(0, device="cuda")
+    args = (empty, grad_image, empty, tensors[0], tensors[1], tensors[2], tensors[3] if mode == 1 else empty, tensors[5], *blobs, *st.as_tuple(), n_inst, sel, False)
+    whole = _C.backward(*args)
+    n = scene.n
+    edges = [0, n // 7, n // 2, n // 2, n - 5, n]          # uneven ranges, one of them empty
+    ranges = [(a, b - a) for a, b in zip(edges[:-1], edges[1:])]
+    seen, snapshots = [], []
+
+    def after_range(k, first, count, grads):
+        seen.append((k, first, count))
+        snapshots.append([g[first:first + count].clone() for g in grads])
+
+    split = _C.backward(*args, ranges=ranges, after_range=after_range)
+    torch.cuda.synchronize()
+    assert seen == [(k, a, c) for k, (a, c) in enumerate(ranges)]
+    for a, b in zip(split, whole):
+        scale = max(b.abs().max().item(), 1e-30)
+        assert (a - b).abs().max().item() <= 1e-5 * scale
+    for (first, count), snap in zip(ranges, snapshots):
+        for g, s in zip(split, snap):
+            assert torch.equal(g[first:first + count], s), "rows of a finished range must not change afterwards"
+    with pytest.raises(ValueError):
+        _C.backward(*args, ranges=[(0, n // 2)])
+
+
+def test_global_ordering_refuses_a_partial_backward():
+    import torch
+    from htgs_b200.torch_bindings import _C
+    scene = scenes.tiny_scene(n=3000, size=96, seed=29, sh_degree=1)
+    view = scene.views[0]
+    tensors = harness.scene_tensors(scene)
+    st = harness.settings_for(harness.ours(), scene, view, 2, 1)
+    fwd = _C.forward(*tensors, *st.as_tuple())
+    empty = torch.empty(0, device="cuda")
+    args = (empty, torch.ones_like(fwd[0]), fwd[0], tensors[0], tensors[1], tensors[2], empty, tensors[5], *fwd[1:5], *st.as_tuple(), fwd[5], fwd[6], False)
+    whole = _C.backward(*args)
+    same = _C.backward(*args, ranges=[(0, scene.n)])
+    for a, b in zip(same, whole):
+        assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-30)
+    with pytest.raises(RuntimeError):
+        _C.backward(*args, ranges=[(0, 1000), (1000, scene.n - 1000)])

@@ -71,6 +71,55 @@ def _rows_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
+def _chunked_worker(rank, world, port, out):
+    """BackwardExchange on host tensors: a stand-in backward pass fills the gradient rows range by range and calls
+    `after_range` as the rasterizer's binding does; the result must equal the dense sum, for a sparse and a dense union."""
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist = parallel.init_process_group("gloo")
+    n = 1003                                            # not a multiple of the chunk count
+    gen = torch.Generator().manual_seed(5)
+    ok = True
+    for share in (0.2, 0.9):
+        keep = [torch.rand(n, generator=gen) < share for _ in range(world)]
+        data = [[torch.randn((n, 3), generator=gen), torch.randn((n, 4), generator=gen), torch.randn((n, 15, 3), generator=gen)] for _ in range(world)]
+        for r in range(world):
+            for t in data[r]:
+                t[~keep[r]] = 0.0
+        expected = [sum(data[r][k] for r in range(world)) for k in range(3)]
+        xchg = parallel.BackwardExchange(n_chunks=4)
+        xchg.begin(keep[rank])
+        grads = [torch.zeros_like(t) for t in data[rank]]
+        ranges = xchg.ranges(n, 0)
+        ok = ok and len(ranges) == 4 and sum(c for _, c in ranges) == n and ranges[0][0] == 0
+        for k, (first, count) in enumerate(ranges):
+            for g, t in zip(grads, data[rank]):
+                g[first:first + count] = t[first:first + count]         # what htgs_backward_range leaves: rows of the range are final
+            xchg.after_range(k, first, count, grads)
+        xchg.finish(grads)
+        ok = ok and all(torch.allclose(a, b, atol=1e-6) for a, b in zip(grads, expected))
+        ok = ok and xchg.dense == (share > 0.6) and xchg.rows_exchanged == (n if share > 0.6 else int(torch.stack(keep).any(0).sum()))
+    one = parallel.BackwardExchange(n_chunks=4).ranges(n, 2)          # GLOBAL_ORDERING: the pass cannot be split
+    ok = ok and one == [(0, n)]
+    out.put((rank, ok, 0))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_chunked_backward_exchange_equals_dense_sum_two_gloo_ranks():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_chunked_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok, _ in results:
+        assert ok
+
+
 def test_row_exchange_equals_dense_sum_two_gloo_ranks():
     """Summing only the rows of the union of the ranks' kept Gaussians gives exactly the dense all-reduce's result."""
     ctx = mp.get_context("spawn")
