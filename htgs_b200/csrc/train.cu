@@ -241,7 +241,9 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
     // The training forward saved, per pixel and core entry, the POSITION of the entry's Gaussian in the tile's list, so the
     // entries that belong to a batch are those within NT of its start, and position - start is the staged slot.
     // FIRST_K gives gradient to stored fragments only: there the entries also set the pixel masks of the staged instances.
-    [[maybe_unused]] auto scatter_core_entries = [&](uint32_t batch_pos) {
+    // `limit`: staged instances of the batch (entries further down the list belong to a later batch, or - in a pass over a
+    // range of Gaussians - to Gaussians beyond the range, whose slots in this batch hold nothing).
+    [[maybe_unused]] auto scatter_core_entries = [&](uint32_t batch_pos, uint32_t limit) {
         const uint4* row = reinterpret_cast<const uint4*>(s_idx + pix * SM::idx_stride);
         auto put = [&](uint32_t j, int k) {
             s_core[j * 64 + pix] = (signed char)k;
@@ -253,10 +255,10 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
             if (q >= (K + 3) / 4) break;
             const uint4 v = row[q];
             const uint32_t j0 = v.x - batch_pos, j1 = v.y - batch_pos, j2 = v.z - batch_pos, j3 = v.w - batch_pos;
-            if (j0 < NT) put(j0, 4 * q);
-            if (4 * q + 1 < K && j1 < NT) put(j1, 4 * q + 1);
-            if (4 * q + 2 < K && j2 < NT) put(j2, 4 * q + 2);
-            if (4 * q + 3 < K && j3 < NT) put(j3, 4 * q + 3);
+            if (j0 < limit) put(j0, 4 * q);
+            if (4 * q + 1 < K && j1 < limit) put(j1, 4 * q + 1);
+            if (4 * q + 2 < K && j2 < limit) put(j2, 4 * q + 2);
+            if (4 * q + 3 < K && j3 < limit) put(j3, 4 * q + 3);
         }
     };
     for (uint32_t batch_begin = range.x; batch_begin < range.y; batch_begin += NT) {
@@ -282,7 +284,7 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
         if constexpr (kFirstK) {
             s_mask[tid] = 0;
             __syncthreads();
-            scatter_core_entries(batch_begin - __ldg(&tile_ranges[blockIdx.y * grid_w + blockIdx.x].x));   // the forward's stored core positions count from the start of the tile's list
+            scatter_core_entries(batch_begin - __ldg(&tile_ranges[blockIdx.y * grid_w + blockIdx.x].x), min(NT, range.y - batch_begin));   // the forward's stored core positions count from the start of the tile's list
             __syncthreads();
             my_mask = s_mask[tid];
         } else if (valid) {
@@ -316,7 +318,7 @@ __global__ void __launch_bounds__(kBwdThreads, kBwdMinBlocks) backward_tile_kern
         }
         s_off[tid] = excl;
         if (tid == 0) s_off[NT] = total_pairs;
-        if constexpr (SM::has_core && !kFirstK) scatter_core_entries(batch_begin - __ldg(&tile_ranges[blockIdx.y * grid_w + blockIdx.x].x));   // the forward's stored core positions count from the start of the tile's list
+        if constexpr (SM::has_core && !kFirstK) scatter_core_entries(batch_begin - __ldg(&tile_ranges[blockIdx.y * grid_w + blockIdx.x].x), min(NT, range.y - batch_begin));   // the forward's stored core positions count from the start of the tile's list
         __syncthreads();
         if (total_pairs == 0) continue;
         // my share of the pairs
