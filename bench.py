@@ -59,6 +59,7 @@ def parse_args():
                     help="train at N > 1: overlap = the backward pass runs in ranges of Gaussians and each finished range's rows are summed while "
                          "the next is computed (default); rows = the rows some rank kept, after the backward; dense = the dense tensors, after the backward")
     ap.add_argument("--exchange-chunks", type=int, default=4, help="ranges of Gaussians the backward pass is split into for --exchange overlap")
+    ap.add_argument("--exchange-split-pass", action="store_true", help="--exchange overlap: split the per-tile pass along the ranges too (default: only the per-Gaussian chain rule)")
     ap.add_argument("--reference-kind", default="auto", choices=["auto", "cuda", "cpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-views", type=int, default=12)
@@ -200,7 +201,7 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
         from htgs_b200.torch_bindings import rasterization
         rasterization.track_training_visibility(True)
     if overlap:
-        xchg = parallel.BackwardExchange(n_chunks=args.exchange_chunks, measure=True)
+        xchg = parallel.BackwardExchange(n_chunks=args.exchange_chunks, measure=True, split_pass=args.exchange_split_pass)
         rasterization.set_backward_hook(xchg)
     exchanged_rows = []
 
@@ -262,7 +263,7 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
             "config": {"workload": workload_name.replace("config1", "config2 (fwd+bwd, L1, one view per GPU)"), "views_per_step": world,
                        "allreduce_bytes_per_rank": grad_bytes if world > 1 else 0,
                        "gradient_exchange": ("none" if world == 1 else
-                                             f"rows of the union of the ranks' visible Gaussians, summed range by range ({args.exchange_chunks} ranges) while the backward pass runs" if overlap else
+                                             f"rows of the union of the ranks' visible Gaussians, summed range by range ({args.exchange_chunks} ranges{', per-tile pass split too' if args.exchange_split_pass else ''}) while the backward pass runs" if overlap else
                                              "rows of the union of the ranks' visible Gaussians" if sparse else "dense tensors"),
                        "exchange_exposed_ms": exposed,
                        "views_per_s": world * steps / (ms / 1000.0), "views_of_a_step": "spread evenly over the orbit", "parallelism": f"view-partitioned x{world} + gradient all-reduce"},

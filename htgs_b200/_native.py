@@ -141,6 +141,9 @@ def lib():
                                             ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(HtgsGradients), ctypes.c_void_p]
                 l.htgs_backward_static.argtypes = l.htgs_backward.argtypes
                 l.htgs_backward_range.argtypes = l.htgs_backward.argtypes[:8] + [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]
+                l.htgs_backward_accumulate.argtypes = l.htgs_backward.argtypes
+                l.htgs_backward_finish_range.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(HtgsTrainBlobs),
+                                                         ctypes.POINTER(HtgsGradients), ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]
                 l.htgs_gather_rows.argtypes = [ctypes.POINTER(HtgsRowTensors), ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
                 l.htgs_scatter_rows.argtypes = l.htgs_gather_rows.argtypes
                 l.htgs_forward_visibility.argtypes = [ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsTrainBlobs), ctypes.c_void_p, ctypes.c_void_p]

@@ -741,7 +741,25 @@ int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view
     if (!grads) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     if (!grads->scratch || grads->scratch_bytes < htgs_backward_scratch_bytes(scene)) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "backward scratch too small");
     return htgs::backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, grads->scratch, 0,
-                                     uint32_t(scene && scene->n_primitives > 0 ? scene->n_primitives : 0), stream_ptr);
+                                     uint32_t(scene && scene->n_primitives > 0 ? scene->n_primitives : 0), kBackwardAccumulate | kBackwardChainRule, stream_ptr);
+}
+
+int htgs_backward_accumulate(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                             const float* grad_image, const float* image, const HtgsGradients* grads, void* stream_ptr) {
+    if (!grads) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    if (!grads->scratch || grads->scratch_bytes < htgs_backward_scratch_bytes(scene)) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "backward scratch too small");
+    return htgs::backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, grads->scratch, 0,
+                                     uint32_t(scene && scene->n_primitives > 0 ? scene->n_primitives : 0), kBackwardAccumulate, stream_ptr);
+}
+
+int htgs_backward_finish_range(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, const HtgsGradients* grads,
+                               uint32_t first_gaussian, uint32_t n_gaussians, void* stream_ptr) {
+    if (!grads || !scene) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    if (!grads->scratch || grads->scratch_bytes < htgs_backward_scratch_bytes(scene)) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "backward scratch too small");
+    if (scene->n_primitives < 0 || uint64_t(first_gaussian) + uint64_t(n_gaussians) > uint64_t(scene->n_primitives))
+        return fail(HTGS_ERR_INVALID_ARGUMENT, "the range of Gaussians reaches beyond the scene");
+    static const float unused = 0.0f;      // the chain rule reads neither the image gradient nor the image
+    return htgs::backward_with_accum(ctx, scene, view, blobs, 0, &unused, &unused, grads, grads->scratch, first_gaussian, n_gaussians, kBackwardChainRule, stream_ptr);
 }
 
 int htgs_backward_range(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
@@ -753,14 +771,15 @@ int htgs_backward_range(HtgsContext* ctx, const HtgsScene* scene, const HtgsView
         return fail(HTGS_ERR_INVALID_ARGUMENT, "the range of Gaussians reaches beyond the scene");
     if (view && view->mode == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING && !(first_gaussian == 0 && n_gaussians == uint32_t(scene->n_primitives)))
         return fail(HTGS_ERR_UNSUPPORTED_MODE, "ALPHA_BLEND_GLOBAL_ORDERING cannot run its backward pass over a part of the Gaussians");
-    return htgs::backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, grads->scratch, first_gaussian, n_gaussians, stream_ptr);
+    return htgs::backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, grads->scratch, first_gaussian, n_gaussians,
+                                     kBackwardAccumulate | kBackwardChainRule, stream_ptr);
 }
 
 }  // extern "C"
 
 int htgs::backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                              const float* grad_image, const float* image, const HtgsGradients* grads, void* accum_ptr, uint32_t first, uint32_t count,
-                             void* stream_ptr) {
+                             int stages, void* stream_ptr) {
     if (!ctx || !blobs || !grads || !grad_image || !accum_ptr) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     int rc = validate(scene, view);
     if (rc != HTGS_OK) return rc;
@@ -778,8 +797,9 @@ int htgs::backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const Ht
     const PrimLayout P = carve_primitive_blob(blobs->per_primitive, scene->n_primitives);
     const InstLayout I = carve_instance_blob(blobs->per_instance, plan, n_instances);
     const PixelLayout X = carve_pixel_blob(blobs->per_pixel, view->mode, view->K, geo);
-    if (!blobs->per_primitive || blobs->per_primitive_bytes < P.bytes || !blobs->per_instance || blobs->per_instance_bytes < I.bytes ||
-        !blobs->per_pixel || blobs->per_pixel_bytes < X.bytes || !blobs->per_tile)
+    const bool accumulate = (stages & kBackwardAccumulate) != 0;      // the chain rule alone reads the per-Gaussian blob only
+    if (!blobs->per_primitive || blobs->per_primitive_bytes < P.bytes ||
+        (accumulate && (!blobs->per_instance || blobs->per_instance_bytes < I.bytes || !blobs->per_pixel || blobs->per_pixel_bytes < X.bytes || !blobs->per_tile)))
         return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "a forward blob is missing or too small");
     const GradAccumBuffers acc{static_cast<float4*>(accum_ptr)};
     const BackwardOutputs out{grads->grad_positions, grads->grad_scales, grads->grad_rotations, grads->grad_opacities, grads->grad_sh_0, grads->grad_sh_rest,
@@ -787,7 +807,7 @@ int htgs::backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const Ht
     // The six gradient tensors are only written after the per-tile kernel (2 ms of arithmetic), so they are cleared (0.7 GB at
     // configuration 2) on the context's side stream meanwhile, ordered after whatever the caller queued before this call.
     cudaEvent_t outputs_cleared = nullptr;
-    if (ctx->front_priority && count > 0) {
+    if (ctx->front_priority && count > 0 && accumulate) {
         cudaError_t e;
         if ((e = cudaEventRecord(ctx->front_begin, stream)) != cudaSuccess) return fail_cuda(e, "front event record");
         if ((e = cudaStreamWaitEvent(ctx->front_stream, ctx->front_begin, 0)) != cudaSuccess) return fail_cuda(e, "front stream wait");
@@ -796,7 +816,7 @@ int htgs::backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const Ht
         outputs_cleared = ctx->front_end;
     }
     const cudaError_t err = launch_backward(view->mode, view->K, *scene, *view, geo, P.prim, I.inst.prims[plan.final_buffer], static_cast<const uint2*>(blobs->per_tile),
-                                            X.px, grad_image, image, acc, out, outputs_cleared, ctx->sm_count, first, count, stream);
+                                            X.px, grad_image, image, acc, out, outputs_cleared, ctx->sm_count, first, count, stages, stream);
     if (err != cudaSuccess) return fail_cuda(err, "backward");
     return HTGS_OK;
 }

@@ -124,6 +124,7 @@ cudaError_t launch_max_weights(int mode, int K, const FrameGeometry& geo, const 
 struct GradAccumBuffers {
     float4* accum;           // [N][5] float4: dL/dVPMT1, dL/dVPMT2, dL/dVPMT4, (dL/drgb, dL/dopacity), (sum |dL/dposition|, 0, 0, 0)
 };
+constexpr int kBackwardAccumulate = 1, kBackwardChainRule = 2;
 struct BackwardOutputs {
     float* grad_positions; float* grad_scales; float* grad_rotations; float* grad_opacities; float* grad_sh_0; float* grad_sh_rest;
     float* densification_info;   // [rows][N] or null
@@ -134,7 +135,9 @@ cudaError_t launch_visibility(const uint32_t* n_touched, uint8_t* visible, uint3
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
                             const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
                             const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, cudaEvent_t outputs_cleared, int sm_count,
-                            uint32_t first, uint32_t count, cudaStream_t stream);
+                            uint32_t first, uint32_t count, int stages, cudaStream_t stream);
+// `stages`: kBackwardAccumulate = the per-tile (per-pixel for GLOBAL_ORDERING) pass that accumulates one record per Gaussian,
+// kBackwardChainRule = the per-Gaussian kernel that turns the records into the six gradients; both for a whole backward pass.
 // `outputs_cleared`: event after which rows [first, first + count) of the six tensors are zero, or null to clear them here.
 // [first, first + count): the Gaussians whose gradients the call computes (everything else is left untouched); a proper part
 // of the scene is refused (cudaErrorNotSupported) for GLOBAL_ORDERING.
@@ -143,7 +146,8 @@ cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs
 
 // api.cu: internals shared with the other translation units (C++ linkage: not part of the C-ABI).
 int backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
-                        const float* grad_image, const float* image, const HtgsGradients* grads, void* accum, uint32_t first, uint32_t count, void* stream);
+                        const float* grad_image, const float* image, const HtgsGradients* grads, void* accum, uint32_t first, uint32_t count, int stages,
+                        void* stream);
 int context_device(const HtgsContext* ctx);
 void set_last_error(const char* message);   // message htgs_last_error() returns on the calling thread
 

@@ -46,5 +46,6 @@ extern "C" int htgs_backward_static(HtgsContext* ctx, const HtgsScene* scene, co
         }
         g_static_accum_ptr[device] = static_cast<float4*>(ptr);
     }
-    return htgs::backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, g_static_accum_ptr[device], 0, uint32_t(scene->n_primitives > 0 ? scene->n_primitives : 0), stream);
+    return htgs::backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, g_static_accum_ptr[device], 0, uint32_t(scene->n_primitives > 0 ? scene->n_primitives : 0),
+                                     htgs::kBackwardAccumulate | htgs::kBackwardChainRule, stream);
 }

@@ -774,11 +774,19 @@ cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
                             const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
                             const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, cudaEvent_t outputs_cleared, int sm_count,
-                            uint32_t first, uint32_t count, cudaStream_t stream) {
+                            uint32_t first, uint32_t count, int stages, cudaStream_t stream) {
     (void)sm_count;
     const uint32_t n = uint32_t(scene.n_primitives);
     if (n == 0 || count == 0) return cudaSuccess;
     const bool whole = first == 0 && count == n;
+    if (!(stages & kBackwardAccumulate)) {      // the per-Gaussian chain rule alone, over records an earlier call accumulated
+        cudaError_t e = cudaSuccess;
+        if (outputs_cleared != nullptr && (e = cudaStreamWaitEvent(stream, outputs_cleared, 0)) != cudaSuccess) return e;
+        preprocess_backward_kernel<<<(count + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
+                                                                            view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
+                                                                            view.active_sh_bases, scene.total_sh_bases, first, first + count);
+        return cudaGetLastError();
+    }
     // the pixel-parallel GLOBAL_ORDERING pass needs every fragment in front of a fragment: it cannot run over a part of the Gaussians
     if (!whole && mode == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) return cudaErrorNotSupported;
     const uint32_t g_first = whole ? 0u : first, g_end = whole ? 0xffffffffu : first + count;
@@ -805,6 +813,7 @@ cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsV
     }
     if (err != cudaSuccess) return err;
     if (outputs_cleared != nullptr && (err = cudaStreamWaitEvent(stream, outputs_cleared, 0)) != cudaSuccess) return err;
+    if (!(stages & kBackwardChainRule)) return cudaSuccess;
     preprocess_backward_kernel<<<(count + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
                                                                         view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
                                                                         view.active_sh_bases, scene.total_sh_bases, first, first + count);

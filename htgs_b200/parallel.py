@@ -200,9 +200,16 @@ class BackwardExchange:
     (regularisers, weight decay) are NOT summed by this and stay the caller's to handle.
     ALPHA_BLEND_GLOBAL_ORDERING cannot run over a part of the Gaussians: it gets one range (no overlap)."""
 
-    def __init__(self, n_chunks: int = 4, group=None, measure: bool = False):
+    def __init__(self, n_chunks: int = 4, group=None, measure: bool = False, split_pass: bool = False):
         self.n_chunks = max(1, int(n_chunks))
         self.group = group
+        # split_pass = True: the per-tile pass of the backward runs range by range too (`htgs_backward_range`), so a range's
+        # exchange overlaps the next range's share of the whole pass - but every extra pass over the tiles has a fixed cost
+        # (measured: about a third of the whole pass per extra range at 3 M Gaussians), which only a slow interconnect repays.
+        # split_pass = False (default): the per-tile pass runs once and only the per-Gaussian chain rule runs range by range;
+        # packing, all-reduce and unpacking of successive ranges then overlap each other on three streams.
+        self.split_pass = bool(split_pass)
+        self._pack = self._unpack = None
         self.measure = measure          # record CUDA events around the wait for the last range's exchange (exposed_ms)
         self._marks = []
         self.exchange = None
@@ -213,7 +220,7 @@ class BackwardExchange:
         self._comm = None
 
     def chunk_ranges(self, n: int, mode: int = 0):
-        chunks = 1 if mode == 2 else self.n_chunks
+        chunks = 1 if (mode == 2 and self.split_pass) else self.n_chunks
         edges = [(n * k) // chunks for k in range(chunks + 1)]
         return [(edges[k], edges[k + 1] - edges[k]) for k in range(chunks)]
 
@@ -254,6 +261,9 @@ class BackwardExchange:
             self._comm = comm
             done = torch.cuda.Event()
             done.record(torch.cuda.current_stream(device))
+            if not self.dense and self.bounds is not None:
+                self._sum_rows_pipelined(tensors, self.bounds[k], self.bounds[k + 1], done)
+                return
             comm.wait_event(done)
             context = torch.cuda.stream(comm)
         else:
@@ -266,6 +276,42 @@ class BackwardExchange:
             elif self.bounds is not None:
                 _sum_rows(tensors, self.exchange.index, self.bounds[k], self.bounds[k + 1], comm, self.group)
 
+    def _sum_rows_pipelined(self, tensors, lo: int, hi: int, done) -> None:
+        """Packing, all-reduce and unpacking of one range on three streams, so that the packing of range k + 1 and the unpacking
+        of range k - 1 run while range k is on the wire."""
+        import ctypes
+        import torch
+        import torch.distributed as dist
+        from . import _native
+        if hi <= lo:
+            return
+        device = tensors[0].device
+        comm = self._comm
+        if self._pack is None:
+            self._pack, self._unpack = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+        table = _native.HtgsRowTensors()
+        table.n_tensors = len(tensors)
+        width = 0
+        for t, g in enumerate(tensors):
+            table.data[t] = g.data_ptr()
+            table.width[t] = g[0].numel()
+            width += g[0].numel()
+        lib = _native.lib()
+        first = self.exchange.index.data_ptr() + 8 * lo
+        self._pack.wait_event(done)
+        self._pack.wait_stream(comm)         # the index list was made on the communication stream
+        with torch.cuda.stream(self._pack):
+            packed = torch.empty((hi - lo, width), dtype=torch.float32, device=device)
+            _native.check(lib.htgs_gather_rows(ctypes.byref(table), first, hi - lo, packed.data_ptr(), self._pack.cuda_stream))
+        comm.wait_stream(self._pack)
+        with torch.cuda.stream(comm):
+            dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=self.group)
+        packed.record_stream(comm)
+        self._unpack.wait_stream(comm)
+        with torch.cuda.stream(self._unpack):
+            _native.check(lib.htgs_scatter_rows(ctypes.byref(table), first, hi - lo, packed.data_ptr(), self._unpack.cuda_stream))
+        packed.record_stream(self._unpack)
+
     def finish(self, grads) -> None:
         import torch
         if self._comm is not None:
@@ -274,6 +320,8 @@ class BackwardExchange:
                 before, after = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 before.record(current)
             current.wait_stream(self._comm)
+            if self._unpack is not None:
+                current.wait_stream(self._unpack)
             if self.measure:
                 after.record(current)
                 self._marks.append((before, after))

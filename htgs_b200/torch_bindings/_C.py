@@ -217,7 +217,8 @@ def forward_visibility(per_primitive_buffers, n_primitives: int):
 
 def backward(densification_info, grad_image, image, positions, scales, rotations, opacities, sh_rest, per_primitive_buffers, per_tile_buffers,
              per_instance_buffers, per_pixel_buffers, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases, width, height, near_plane,
-             far_plane, scale_modifier, n_instances, instance_primitive_indices_selector, use_distance_scaling, ranges=None, after_range=None):
+             far_plane, scale_modifier, n_instances, instance_primitive_indices_selector, use_distance_scaling, ranges=None, after_range=None,
+             split_pass=True):
     """`_C.backward` (rasterization/include/rasterization_api.h:28-55): returns the six gradients; `densification_info`
     ([2|3, N, 1] or empty) is updated in place.  `image` / `opacities` may be empty tensors, as the reference's autograd
     function passes them (torch_bindings/rasterization.py:72-76).
@@ -225,7 +226,9 @@ def backward(densification_info, grad_image, image, positions, scales, rotations
     Beyond the reference: with `ranges` (a list of (first Gaussian, count) that tiles [0, N)) the pass runs range by range
     (`htgs_backward_range`) and `after_range(k, first, count, grads)` is called after range k has been queued, with the six
     gradient tensors whose rows [first, first + count) are final once the stream gets there; a multi-GPU trainer starts
-    summing those rows over the ranks while the next range is computed (htgs_b200.parallel.BackwardExchange)."""
+    summing those rows over the ranks while the next range is computed (htgs_b200.parallel.BackwardExchange).  With
+    `split_pass=False` the per-tile pass runs once for all Gaussians (`htgs_backward_accumulate`) and only the per-Gaussian
+    chain rule runs range by range (`htgs_backward_finish_range`): less to hide the exchange behind, but no cost for the split."""
     device = positions.device
     if device.type != "cuda":
         raise ValueError("htgs_b200 rasterizer: tensors must live on a CUDA device")
@@ -275,12 +278,19 @@ def backward(densification_info, grad_image, image, positions, scales, rotations
                                             image_ptr, ctypes.byref(grads), stream))
         else:
             covered = 0
+            if not split_pass:
+                _native.check(lib.htgs_backward_accumulate(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), int(n_instances),
+                                                           grad_image.data_ptr(), image_ptr, ctypes.byref(grads), stream))
             for k, (first, count) in enumerate(ranges):
                 if first != covered:
                     raise ValueError("ranges must tile [0, N) in ascending order")
                 covered += count
-                _native.check(lib.htgs_backward_range(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), int(n_instances),
-                                                      grad_image.data_ptr(), image_ptr, ctypes.byref(grads), int(first), int(count), stream))
+                if split_pass:
+                    _native.check(lib.htgs_backward_range(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), int(n_instances),
+                                                          grad_image.data_ptr(), image_ptr, ctypes.byref(grads), int(first), int(count), stream))
+                else:
+                    _native.check(lib.htgs_backward_finish_range(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), ctypes.byref(grads),
+                                                                 int(first), int(count), stream))
                 if after_range is not None:
                     after_range(k, int(first), int(count), outs)
             if covered != n:

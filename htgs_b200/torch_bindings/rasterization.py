@@ -109,7 +109,8 @@ _backward_hook = None
 
 
 def set_backward_hook(hook) -> None:
-    """`hook` needs ranges(n_primitives, mode) -> [(first, count), ...], after_range(k, first, count, grads) and finish(grads)."""
+    """`hook` needs ranges(n_primitives, mode) -> [(first, count), ...], after_range(k, first, count, grads) and finish(grads);
+    an attribute `split_pass` (default True) says whether the per-tile pass is split along the ranges too or runs once."""
     global _backward_hook
     _backward_hook = hook
 
@@ -145,7 +146,8 @@ class _Rasterize(torch.autograd.Function):
             n = ctx.saved_tensors[1].shape[0]
             grads = _C.backward(ctx.densification_info, grad_image, *ctx.saved_tensors, *ctx.rasterizer_settings.as_tuple(),
                                 ctx.n_instances, ctx.instance_primitive_indices_selector, ctx.use_distance_scaling,
-                                ranges=hook.ranges(n, ctx.rasterizer_settings.mode.value), after_range=hook.after_range)
+                                ranges=hook.ranges(n, ctx.rasterizer_settings.mode.value), after_range=hook.after_range,
+                                split_pass=bool(getattr(hook, "split_pass", True)))
             hook.finish(grads)
         grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest = grads
         return (grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest, None, None, None)

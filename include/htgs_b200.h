@@ -218,6 +218,18 @@ int htgs_backward_range(HtgsContext* ctx, const HtgsScene* scene, const HtgsView
                         const float* grad_image, const float* image, const HtgsGradients* grads, uint32_t first_gaussian, uint32_t n_gaussians,
                         void* stream);
 
+/* The two stages of htgs_backward as separate calls, for trainers that start summing gradients over the ranks before the
+ * whole pass has finished without splitting the per-tile pass.  No counterparts in the reference.
+ *   htgs_backward_accumulate:    clears the six tensors and the scratch and runs the per-tile pass (per-pixel for
+ *                                ALPHA_BLEND_GLOBAL_ORDERING) that accumulates one record per Gaussian in `grads->scratch`;
+ *   htgs_backward_finish_range:  turns the records of the Gaussians [first_gaussian, first_gaussian + n_gaussians) into rows of the
+ *                                six gradient tensors (and updates densification_info for them).  Works for all four modes.
+ * htgs_backward equals accumulate followed by finish_range over the whole scene.  Stream-ordered, no host synchronisation. */
+int htgs_backward_accumulate(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                             const float* grad_image, const float* image, const HtgsGradients* grads, void* stream);
+int htgs_backward_finish_range(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, const HtgsGradients* grads,
+                               uint32_t first_gaussian, uint32_t n_gaussians, void* stream);
+
 /* Which Gaussians the training forward kept: visible[i] = 1 when Gaussian i passed culling and touches a tile (these are
  * the only rows of the six gradient tensors the backward pass can make non-zero), else 0.  Reads the per-Gaussian blob
  * htgs_forward_begin filled.  No counterpart in the reference; multi-GPU training uses it to exchange only the rows some

@@ -228,6 +228,10 @@ def test_backward_in_ranges_of_gaussians_equals_the_whole_pass(mode, K):
             assert torch.equal(g[first:first + count], s), "rows of a finished range must not change afterwards"
     with pytest.raises(ValueError):
         _C.backward(*args, ranges=[(0, n // 2)])
+    # the per-tile pass once, only the per-Gaussian chain rule range by range
+    staged = _C.backward(*args, ranges=ranges, split_pass=False)
+    for a, b in zip(staged, whole):
+        assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-30)
 
 
 def test_global_ordering_refuses_a_partial_backward():
@@ -246,3 +250,6 @@ def test_global_ordering_refuses_a_partial_backward():
         assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-30)
     with pytest.raises(RuntimeError):
         _C.backward(*args, ranges=[(0, 1000), (1000, scene.n - 1000)])
+    staged = _C.backward(*args, ranges=[(0, 1000), (1000, scene.n - 1000)], split_pass=False)      # the chain rule alone may be split
+    for a, b in zip(staged, whole):
+        assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-30)

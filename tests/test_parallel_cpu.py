@@ -98,8 +98,8 @@ def _chunked_worker(rank, world, port, out):
         xchg.finish(grads)
         ok = ok and all(torch.allclose(a, b, atol=1e-6) for a, b in zip(grads, expected))
         ok = ok and xchg.dense == (share > 0.6) and xchg.rows_exchanged == (n if share > 0.6 else int(torch.stack(keep).any(0).sum()))
-    one = parallel.BackwardExchange(n_chunks=4).ranges(n, 2)          # GLOBAL_ORDERING: the pass cannot be split
-    ok = ok and one == [(0, n)]
+    one = parallel.BackwardExchange(n_chunks=4, split_pass=True).ranges(n, 2)          # GLOBAL_ORDERING: the per-pixel pass cannot be split
+    ok = ok and one == [(0, n)] and len(parallel.BackwardExchange(n_chunks=4).ranges(n, 2)) == 4
     out.put((rank, ok, 0))
     dist.barrier()
     dist.destroy_process_group()
