@@ -93,8 +93,7 @@ FrameLayout carve_frame(void* blob, int n_primitives, int n_tiles, const SortPla
     L.inst.keys[1] = c.take_bytes<void>(size_t(cap) * plan.key_bytes);
     L.inst.prims[0] = c.take<uint32_t>(size_t(cap));
     L.inst.prims[1] = c.take<uint32_t>(size_t(cap));
-    L.inst.radix_table = c.take<uint32_t>(size_t(kMaxRadixBins) * (L.inst.sort_blocks_cap + 1));
-    L.inst.digit_totals = c.take<uint32_t>(kMaxRadixBins);
+    L.inst.sort_scratch = c.take_bytes<void>(sort_scratch_bytes(plan, L.inst.sort_blocks_cap));
     L.bytes = align_up(c.offset);
     return L;
 }
@@ -361,7 +360,7 @@ static int begin_frame(HtgsContext* ctx, const HtgsScene* scene, const HtgsView*
             if (info) { std::memset(info, 0, sizeof(*info)); info->workspace_bytes = fixed + 4096; }
             return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "workspace too small for the per-Gaussian buffers");
         }
-        const size_t per_inst = size_t(f.plan.key_bytes) * 2 + 8 + (size_t(kMaxRadixBins) * 4 + kSortTile - 1) / kSortTile;
+        const size_t per_inst = size_t(f.plan.key_bytes) * 2 + 8 + (sort_scratch_bytes(f.plan, 1024) / 1024 + kSortTile - 1) / kSortTile + 1;
         uint64_t capacity = (workspace_bytes - fixed - 8 * kAlign) / per_inst;
         while (capacity > 0 && carve_frame(nullptr, scene->n_primitives, f.geo.n_tiles, f.plan, capacity, false).bytes > workspace_bytes) capacity -= std::min<uint64_t>(capacity, 4096);
         f.capacity = capacity;
@@ -619,8 +618,7 @@ InstLayout carve_instance_blob(void* blob, const SortPlan& plan, uint64_t capaci
     L.inst.keys[1] = c.take_bytes<void>(size_t(cap) * plan.key_bytes);
     L.inst.prims[0] = c.take<uint32_t>(size_t(cap));
     L.inst.prims[1] = c.take<uint32_t>(size_t(cap));
-    L.inst.radix_table = c.take<uint32_t>(size_t(kMaxRadixBins) * (L.inst.sort_blocks_cap + 1));
-    L.inst.digit_totals = c.take<uint32_t>(kMaxRadixBins);
+    L.inst.sort_scratch = c.take_bytes<void>(sort_scratch_bytes(plan, L.inst.sort_blocks_cap));
     L.bytes = align_up(c.offset);
     return L;
 }

@@ -41,8 +41,7 @@ struct PrimBuffers {
 struct InstBuffers {
     void* keys[2];            // ping-pong key buffers, `key_bytes` wide
     uint32_t* prims[2];       // ping-pong Gaussian indices
-    uint32_t* radix_table;    // [n_bins_max * sort_blocks_cap]
-    uint32_t* digit_totals;   // [n_bins_max]
+    void* sort_scratch;       // ticket counters, digit histograms and look-back words of the radix passes (sort_scratch_bytes)
     uint32_t capacity;        // instances the buffers can hold
     uint32_t sort_blocks_cap; // ceil(capacity / kSortTile)
 };
@@ -61,6 +60,7 @@ struct SortPlan {
     int final_buffer;  // which ping-pong buffer holds the sorted result
 };
 SortPlan make_sort_plan(int mode, int n_tiles);
+size_t sort_scratch_bytes(const SortPlan& plan, uint32_t sort_blocks_cap);   // binning.cu
 
 struct FrameGeometry {
     int width, height, grid_w, grid_h, n_tiles, tile_w, tile_h;
