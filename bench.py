@@ -55,9 +55,10 @@ def parse_args():
     ap.add_argument("--k", type=int, default=16, choices=[1, 2, 4, 8, 16, 32], help="K of HYBRID_BLEND / FIRST_K (16 is the benchmark)")
     ap.add_argument("--workload", default="render", choices=["render", "render_fast", "train"],
                     help="render: configuration 1 (default, the headline metric); train: configuration 2 (fwd+bwd, L1 loss, one view per GPU, gradient all-reduce)")
-    ap.add_argument("--exchange", default="overlap", choices=["overlap", "rows", "dense"],
-                    help="train at N > 1: overlap = the backward pass runs in ranges of Gaussians and each finished range's rows are summed while "
-                         "the next is computed (default); rows = the rows some rank kept, after the backward; dense = the dense tensors, after the backward")
+    ap.add_argument("--exchange", default="rows", choices=["rows", "overlap", "dense"],
+                    help="train at N > 1: rows = the gradient rows of Gaussians some rank kept, summed after the backward (default: fastest on NVLink); "
+                         "overlap = the chain rule (optionally the whole backward pass) runs in ranges of Gaussians and each finished range's rows are summed "
+                         "while the next is computed; dense = the dense tensors, after the backward")
     ap.add_argument("--exchange-chunks", type=int, default=4, help="ranges of Gaussians the backward pass is split into for --exchange overlap")
     ap.add_argument("--exchange-split-pass", action="store_true", help="--exchange overlap: split the per-tile pass along the ranges too (default: only the per-Gaussian chain rule)")
     ap.add_argument("--reference-kind", default="auto", choices=["auto", "cuda", "cpu"])

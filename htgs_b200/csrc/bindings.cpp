@@ -32,6 +32,7 @@ using torch::Tensor;
 std::atomic<bool> g_deferred_checks{false};
 std::atomic<bool> g_max_weights_tail_credit{false};
 std::atomic<bool> g_track_visibility{false};
+std::atomic<bool> g_accumulate_visibility{false};   // OR the masks of successive training forwards until reset (several forwards per step)
 
 // One library context per (device, host thread, stream key): a context owns its workspace and pinned status word, so two
 // frames in flight at once must not share one.  Blocking calls use stream key 0, the non-blocking mode the stream's handle.
@@ -198,8 +199,11 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, int, int> forward(
         head.per_primitive = per_primitive.data_ptr(); head.per_primitive_bytes = pp_bytes;
         check(htgs_forward_visibility(&a.scene, &head, reinterpret_cast<uint8_t*>(visible.data_ptr()), stream));
         auto ready = std::make_shared<at::cuda::CUDAEvent>();
-        ready->record(torch_stream);
         std::lock_guard<std::mutex> lock(g_visibility_mutex);
+        auto earlier = g_visibility.find(a.device.index());
+        if (g_accumulate_visibility.load() && earlier != g_visibility.end() && earlier->second.visible.sizes() == visible.sizes())
+            visible.logical_or_(earlier->second.visible);      // a row any forward of the step kept can be non-zero
+        ready->record(torch_stream);
         g_visibility[a.device.index()] = VisibilityRecord{visible, ready};
     }
     const size_t pi_bytes = htgs_forward_instance_bytes(&a.view, n_instances);
@@ -360,6 +364,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         g_track_visibility.store(enable);
         if (!enable) { std::lock_guard<std::mutex> lock(g_visibility_mutex); g_visibility.clear(); }
     });
+    m.def("set_accumulate_visibility", [](bool enable) { g_accumulate_visibility.store(enable); });
+    m.def("reset_visibility", [](int device) {
+        std::lock_guard<std::mutex> lock(g_visibility_mutex);
+        if (device < 0) g_visibility.clear(); else g_visibility.erase(device);
+    }, py::arg("device") = -1);
     m.def("last_visibility", [](int device) -> py::object {
         std::lock_guard<std::mutex> lock(g_visibility_mutex);
         auto it = g_visibility.find(device);

@@ -98,6 +98,22 @@ def begin_row_exchange(rows, group=None, ready=None) -> "RowExchange":
     return RowExchange(torch.nonzero(union, as_tuple=False).squeeze(1))
 
 
+def rows_outside_are_zero(grads: Sequence, exchange: "RowExchange") -> bool:
+    """Debug check for the row exchange's one assumption: on this rank, every gradient row outside `exchange.index` is exactly
+    zero.  It fails when something other than the rasterizer's backward reaches the parameters - a regulariser on opacities
+    or scales, weight decay - or when a step ran several forwards without accumulating their visibility
+    (`track_training_visibility(True, accumulate=True)`): such rows would stay un-summed and the replicas would drift apart.
+    One masked abs-max per tensor and a host read: for tests and debugging, not for the training loop."""
+    import torch
+    tensors = [g for g in grads if g is not None and g.numel() > 0]
+    if not tensors:
+        return True
+    n = tensors[0].shape[0]
+    outside = torch.ones(n, dtype=torch.bool, device=tensors[0].device)
+    outside[exchange.index] = False
+    return all(float(g.reshape(n, -1)[outside].abs().max().item() if bool(outside.any()) else 0.0) == 0.0 for g in tensors)
+
+
 def finish_row_exchange(grads: Sequence, exchange: "RowExchange", group=None) -> int:
     """Second half: sums rows `exchange.index` of the per-Gaussian gradient tensors over the ranks, in place; every other row
     must be zero on every rank and stays untouched.  On CUDA the rows of all tensors are packed into one buffer by one kernel

@@ -150,8 +150,13 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
             head = _native.HtgsTrainBlobs(per_primitive.data_ptr(), per_primitive.numel(), None, 0, None, 0, None, 0)
             _native.check(lib.htgs_forward_visibility(ctypes.byref(scene), ctypes.byref(head), visible.data_ptr(), stream))
             ready = torch.cuda.Event()
+            key = torch.device(device)
+            mask = visible.view(torch.bool)
+            earlier = last_visibility.get(key)
+            if earlier is not None and accumulate_visibility and earlier[0].shape == mask.shape:
+                mask |= earlier[0]          # several forwards per step: a row any of them kept can be non-zero
             ready.record(torch.cuda.current_stream(device))
-            last_visibility[torch.device(device)] = (visible.view(torch.bool), ready)
+            last_visibility[key] = (mask, ready)
         per_instance = torch.empty(lib.htgs_forward_instance_bytes(ctypes.byref(view), n_inst.value), **byte)
         blobs = _native.HtgsTrainBlobs(per_primitive.data_ptr(), per_primitive.numel(), per_tile.data_ptr(), per_tile.numel(),
                                        per_instance.data_ptr(), per_instance.numel(), per_pixel.data_ptr(), per_pixel.numel())
@@ -166,6 +171,7 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
 # written) here, per device; see torch_bindings.rasterization.track_training_visibility.
 track_visibility = False
 last_visibility: dict = {}
+accumulate_visibility = False     # OR the masks of successive forwards until the mask is reset (several forwards per training step)
 
 
 # The extras of the compiled module `htgs_b200.pybind._C` under the same names, so that the surface can use either binding.
@@ -194,6 +200,13 @@ def set_track_visibility(enable: bool) -> None:
 
 def get_last_visibility(device_index: int):
     return last_visibility.get(torch.device("cuda", int(device_index)))
+
+
+def reset_visibility(device_index=None) -> None:
+    if device_index is None:
+        last_visibility.clear()
+    else:
+        last_visibility.pop(torch.device("cuda", int(device_index)), None)
 
 
 def benchmark(*args):

@@ -60,8 +60,22 @@ class RasterizerSettings(NamedTuple):
 
 # Multi-GPU training exchanges only the gradient rows some rank can have touched (htgs_b200.parallel): when tracking is on,
 # every training forward leaves the visibility of its Gaussians, per device.  No counterpart in the reference.
-def track_training_visibility(enable: bool) -> None:
+def track_training_visibility(enable: bool, accumulate: bool = False) -> None:
+    """`accumulate`: a training step with SEVERAL `diff_rasterize` forwards per rank needs the union of what they kept;
+    with it the masks of successive forwards are OR-ed until `reset_training_visibility()` (call that once per step)."""
     _impl.set_track_visibility(bool(enable))
+    if _via_pybind:
+        _impl.set_accumulate_visibility(bool(enable and accumulate))
+    else:
+        _C.accumulate_visibility = bool(enable and accumulate)
+
+
+def reset_training_visibility(device=None) -> None:
+    index = None if device is None else (torch.cuda.current_device() if torch.device(device).index is None else torch.device(device).index)
+    if _via_pybind:
+        _impl.reset_visibility(-1 if index is None else index)
+    else:
+        _C.reset_visibility(index)
 
 
 def last_training_visibility(device, with_event: bool = False):

@@ -59,6 +59,14 @@ def _rows_worker(rank, world, port, out):
     expected = [sum(data[r][i] for r in range(world)) for i in range(3)]
     union = torch.stack(keep).any(0)
     ok = count == int(union.sum()) and all(torch.equal(a, b) for a, b in zip(mine[:3], expected))
+    # the debug check of the exchange's assumption: true for conforming gradients, false once a row outside the union is touched
+    exchange = parallel.begin_row_exchange(keep[rank])
+    probe = [t.clone() for t in data[rank]]
+    ok = ok and parallel.rows_outside_are_zero(probe, exchange)
+    outside = torch.nonzero(~union).squeeze(1)
+    if outside.numel():
+        probe[0][outside[0]] = 1e-3         # what an opacity regulariser or weight decay would do
+        ok = ok and not parallel.rows_outside_are_zero(probe, exchange)
     empty = parallel.allreduce_gradients_rows([torch.zeros((n, 3))], torch.zeros(n, dtype=torch.bool))
     # a union above parallel.kDenseAbove of the rows switches to the dense all-reduce: same result
     wide = torch.rand(n, generator=gen) < 0.9
