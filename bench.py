@@ -650,7 +650,8 @@ def main():
     for vi in probe_views:
         mod.rasterize(*tensors, settings(cams_dev[vi]), True, False)   # the exact kernel counts candidates / accepted fragments
         fi = our_C.last_frame_info
-        infos.append((fi.n_instances, fi.n_visible, fi.candidate_pairs, fi.accepted_fragments, fi.key_bytes, fi.end_bit))
+        infos.append((fi.n_instances, fi.n_visible, fi.candidate_pairs, fi.accepted_fragments, fi.key_bytes, fi.end_bit, fi.warp_trips, fi.warp_trips_inserting,
+                      fi.lane_insertions))
     lib.htgs_set_collect_stats(ctx, 0)
     infos = np.array(infos, np.float64)
     I, n_vis, cand, acc = infos[:, 0].mean(), infos[:, 1].mean(), infos[:, 2].mean(), infos[:, 3].mean()
@@ -683,6 +684,10 @@ def main():
         "hbm_view": {"bound": "hbm", "bytes": I * 84.0 + n_pix * 16.0, "achieved": (I * 84.0 + n_pix * 16.0) / (blend_ms * 1e-3) / 1e9,
                      "peak": hbm_peak, "unit": "GB/s", "frac": (I * 84.0 + n_pix * 16.0) / (blend_ms * 1e-3) / 1e9 / hbm_peak,
                      "peak_source": f"{peak_kind} copy bandwidth"},
+        "insertion_chain": None if (fast or scene.mode != 0 or not infos[:, 6].mean()) else {
+            "warp_trips": float(infos[:, 6].mean()), "share_of_trips_with_an_insertion": float(infos[:, 7].mean() / infos[:, 6].mean()),
+            "inserting_lanes_per_such_trip": float(infos[:, 8].mean() / max(infos[:, 7].mean(), 1.0)),
+            "note": "the K-level chain sits behind a per-lane branch, so a warp runs it only when one of its lanes inserts"},
         "algorithmic": {"pairs": pairs, "accepted_fragments": acc, "candidate_pairs": cand, "flops": blend_flops,
                         "formula": "pairs*54 + accepted*(60+7K), the reference algorithm's work (every pixel of a tile tests every instance of the tile)"},
     }

@@ -48,6 +48,7 @@ class HtgsFrameInfo(ctypes.Structure):
         ("end_bit", ctypes.c_uint32), ("reruns", ctypes.c_uint32), ("device_error", ctypes.c_uint32),
         ("kernel_launches", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
         ("workspace_bytes", ctypes.c_uint64), ("candidate_pairs", ctypes.c_uint64), ("accepted_fragments", ctypes.c_uint64),
+        ("warp_trips", ctypes.c_uint64), ("warp_trips_inserting", ctypes.c_uint64), ("lane_insertions", ctypes.c_uint64),
     ]
 
 

@@ -394,6 +394,7 @@ static int finish_frame(HtgsContext* ctx, HtgsFrameInfo* info) {
         li.end_bit = uint32_t(f.plan.end_bit); li.reruns = f.reruns; li.device_error = st.error;
         li.kernel_launches = f.launches; li.reserved = 0;
         li.candidate_pairs = st.candidate_pairs; li.accepted_fragments = st.accepted_fragments;
+        li.warp_trips = st.warp_trips; li.warp_trips_inserting = st.warp_trips_inserting; li.lane_insertions = st.lane_insertions;
         li.workspace_bytes = carve_frame(nullptr, f.scene.n_primitives, f.geo.n_tiles, f.plan, st.overflow ? needed_capacity : f.capacity, false).bytes;
         if (info) *info = li;
         if (st.error) { f.active = false; return fail(HTGS_ERR_DEVICE_FLAG, "a kernel reported an internal error (bounded wait gave up)"); }

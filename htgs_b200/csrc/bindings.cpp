@@ -353,7 +353,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("key_bytes", &HtgsFrameInfo::key_bytes).def_readonly("end_bit", &HtgsFrameInfo::end_bit)
         .def_readonly("reruns", &HtgsFrameInfo::reruns).def_readonly("device_error", &HtgsFrameInfo::device_error)
         .def_readonly("kernel_launches", &HtgsFrameInfo::kernel_launches).def_readonly("workspace_bytes", &HtgsFrameInfo::workspace_bytes)
-        .def_readonly("candidate_pairs", &HtgsFrameInfo::candidate_pairs).def_readonly("accepted_fragments", &HtgsFrameInfo::accepted_fragments);
+        .def_readonly("candidate_pairs", &HtgsFrameInfo::candidate_pairs).def_readonly("accepted_fragments", &HtgsFrameInfo::accepted_fragments)
+        .def_readonly("warp_trips", &HtgsFrameInfo::warp_trips).def_readonly("warp_trips_inserting", &HtgsFrameInfo::warp_trips_inserting)
+        .def_readonly("lane_insertions", &HtgsFrameInfo::lane_insertions);
     py::class_<ReadyEvent>(m, "ReadyEvent").def("wait", &ReadyEvent::wait).def("synchronize", &ReadyEvent::synchronize);
     m.def("frame_info", [] { return tls.last_info; }, "statistics of the calling thread's most recent frame");
     m.def("set_deferred_checks", [](bool enable) { if (!enable) frame_results(-1); g_deferred_checks.store(enable); });

@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
     const uint2 range = tile_ranges[(tile_y / TS::split_y) * grid_w + tile_x / TS::split_x];   // grid_w counts binning tiles
     uint32_t phase = 0;
     bool wait_failed = false;
-    [[maybe_unused]] uint32_t stat_candidates = 0, stat_accepted = 0;
+    [[maybe_unused]] uint32_t stat_candidates = 0, stat_accepted = 0, stat_trips = 0, stat_trips_inserting = 0, stat_insertions = 0;
     // pixel rectangle of this warp (tw x rows_per_warp pixels; lane = row * tw + column)
     const float rect_x0 = float(tile_x * TS::tw);
     const float rect_y0 = float(tile_y * TS::th + warp * TS::rows_per_warp);
@@ -327,7 +327,15 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                     float4 frag0, frag1;
                     const bool ok0 = evaluate(v0, j0, depth0, frag0);
                     const bool ok1 = evaluate(v1, j1, depth1, frag1);
+                    if constexpr (STATS) {   // how often the insertion chain runs for the warp (the branch in commit is the warp vote)
+                        const bool in0 = ok0 && depth0 < kd[K - 1] && frag0.w >= MT::min_alpha_core;
+                        stat_trips += 1; stat_trips_inserting += __any_sync(0xffffffffu, in0) ? 1 : 0; stat_insertions += in0 ? 1 : 0;
+                    }
                     if (ok0) commit(depth0, frag0, j0);
+                    if constexpr (STATS) {
+                        const bool in1 = ok1 && depth1 < kd[K - 1] && frag1.w >= MT::min_alpha_core;
+                        stat_trips += 1; stat_trips_inserting += __any_sync(0xffffffffu, in1) ? 1 : 0; stat_insertions += in1 ? 1 : 0;
+                    }
                     if (ok1) commit(depth1, frag1, j1);
                 }
             } else {
@@ -403,6 +411,11 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
     if constexpr (STATS) {
         const uint32_t c = __reduce_add_sync(0xffffffffu, stat_candidates), a = __reduce_add_sync(0xffffffffu, stat_accepted);
         if (lane == 0) { atomicAdd(&status->candidate_pairs, (unsigned long long)c); atomicAdd(&status->accepted_fragments, (unsigned long long)a); }
+        const uint32_t ins = __reduce_add_sync(0xffffffffu, stat_insertions);
+        if (lane == 0 && stat_trips) {
+            atomicAdd(&status->warp_trips, (unsigned long long)stat_trips); atomicAdd(&status->warp_trips_inserting, (unsigned long long)stat_trips_inserting);
+            atomicAdd(&status->lane_insertions, (unsigned long long)ins);
+        }
     }
     if (!inside) return;
 

@@ -111,7 +111,10 @@ struct FrameStatus {
     unsigned int error;           // bounded waits that gave up, bad arguments seen on the device, ...
     unsigned long long candidate_pairs;     // statistics mode of the blend kernels
     unsigned long long accepted_fragments;  // statistics mode of the blend kernels
-    unsigned int reserved[8];
+    unsigned long long warp_trips;          // statistics mode, HYBRID_BLEND: warp-level evaluations of one candidate per lane
+    unsigned long long warp_trips_inserting;// ... of which at least one lane inserted into its K-buffer (the insertion chain ran)
+    unsigned long long lane_insertions;     // ... and the lanes that inserted
+    unsigned int reserved[2];
 };
 
 // ---------------------------------------------------------------------------

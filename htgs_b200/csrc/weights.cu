@@ -247,7 +247,13 @@ cudaError_t launch_max_weights(int mode, int K, const FrameGeometry& geo, const 
                                float* max_weights, float weight_threshold, bool credit_tail, cudaStream_t stream) {
     const int k = effective_k(mode, K);
     switch (mode) {
-        case HTGS_MODE_HYBRID_BLEND: return launch_w_k<HTGS_MODE_HYBRID_BLEND>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
+        case HTGS_MODE_HYBRID_BLEND:
+            // Without the tail credit HYBRID needs its K-buffer weights only, which is what the reference extension computes: its
+            // link resolves HYBRID's kernel dispatcher to FIRST_K's copy (hybrid_blend/update_max_weights.cu:15-28 against
+            // alpha_blend_first_k/update_max_weights.cu:15-28), so FIRST_K's kernel walks HYBRID's tile lists.  The same is done
+            // here: fragments below alpha 1/20 are dropped at once instead of being summed into a tail nobody reads.
+            if (!credit_tail) return launch_w_k<HTGS_MODE_ALPHA_BLEND_FIRST_K>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, false, stream);
+            return launch_w_k<HTGS_MODE_HYBRID_BLEND>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, true, stream);
         case HTGS_MODE_ALPHA_BLEND_FIRST_K: return launch_w_k<HTGS_MODE_ALPHA_BLEND_FIRST_K>(k, geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
         case HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING: return launch_w<HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);
         case HTGS_MODE_OIT_BLEND: return launch_w<HTGS_MODE_OIT_BLEND, 1>(geo, prim, prims_sorted, tile_ranges, max_weights, weight_threshold, credit_tail, stream);

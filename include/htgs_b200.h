@@ -84,6 +84,9 @@ typedef struct HtgsFrameInfo {
     uint64_t workspace_bytes;    /* bytes a caller-provided workspace must have for this frame */
     uint64_t candidate_pairs;    /* statistics mode only: (pixel, Gaussian) pairs that passed the outline test */
     uint64_t accepted_fragments; /* statistics mode only: fragments accepted by the exact test */
+    uint64_t warp_trips;           /* statistics mode, HYBRID_BLEND: warp-level evaluations of one candidate per lane */
+    uint64_t warp_trips_inserting; /* ... in which at least one lane inserted into its K-buffer (the insertion chain ran) */
+    uint64_t lane_insertions;      /* ... and the number of lanes that inserted */
 } HtgsFrameInfo;
 
 /* Device pointers into the workspace of the last htgs_render call of a context; valid
