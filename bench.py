@@ -55,8 +55,9 @@ def parse_args():
     ap.add_argument("--k", type=int, default=16, choices=[1, 2, 4, 8, 16, 32], help="K of HYBRID_BLEND / FIRST_K (16 is the benchmark)")
     ap.add_argument("--workload", default="render", choices=["render", "render_fast", "train"],
                     help="render: configuration 1 (default, the headline metric); train: configuration 2 (fwd+bwd, L1 loss, one view per GPU, gradient all-reduce)")
-    ap.add_argument("--exchange", default="rows", choices=["rows", "overlap", "dense"],
-                    help="train at N > 1: rows = the gradient rows of Gaussians some rank kept, summed after the backward (default: fastest on NVLink); "
+    ap.add_argument("--exchange", default="compact", choices=["rows", "compact", "compact-nccl", "overlap", "dense"],
+                    help="train at N > 1: compact = every rank publishes 64 bytes per Gaussian its view kept and expands every rank's buffer into the "
+                         "dense sums, reading the peers' buffers over NVLink inside the kernel (default; compact-nccl: through one all-gather instead); rows = the gradient rows of Gaussians some rank kept, summed after the backward; "
                          "overlap = the chain rule (optionally the whole backward pass) runs in ranges of Gaussians and each finished range's rows are summed "
                          "while the next is computed; dense = the dense tensors, after the backward")
     ap.add_argument("--exchange-chunks", type=int, default=4, help="ranges of Gaussians the backward pass is split into for --exchange overlap")
@@ -195,8 +196,9 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
 
     # Exchange: this library's arm sums only the gradient rows of Gaussians some rank's view kept (the others are zero on
     # every rank); the reference has no multi-GPU path and no such list, its arm all-reduces the dense tensors.
-    sparse = dist is not None and not is_reference and args.exchange in ("rows", "overlap")
+    sparse = dist is not None and not is_reference and args.exchange in ("rows", "overlap", "compact", "compact-nccl")
     overlap = sparse and args.exchange == "overlap"
+    compact = sparse and args.exchange in ("compact", "compact-nccl")
     xchg = None
     if sparse:
         from htgs_b200.torch_bindings import rasterization
@@ -204,7 +206,12 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
     if overlap:
         xchg = parallel.BackwardExchange(n_chunks=args.exchange_chunks, measure=True, split_pass=args.exchange_split_pass)
         rasterization.set_backward_hook(xchg)
+    if compact:
+        xchg = parallel.CompactExchange(transport="peer" if args.exchange == "compact" else "nccl")
+        compact_transport = xchg.prepare(scene.n, device)      # falls back to the all-gather transport on all ranks if the buffers cannot be mapped
+        rasterization.set_backward_hook(xchg)
     exchanged_rows = []
+    gathered_bytes = []
 
     def step(s):
         vi = (s + rank * (n_views // world)) % n_views      # the views of a step are spread evenly over the orbit, as a random batch would be
@@ -216,12 +223,17 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
             visible, ready = rasterization.last_training_visibility(device, with_event=True)
             if overlap:
                 xchg.begin(visible, ready, mode=scene.mode)
+            elif compact:
+                xchg.begin(visible, ready)
             else:
                 exchange = parallel.begin_row_exchange(visible, ready=ready)
         loss = (image - target).abs().mean()
         loss.backward()      # with --exchange overlap the rasterizer's backward sums its gradients over the ranks range by range
         if overlap:
             exchanged_rows.append(xchg.rows_exchanged)
+        elif compact:
+            exchanged_rows.append(xchg.rows_published)
+            gathered_bytes.append(xchg.bytes_gathered)
         elif sparse:
             exchanged_rows.append(parallel.finish_row_exchange([l.grad for l in leaves], exchange))
         elif dist is not None:
@@ -250,6 +262,12 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
     clocks = sampler.stop(t0, t1)
     ms = parallel.max_over_ranks(e0.elapsed_time(e1), device)
     exposed = None
+    if compact:
+        rasterization.set_backward_hook(None)
+        counts = xchg.published_rows()
+        if counts is not None:      # peer transport: bytes this rank read from the other ranks' buffers in the last step
+            gathered_bytes = [sum(c for r, c in enumerate(counts) if r != rank) * parallel.kCompactRowBytes] * (warmup + 1)
+        xchg.close()
     if overlap:
         rasterization.set_backward_hook(None)
         waits = xchg.exposed_ms(last=steps)
@@ -258,13 +276,15 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
         rasterization.track_training_visibility(False)
     n = scene.n
     row_bytes = (3 + 3 + 4 + 1 + 3 + 3 * scene.sh_rest.shape[1]) * 4
-    grad_bytes = int(np.mean(exchanged_rows[warmup:])) * row_bytes if sparse else n * row_bytes
+    grad_bytes = int(np.mean(gathered_bytes[warmup:])) if compact else int(np.mean(exchanged_rows[warmup:])) * row_bytes if sparse else n * row_bytes
     line = {"metric": "train-steps/s", "value": steps / (ms / 1000.0), "unit": "steps/s", "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name.replace("config1", "config2 (fwd+bwd, L1, one view per GPU)"), "views_per_step": world,
                        "allreduce_bytes_per_rank": grad_bytes if world > 1 else 0,
                        "gradient_exchange": ("none" if world == 1 else
                                              f"rows of the union of the ranks' visible Gaussians, summed range by range ({args.exchange_chunks} ranges{', per-tile pass split too' if args.exchange_split_pass else ''}) while the backward pass runs" if overlap else
+                                             ("compact rows (64 B per Gaussian a rank's view kept), read from the peers' buffers over NVLink by the kernel that expands them" if compact_transport == "peer"
+                                              else "compact rows (64 B per Gaussian a rank's view kept), all-gathered and expanded on every rank") if compact else
                                              "rows of the union of the ranks' visible Gaussians" if sparse else "dense tensors"),
                        "exchange_exposed_ms": exposed,
                        "views_per_s": world * steps / (ms / 1000.0), "views_of_a_step": "spread evenly over the orbit", "parallelism": f"view-partitioned x{world} + gradient all-reduce"},
@@ -280,7 +300,8 @@ def train_leg_summary(line):
     """The training line folded into the `train` object of the default workload's JSON line."""
     cfg = line["config"]
     return {"metric": "train-steps/s", "steps_per_s": line["value"], "ms_per_step": line["ms_per_step"], "views_per_s": cfg["views_per_s"],
-            "exchange": {"none": "none", "dense tensors": "dense"}.get(cfg["gradient_exchange"], "rows, overlapped with the backward" if "range by range" in cfg["gradient_exchange"] else "rows"),
+            "exchange": {"none": "none", "dense tensors": "dense"}.get(cfg["gradient_exchange"], "rows, overlapped with the backward" if "range by range" in cfg["gradient_exchange"]
+                                                                       else "compact" if cfg["gradient_exchange"].startswith("compact") else "rows"),
             "exchange_exposed_ms": cfg.get("exchange_exposed_ms"),
             "allreduce_bytes_per_rank": cfg["allreduce_bytes_per_rank"], "n_gpus": line["n_gpus"], "steps": line["steps"], "warmup": line["warmup"],
             "workload": cfg["workload"], "clocks": line["clocks"], "final_loss": line["final_loss"]}

@@ -145,6 +145,14 @@ def lib():
                 l.htgs_backward_accumulate.argtypes = l.htgs_backward.argtypes
                 l.htgs_backward_finish_range.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(HtgsTrainBlobs),
                                                          ctypes.POINTER(HtgsGradients), ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]
+                l.htgs_compact_rows_bytes.restype = ctypes.c_size_t
+                l.htgs_compact_rows_bytes.argtypes = [ctypes.c_uint32]
+                l.htgs_backward_compact.argtypes = l.htgs_backward.argtypes[:8] + [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p]
+                l.htgs_expand_add_rows.argtypes = [ctypes.POINTER(HtgsScene), ctypes.c_void_p, ctypes.c_uint32, ctypes.POINTER(HtgsGradients), ctypes.c_void_p]
+                l.htgs_peer_buffer_create.argtypes = [ctypes.c_int, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
+                l.htgs_peer_buffer_open.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]
+                l.htgs_peer_buffer_close.argtypes = [ctypes.c_int, ctypes.c_void_p]
+                l.htgs_peer_buffer_destroy.argtypes = [ctypes.c_int, ctypes.c_void_p]
                 l.htgs_gather_rows.argtypes = [ctypes.POINTER(HtgsRowTensors), ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
                 l.htgs_scatter_rows.argtypes = l.htgs_gather_rows.argtypes
                 l.htgs_forward_visibility.argtypes = [ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsTrainBlobs), ctypes.c_void_p, ctypes.c_void_p]

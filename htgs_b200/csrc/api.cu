@@ -395,6 +395,9 @@ static int finish_frame(HtgsContext* ctx, HtgsFrameInfo* info) {
         li.kernel_launches = f.launches; li.reserved = 0;
         li.candidate_pairs = st.candidate_pairs; li.accepted_fragments = st.accepted_fragments;
         li.warp_trips = st.warp_trips; li.warp_trips_inserting = st.warp_trips_inserting; li.lane_insertions = st.lane_insertions;
+#ifdef HTGS_PROBE_FLOOR
+        li.lane_insertions = ((unsigned long long)st.reserved[0] << 32) | st.reserved[1];
+#endif
         li.workspace_bytes = carve_frame(nullptr, f.scene.n_primitives, f.geo.n_tiles, f.plan, st.overflow ? needed_capacity : f.capacity, false).bytes;
         if (info) *info = li;
         if (st.error) { f.active = false; return fail(HTGS_ERR_DEVICE_FLAG, "a kernel reported an internal error (bounded wait gave up)"); }
@@ -743,6 +746,15 @@ int htgs_backward(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view
                                      uint32_t(scene && scene->n_primitives > 0 ? scene->n_primitives : 0), kBackwardAccumulate | kBackwardChainRule, stream_ptr);
 }
 
+int htgs_backward_compact(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                          const float* grad_image, const float* image, const HtgsGradients* grads, void* rows, uint32_t capacity_rows, void* stream_ptr) {
+    if (!grads || !rows) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
+    if (!grads->scratch || grads->scratch_bytes < htgs_backward_scratch_bytes(scene)) return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "backward scratch too small");
+    return htgs::backward_with_accum(ctx, scene, view, blobs, n_instances, grad_image, image, grads, grads->scratch, 0,
+                                     uint32_t(scene && scene->n_primitives > 0 ? scene->n_primitives : 0), kBackwardAccumulate | kBackwardChainRule, stream_ptr,
+                                     rows, capacity_rows);
+}
+
 int htgs_backward_accumulate(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                              const float* grad_image, const float* image, const HtgsGradients* grads, void* stream_ptr) {
     if (!grads) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
@@ -778,14 +790,16 @@ int htgs_backward_range(HtgsContext* ctx, const HtgsScene* scene, const HtgsView
 
 int htgs::backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                              const float* grad_image, const float* image, const HtgsGradients* grads, void* accum_ptr, uint32_t first, uint32_t count,
-                             int stages, void* stream_ptr) {
+                             int stages, void* stream_ptr, void* compact_rows, uint32_t compact_capacity) {
     if (!ctx || !blobs || !grads || !grad_image || !accum_ptr) return fail(HTGS_ERR_INVALID_ARGUMENT, "null argument");
     int rc = validate(scene, view);
     if (rc != HTGS_OK) return rc;
     DeviceGuard guard(ctx->device);
     if (guard.status != cudaSuccess) return fail_cuda(guard.status, "cudaSetDevice");
     if (view->mode == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING && !image) return fail(HTGS_ERR_INVALID_ARGUMENT, "ALPHA_BLEND_GLOBAL_ORDERING needs the forward image");
-    if (scene->n_primitives > 0 && (!grads->grad_positions || !grads->grad_scales || !grads->grad_rotations || !grads->grad_opacities || !grads->grad_sh_0 ||
+    if (compact_rows && (reinterpret_cast<uintptr_t>(compact_rows) & 15u) != 0) return fail(HTGS_ERR_INVALID_ARGUMENT, "the compact row buffer must be 16-byte aligned");
+    const bool dense_given = grads->grad_positions || grads->grad_scales || grads->grad_rotations || grads->grad_opacities || grads->grad_sh_0 || grads->grad_sh_rest;
+    if ((!compact_rows || dense_given) && scene->n_primitives > 0 && (!grads->grad_positions || !grads->grad_scales || !grads->grad_rotations || !grads->grad_opacities || !grads->grad_sh_0 ||
                                     (scene->total_sh_bases > 0 && !grads->grad_sh_rest)))
         return fail(HTGS_ERR_INVALID_ARGUMENT, "gradient output pointers must not be null");
     if (grads->densification_info && grads->densification_rows != 2 && grads->densification_rows != 3)
@@ -801,12 +815,14 @@ int htgs::backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const Ht
         (accumulate && (!blobs->per_instance || blobs->per_instance_bytes < I.bytes || !blobs->per_pixel || blobs->per_pixel_bytes < X.bytes || !blobs->per_tile)))
         return fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "a forward blob is missing or too small");
     const GradAccumBuffers acc{static_cast<float4*>(accum_ptr)};
-    const BackwardOutputs out{grads->grad_positions, grads->grad_scales, grads->grad_rotations, grads->grad_opacities, grads->grad_sh_0, grads->grad_sh_rest,
-                              grads->densification_info, grads->densification_info ? grads->densification_rows : 0, grads->use_distance_scaling != 0};
+    BackwardOutputs out{grads->grad_positions, grads->grad_scales, grads->grad_rotations, grads->grad_opacities, grads->grad_sh_0, grads->grad_sh_rest,
+                        grads->densification_info, grads->densification_info ? grads->densification_rows : 0, grads->use_distance_scaling != 0};
+    out.compact_rows = static_cast<float4*>(compact_rows);
+    out.compact_capacity = compact_capacity;
     // The six gradient tensors are only written after the per-tile kernel (2 ms of arithmetic), so they are cleared (0.7 GB at
     // configuration 2) on the context's side stream meanwhile, ordered after whatever the caller queued before this call.
     cudaEvent_t outputs_cleared = nullptr;
-    if (ctx->front_priority && count > 0 && accumulate) {
+    if (ctx->front_priority && count > 0 && accumulate && (!compact_rows || dense_given)) {
         cudaError_t e;
         if ((e = cudaEventRecord(ctx->front_begin, stream)) != cudaSuccess) return fail_cuda(e, "front event record");
         if ((e = cudaStreamWaitEvent(ctx->front_stream, ctx->front_begin, 0)) != cudaSuccess) return fail_cuda(e, "front stream wait");

@@ -190,6 +190,9 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
     uint32_t phase = 0;
     bool wait_failed = false;
     [[maybe_unused]] uint32_t stat_candidates = 0, stat_accepted = 0, stat_trips = 0, stat_trips_inserting = 0, stat_insertions = 0;
+#ifdef HTGS_PROBE_FLOOR
+    [[maybe_unused]] uint32_t probe_floor_chain = 0, probe_floor_eval = 0;
+#endif
     // pixel rectangle of this warp (tw x rows_per_warp pixels; lane = row * tw + column)
     const float rect_x0 = float(tile_x * TS::tw);
     const float rect_y0 = float(tile_y * TS::th + warp * TS::rows_per_warp);
@@ -272,6 +275,9 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
             }
             const uint32_t n_cand = __popcll(cand);
             if constexpr (STATS) stat_candidates += n_cand;
+#ifdef HTGS_PROBE_FLOOR
+            uint32_t probe_ins = 0;
+#endif
             const uint32_t n_iter = __reduce_max_sync(0xffffffffu, n_cand);
             const uint32_t chunk_base = chunk * TS::chunk;
             auto pop_candidate = [&](bool& valid) -> uint32_t {
@@ -330,14 +336,23 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                     if constexpr (STATS) {   // how often the insertion chain runs for the warp (the branch in commit is the warp vote)
                         const bool in0 = ok0 && depth0 < kd[K - 1] && frag0.w >= MT::min_alpha_core;
                         stat_trips += 1; stat_trips_inserting += __any_sync(0xffffffffu, in0) ? 1 : 0; stat_insertions += in0 ? 1 : 0;
+#ifdef HTGS_PROBE_FLOOR
+                        probe_ins += in0 ? 1 : 0;
+#endif
                     }
                     if (ok0) commit(depth0, frag0, j0);
                     if constexpr (STATS) {
                         const bool in1 = ok1 && depth1 < kd[K - 1] && frag1.w >= MT::min_alpha_core;
                         stat_trips += 1; stat_trips_inserting += __any_sync(0xffffffffu, in1) ? 1 : 0; stat_insertions += in1 ? 1 : 0;
+#ifdef HTGS_PROBE_FLOOR
+                        probe_ins += in1 ? 1 : 0;
+#endif
                     }
                     if (ok1) commit(depth1, frag1, j1);
                 }
+#ifdef HTGS_PROBE_FLOOR
+                if constexpr (STATS) { probe_floor_chain += __reduce_max_sync(0xffffffffu, probe_ins); probe_floor_eval += n_iter; }
+#endif
             } else {
                 // The other three modes use the same two-candidates-per-trip shape: both evaluations (divide, expf, depth) are
                 // independent instruction streams; the state updates happen in list order.  A fragment counts iff it passes
@@ -415,6 +430,9 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
         if (lane == 0 && stat_trips) {
             atomicAdd(&status->warp_trips, (unsigned long long)stat_trips); atomicAdd(&status->warp_trips_inserting, (unsigned long long)stat_trips_inserting);
             atomicAdd(&status->lane_insertions, (unsigned long long)ins);
+#ifdef HTGS_PROBE_FLOOR
+            atomicAdd(&status->reserved[0], probe_floor_chain); atomicAdd(&status->reserved[1], probe_floor_eval);
+#endif
         }
     }
     if (!inside) return;

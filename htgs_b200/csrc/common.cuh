@@ -185,4 +185,49 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gm
 
 __device__ __forceinline__ unsigned int lanemask_lt() { unsigned int m; asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m)); return m; }
 
+// ---------------------------------------------------------------------------
+// Compact gradient rows (multi-GPU gradient exchange).  A buffer is one 64-byte header followed by 64-byte rows,
+// one per Gaussian the view kept, in no particular order:
+//     float4 0: Gaussian index (bits), dL/dposition          float4 2: dL/drotation (r, x, y, z)
+//     float4 1: dL/dscale, dL/dopacity                       float4 3: dL/drgb after the clamp mask, 0
+// The rows of grad_sh_0 and grad_sh_rest are products of dL/drgb with functions of the view direction
+// (kernel_utils.cuh:190-281 of the reference), so a reader that has the camera position rebuilds them.
+// ---------------------------------------------------------------------------
+struct CompactGradientHeader {
+    unsigned int count;            // rows appended (may exceed the capacity: rows beyond it were dropped)
+    float cam_x, cam_y, cam_z;     // camera position of the view the rows were computed for
+    unsigned int active_sh_bases;  // 1, 4, 9 or 16
+    unsigned int reserved[11];
+};
+static_assert(sizeof(CompactGradientHeader) == 64, "the header takes one row");
+constexpr int kCompactRowFloat4s = 4;
+constexpr float kShBand0 = 0.28209479177387814f;
+
+// dL/dsh_rest of one Gaussian: rows[i] = (basis function i + 1 of `dir`) * grad_rgb for the active bases; returns how many
+// rows were written (0, 3, 8 or 15).  One definition for the kernel that writes dense gradients and for the kernels that
+// rebuild them from compact rows, so that both produce the same bits.
+__device__ __forceinline__ int sh_rest_gradient_rows(const float3& dir, const float3& grad_rgb, int active_sh_bases, float3 (&rows)[15]) {
+    if (active_sh_bases <= 1) return 0;
+    const float dx = dir.x, dy = dir.y, dz = dir.z;
+    rows[0] = (-0.48860251190291987f * dy) * grad_rgb;
+    rows[1] = (0.48860251190291987f * dz) * grad_rgb;
+    rows[2] = (-0.48860251190291987f * dx) * grad_rgb;
+    if (active_sh_bases <= 4) return 3;
+    const float sxx = dx * dx, syy = dy * dy, szz = dz * dz, sxy = dx * dy, sxz = dx * dz, syz = dy * dz;
+    rows[3] = (1.0925484305920792f * sxy) * grad_rgb;
+    rows[4] = (-1.0925484305920792f * syz) * grad_rgb;
+    rows[5] = (0.94617469575755997f * szz - 0.31539156525251999f) * grad_rgb;
+    rows[6] = (-1.0925484305920792f * sxz) * grad_rgb;
+    rows[7] = (0.54627421529603959f * sxx - 0.54627421529603959f * syy) * grad_rgb;
+    if (active_sh_bases <= 9) return 8;
+    rows[8] = (0.59004358992664352f * dy * (-3.0f * sxx + syy)) * grad_rgb;
+    rows[9] = (2.8906114426405538f * sxy * dz) * grad_rgb;
+    rows[10] = (0.45704579946446572f * dy * (1.0f - 5.0f * szz)) * grad_rgb;
+    rows[11] = (0.3731763325901154f * dz * (5.0f * szz - 3.0f)) * grad_rgb;
+    rows[12] = (0.45704579946446572f * dx * (1.0f - 5.0f * szz)) * grad_rgb;
+    rows[13] = (1.4453057213202769f * dz * (sxx - syy)) * grad_rgb;
+    rows[14] = (0.59004358992664352f * dx * (-sxx + 3.0f * syy)) * grad_rgb;
+    return 15;
+}
+
 }  // namespace htgs

@@ -8,6 +8,8 @@
 // coalesced, the tensor side moves whole rows of 4 to 540 bytes.
 #include "kernels.h"
 
+#include <cstring>
+
 
 namespace htgs {
 
@@ -58,6 +60,128 @@ __global__ void __launch_bounds__(kRowBlock) move_rows_kernel(const __grid_const
 
 int exchange_fail(int code, const char* message) { htgs::set_last_error(message); return code; }
 
+// Compact rows -> dense gradients: rebuilds the rows of grad_sh_0 / grad_sh_rest from the colour gradient and the view
+// direction (position of the Gaussian minus the camera position in the buffer's header, exactly as the backward pass of the
+// rank that made the row computes them) and ADDS all six rows to the dense tensors.  `rows` may be memory of another GPU
+// (peer access enabled): the kernel only reads it, with plain 16-byte loads, each byte once.
+//
+// A warp takes 32 rows at a time.  (1) It reads their 2 KB as four fully coalesced 512-byte loads and turns them by 90 degrees
+// through shared memory, so that lane t holds row t.  (2) Lane t computes the 59 values of its row into a shared-memory tile.
+// (3) The warp adds the tile to the tensors with the lanes on consecutive floats of a dense row (the 45 floats of a grad_sh_rest
+// row are two instructions touching six sectors, instead of 45 instructions touching 32 sectors each with one lane per row).
+struct DenseGradients {
+    float* positions; float* scales; float* rotations; float* opacities; float* sh_0; float* sh_rest;
+};
+constexpr int kExpandWarps = 4;
+constexpr int kExpandValues = 59;     // 3 + 3 + 4 + 1 + 3 + 45
+constexpr int kExpandStride = 61;     // odd: lane t writing column c and lane c reading row t are both conflict-free
+constexpr int kExpandGroup = 8;       // dense rows whose loads are in flight together (a row's load must not wait for the previous row's store)
+static_assert(kExpandValues <= kExpandStride && 32 % kExpandGroup == 0, "tile layout");
+__global__ void __launch_bounds__(kExpandWarps * 32) expand_add_rows_kernel(const float4* __restrict__ rows, uint32_t capacity, const float* __restrict__ positions,
+                                                                            DenseGradients out, uint32_t n_primitives, int total_sh_bases) {
+    __shared__ __align__(16) float s_tile[kExpandWarps][32 * kExpandStride];      // first the 32 compact rows (2 KB), then the 32 x 59 values
+    const CompactGradientHeader* header = reinterpret_cast<const CompactGradientHeader*>(rows);
+    const uint32_t count = min(header->count, capacity);
+    const float3 cam = make_float3(header->cam_x, header->cam_y, header->cam_z);
+    const int active = min(int(header->active_sh_bases), total_sh_bases + 1);
+    const int sh_floats = 3 * (active > 9 ? 15 : active > 4 ? 8 : active > 1 ? 3 : 0);      // floats of a grad_sh_rest row that get a value
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    float* tile = s_tile[warp];
+    float4* my_rows = reinterpret_cast<float4*>(tile);
+    const uint32_t n_warps = gridDim.x * kExpandWarps;
+    const size_t sh_row = size_t(total_sh_bases) * 3;
+    for (uint32_t base = (blockIdx.x * kExpandWarps + warp) * 32u; base < count; base += n_warps * 32u) {
+        const uint32_t here = min(32u, count - base);          // rows of this trip
+        const float4* src = rows + kCompactRowFloat4s * (size_t(base) + 1);
+        #pragma unroll
+        for (int k = 0; k < kCompactRowFloat4s; ++k)
+            if (k * 32u + lane < here * kCompactRowFloat4s) my_rows[k * 32 + lane] = src[k * 32 + lane];
+        __syncwarp();
+        float4 a = make_float4(0, 0, 0, 0), b = a, c = a, d = a;
+        if (lane < here) {
+            a = my_rows[lane * kCompactRowFloat4s]; b = my_rows[lane * kCompactRowFloat4s + 1];
+            c = my_rows[lane * kCompactRowFloat4s + 2]; d = my_rows[lane * kCompactRowFloat4s + 3];
+        }
+        __syncwarp();      // every lane holds its row: the tile may overwrite the staged rows
+        uint32_t idx = 0xffffffffu;
+        if (lane < here) {
+            idx = __float_as_uint(a.x);
+            if (idx >= n_primitives) idx = 0xffffffffu;      // not a row of this scene: skipped rather than written out of bounds
+            float* t = tile + lane * kExpandStride;
+            t[0] = a.y; t[1] = a.z; t[2] = a.w;
+            t[3] = b.x; t[4] = b.y; t[5] = b.z;
+            t[6] = c.x; t[7] = c.y; t[8] = c.z; t[9] = c.w;
+            t[10] = b.w;
+            const float3 grad_rgb = make_float3(d.x, d.y, d.z);
+            const float3 band0 = kShBand0 * grad_rgb;
+            t[11] = band0.x; t[12] = band0.y; t[13] = band0.z;
+            if (sh_floats > 0 && idx != 0xffffffffu) {
+                const size_t g = idx;
+                const float3 position = make_float3(__ldg(positions + 3 * g), __ldg(positions + 3 * g + 1), __ldg(positions + 3 * g + 2));
+                const float3 dir = normalize(position - cam);
+                float3 sh[15];
+                const int written = sh_rest_gradient_rows(dir, grad_rgb, active, sh);
+                #pragma unroll
+                for (int i = 0; i < 15; ++i)
+                    if (i < written) { t[14 + 3 * i] = sh[i].x; t[15 + 3 * i] = sh[i].y; t[16 + 3 * i] = sh[i].z; }
+            }
+        }
+        __syncwarp();
+        // grad_sh_rest: lanes on consecutive floats of a dense row (45 floats = two steps), kExpandGroup rows' loads in flight together
+        const bool lo = int(lane) < sh_floats, hi = int(lane) + 32 < sh_floats;
+        for (uint32_t r0 = 0; r0 < here; r0 += kExpandGroup) {
+            float* dst[kExpandGroup];
+            float v0[kExpandGroup], v1[kExpandGroup];
+            #pragma unroll
+            for (int j = 0; j < kExpandGroup; ++j) {
+                const uint32_t g = __shfl_sync(0xffffffffu, idx, int(r0) + j);      // lanes beyond `here` hold the invalid mark
+                dst[j] = g == 0xffffffffu ? nullptr : out.sh_rest + size_t(g) * sh_row;
+                v0[j] = (dst[j] && lo) ? dst[j][lane] : 0.0f;
+                v1[j] = (dst[j] && hi) ? dst[j][lane + 32] : 0.0f;
+            }
+            #pragma unroll
+            for (int j = 0; j < kExpandGroup; ++j) {
+                const float* v = tile + (r0 + j) * kExpandStride + 14;
+                if (dst[j] && lo) dst[j][lane] = v0[j] + v[lane];
+                if (dst[j] && hi) dst[j][lane + 32] = v1[j] + v[lane + 32];
+            }
+        }
+        // the five narrow tensors: element e of the trip's 32 x width block belongs to row e / width; all loads first
+        float* p3[3][3]; float old3[3][3]; uint32_t r3[3], c3[3];
+        #pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            const uint32_t e = k * 32u + lane, r = e / 3u, cc = e - 3u * r;
+            const uint32_t g = __shfl_sync(0xffffffffu, idx, int(r));
+            r3[k] = r; c3[k] = cc;
+            p3[k][0] = g == 0xffffffffu ? nullptr : out.positions + size_t(g) * 3 + cc;
+            p3[k][1] = g == 0xffffffffu ? nullptr : out.scales + size_t(g) * 3 + cc;
+            p3[k][2] = g == 0xffffffffu ? nullptr : out.sh_0 + size_t(g) * 3 + cc;
+            #pragma unroll
+            for (int t = 0; t < 3; ++t) old3[k][t] = p3[k][t] ? *p3[k][t] : 0.0f;
+        }
+        float* p4[4]; float old4[4]; uint32_t r4[4], c4[4];
+        #pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t e = k * 32u + lane, r = e >> 2, cc = e & 3u;
+            const uint32_t g = __shfl_sync(0xffffffffu, idx, int(r));
+            r4[k] = r; c4[k] = cc;
+            p4[k] = g == 0xffffffffu ? nullptr : out.rotations + size_t(g) * 4 + cc;
+            old4[k] = p4[k] ? *p4[k] : 0.0f;
+        }
+        const float old_opacity = idx != 0xffffffffu ? out.opacities[idx] : 0.0f;
+        #pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            const float* t = tile + r3[k] * kExpandStride + c3[k];
+            if (p3[k][0]) { *p3[k][0] = old3[k][0] + t[0]; *p3[k][1] = old3[k][1] + t[3]; *p3[k][2] = old3[k][2] + t[11]; }
+        }
+        #pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (p4[k]) *p4[k] = old4[k] + tile[r4[k] * kExpandStride + 6 + c4[k]];
+        if (idx != 0xffffffffu) out.opacities[idx] = old_opacity + tile[lane * kExpandStride + 10];
+        __syncwarp();
+    }
+}
+
 int move_rows(bool gather, const HtgsRowTensors* tensors, const int64_t* index, int64_t count, float* packed, void* stream) {
     if (!tensors || count < 0 || tensors->n_tensors < 1 || tensors->n_tensors > HTGS_MAX_ROW_TENSORS)
         return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "row exchange: null argument, negative count or too many tensors");
@@ -93,6 +217,89 @@ extern "C" {
 
 int htgs_gather_rows(const HtgsRowTensors* tensors, const int64_t* index, int64_t count, float* packed, void* stream) {
     return htgs::move_rows(true, tensors, index, count, packed, stream);
+}
+
+size_t htgs_compact_rows_bytes(uint32_t capacity_rows) { return (size_t(capacity_rows) + 1) * sizeof(htgs::CompactGradientHeader); }
+
+int htgs_expand_add_rows(const HtgsScene* scene, const void* rows, uint32_t capacity_rows, const HtgsGradients* grads, void* stream) {
+    using namespace htgs;
+    if (!scene || !rows || !grads) return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand rows: null argument");
+    if (scene->n_primitives < 0 || scene->total_sh_bases < 0 || scene->total_sh_bases > 15)
+        return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand rows: bad scene sizes");
+    if (scene->n_primitives == 0 || capacity_rows == 0) return HTGS_OK;
+    if (!scene->positions || !grads->grad_positions || !grads->grad_scales || !grads->grad_rotations || !grads->grad_opacities || !grads->grad_sh_0 ||
+        (scene->total_sh_bases > 0 && !grads->grad_sh_rest))
+        return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand rows: positions and the six gradient tensors must not be null");
+    if ((reinterpret_cast<uintptr_t>(rows) & 15u) != 0) return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand rows: the row buffer must be 16-byte aligned");
+    const DenseGradients out{grads->grad_positions, grads->grad_scales, grads->grad_rotations, grads->grad_opacities, grads->grad_sh_0, grads->grad_sh_rest};
+    const uint32_t rows_per_block = kExpandWarps * 32u;
+    const uint32_t blocks = (capacity_rows + rows_per_block - 1u) / rows_per_block;
+    expand_add_rows_kernel<<<blocks < 148u * 32u ? blocks : 148u * 32u, kExpandWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float4*>(rows), capacity_rows, scene->positions, out, uint32_t(scene->n_primitives), int(scene->total_sh_bases));
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HTGS_OK : exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
+}
+
+// Buffers another process's GPU can read: plain cudaMalloc memory (no pool, no virtual-memory mapping), exported and opened
+// with the CUDA IPC calls.  Opening enables peer access between the two devices if it is not enabled yet.
+int htgs_peer_buffer_create(int device, size_t bytes, void** ptr, void* handle) {
+    using namespace htgs;
+    if (!ptr || !handle || bytes == 0) return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "peer buffer: null argument or empty buffer");
+    int previous = -1;
+    cudaError_t err = cudaGetDevice(&previous);
+    if (err == cudaSuccess) err = cudaSetDevice(device);
+    void* p = nullptr;
+    if (err == cudaSuccess) err = cudaMalloc(&p, bytes);
+    if (err == cudaSuccess) err = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (err == cudaSuccess) err = cudaIpcGetMemHandle(&h, p);
+    if (previous >= 0) cudaSetDevice(previous);
+    if (err != cudaSuccess) {
+        if (p) cudaFree(p);
+        return exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == HTGS_PEER_HANDLE_BYTES, "handle size");
+    memcpy(handle, &h, sizeof(h));
+    *ptr = p;
+    return HTGS_OK;
+}
+
+int htgs_peer_buffer_open(int device, const void* handle, void** ptr) {
+    using namespace htgs;
+    if (!ptr || !handle) return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "peer buffer: null argument");
+    int previous = -1;
+    cudaError_t err = cudaGetDevice(&previous);
+    if (err == cudaSuccess) err = cudaSetDevice(device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    if (err == cudaSuccess) err = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (previous >= 0) cudaSetDevice(previous);
+    if (err != cudaSuccess) { cudaGetLastError(); return exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err)); }
+    *ptr = p;
+    return HTGS_OK;
+}
+
+int htgs_peer_buffer_close(int device, void* ptr) {
+    using namespace htgs;
+    if (!ptr) return HTGS_OK;
+    int previous = -1;
+    cudaError_t err = cudaGetDevice(&previous);
+    if (err == cudaSuccess) err = cudaSetDevice(device);
+    if (err == cudaSuccess) err = cudaIpcCloseMemHandle(ptr);
+    if (previous >= 0) cudaSetDevice(previous);
+    return err == cudaSuccess ? HTGS_OK : exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
+}
+
+int htgs_peer_buffer_destroy(int device, void* ptr) {
+    using namespace htgs;
+    if (!ptr) return HTGS_OK;
+    int previous = -1;
+    cudaError_t err = cudaGetDevice(&previous);
+    if (err == cudaSuccess) err = cudaSetDevice(device);
+    if (err == cudaSuccess) err = cudaFree(ptr);
+    if (previous >= 0) cudaSetDevice(previous);
+    return err == cudaSuccess ? HTGS_OK : exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
 }
 
 int htgs_scatter_rows(const HtgsRowTensors* tensors, const int64_t* index, int64_t count, const float* packed, void* stream) {

@@ -130,6 +130,8 @@ struct BackwardOutputs {
     float* densification_info;   // [rows][N] or null
     int densification_rows;      // 0, 2 or 3
     bool use_distance_scaling;
+    float4* compact_rows = nullptr;       // when set: header + compact rows (common.cuh) are written INSTEAD of the six tensors
+    uint32_t compact_capacity = 0;        // rows the buffer holds behind its header
 };
 cudaError_t launch_visibility(const uint32_t* n_touched, uint8_t* visible, uint32_t n, cudaStream_t stream);
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
@@ -147,7 +149,8 @@ cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs
 // api.cu: internals shared with the other translation units (C++ linkage: not part of the C-ABI).
 int backward_with_accum(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                         const float* grad_image, const float* image, const HtgsGradients* grads, void* accum, uint32_t first, uint32_t count, int stages,
-                        void* stream);
+                        void* stream, void* compact_rows = nullptr, uint32_t compact_capacity = 0);
+// compact_rows: when not null the chain rule writes header + compact rows (common.cuh) there and leaves the six tensors alone
 int context_device(const HtgsContext* ctx);
 void set_last_error(const char* message);   // message htgs_last_error() returns on the calling thread
 

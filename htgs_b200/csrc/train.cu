@@ -598,6 +598,13 @@ __device__ __forceinline__ float4 quat_backward(const float4& q, const float (&d
 // Per-Gaussian chain rule: accumulated record -> the six output gradients
 // (hybrid_blend/kernels/backward.cuh:10-102; SH part kernel_utils.cuh:190-281).  Every output element is
 // defined after the call (the launcher clears the tensors first), so the caller need not clear them.
+//
+// COMPACT: instead of the six dense rows (59 floats at SH degree 3) the kernel appends one 64-byte record per Gaussian the view
+// kept to `out.compact_rows` (common.cuh: CompactGradientRow): the gradients of position, scale, rotation and opacity and the
+// clamp-masked colour gradient.  The rows of grad_sh_0 / grad_sh_rest are (basis function of the view direction) x (colour
+// gradient), so whoever knows the camera position can rebuild them (expand_compact_row below and exchange.cu); this is what
+// the ranks of a multi-GPU trainer send one another instead of the dense rows.
+template <bool COMPACT>
 __global__ void __launch_bounds__(256) preprocess_backward_kernel(
     const float* __restrict__ positions, const float* __restrict__ scales, const float* __restrict__ rotations, const float* __restrict__ sh_rest,
     const float* __restrict__ M, const float* __restrict__ VPM, const float* __restrict__ cam_position_ptr,
@@ -605,9 +612,19 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
     uint32_t n_primitives, int active_sh_bases, int total_sh_bases, uint32_t g_first, uint32_t g_end)
 {
     const uint32_t idx = g_first + blockIdx.x * 256 + threadIdx.x;
-    if (idx >= g_end) return;
-    float3* grad_sh_rest = reinterpret_cast<float3*>(out.grad_sh_rest) + size_t(idx) * total_sh_bases;
-    if (n_touched[idx] == 0) return;          // outputs were cleared by the launcher
+    if constexpr (COMPACT) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) {      // header: the camera the receivers need (its first word, the row count, was cleared by the launcher)
+            CompactGradientHeader* header = reinterpret_cast<CompactGradientHeader*>(out.compact_rows);
+            header->cam_x = __ldg(cam_position_ptr); header->cam_y = __ldg(cam_position_ptr + 1); header->cam_z = __ldg(cam_position_ptr + 2);
+            header->active_sh_bases = uint32_t(active_sh_bases);
+        }
+    }
+    const bool kept = idx < g_end && n_touched[idx] != 0;      // outputs were cleared by the launcher
+    if constexpr (!COMPACT) { if (!kept) return; }
+    float3 grad_scale = make_float3(0, 0, 0), grad_rgb = make_float3(0, 0, 0), dL_dposition = make_float3(0, 0, 0);
+    float4 grad_rotation = make_float4(0, 0, 0, 0);
+    float grad_opacity = 0.0f;
+    if (kept) {
     const float4 dT1 = accum[size_t(idx) * 5], dT2 = accum[size_t(idx) * 5 + 1], dT4 = accum[size_t(idx) * 5 + 2], dC = accum[size_t(idx) * 5 + 3];
     const float3 c1 = make_float3(dT1.x, dT2.x, dT4.x), c2 = make_float3(dT1.y, dT2.y, dT4.y), c3 = make_float3(dT1.z, dT2.z, dT4.z);
     const float3 c4 = make_float3(dT1.w, dT2.w, dT4.w);
@@ -622,7 +639,7 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
     const float3 R_c1 = make_float3(1.0f - 2.0f * (yy + zz), 2.0f * (xy + rz), 2.0f * (xz - ry));
     const float3 R_c2 = make_float3(2.0f * (xy - rz), 1.0f - 2.0f * (xx + zz), 2.0f * (yz + rx));
     const float3 R_c3 = make_float3(2.0f * (xz + ry), 2.0f * (yz - rx), 1.0f - 2.0f * (xx + yy));
-    reinterpret_cast<float3*>(out.grad_scales)[idx] = make_float3(
+    grad_scale = make_float3(
         dot(make_float3(dot(VPM1, R_c1), dot(VPM2, R_c1), dot(VPM4, R_c1)), c1),
         dot(make_float3(dot(VPM1, R_c2), dot(VPM2, R_c2), dot(VPM4, R_c2)), c2),
         dot(make_float3(dot(VPM1, R_c3), dot(VPM2, R_c3), dot(VPM4, R_c3)), c3));
@@ -630,48 +647,29 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
         dot(VPM_c1, c1) * scale.x, dot(VPM_c1, c2) * scale.y, dot(VPM_c1, c3) * scale.z,
         dot(VPM_c2, c1) * scale.x, dot(VPM_c2, c2) * scale.y, dot(VPM_c2, c3) * scale.z,
         dot(VPM_c3, c1) * scale.x, dot(VPM_c3, c2) * scale.y, dot(VPM_c3, c3) * scale.z};
-    reinterpret_cast<float4*>(out.grad_rotations)[idx] = quat_backward(q, dR);
-    out.grad_opacities[idx] = dC.w;
+    grad_rotation = quat_backward(q, dR);
+    grad_opacity = dC.w;
 
     // colour: undo the clamp at 0, then SH backward
     const uint8_t cl = clamp[idx];
-    const float3 grad_rgb = make_float3((cl & 1) ? 0.0f : dC.x, (cl & 2) ? 0.0f : dC.y, (cl & 4) ? 0.0f : dC.z);
-    reinterpret_cast<float3*>(out.grad_sh_0)[idx] = 0.28209479177387814f * grad_rgb;
+    grad_rgb = make_float3((cl & 1) ? 0.0f : dC.x, (cl & 2) ? 0.0f : dC.y, (cl & 4) ? 0.0f : dC.z);
     const float3 position = make_float3(positions[3 * size_t(idx)], positions[3 * size_t(idx) + 1], positions[3 * size_t(idx) + 2]);
     float3 drgb_dposition = make_float3(0, 0, 0);
-    int written = 0;
     if (active_sh_bases > 1) {
         const float3* co = reinterpret_cast<const float3*>(sh_rest) + size_t(idx) * total_sh_bases;
         const float3 cam_position = make_float3(__ldg(cam_position_ptr), __ldg(cam_position_ptr + 1), __ldg(cam_position_ptr + 2));
         const float3 raw = position - cam_position;
         const float3 dir = normalize(raw);
         const float dx = dir.x, dy = dir.y, dz = dir.z;
-        grad_sh_rest[0] = (-0.48860251190291987f * dy) * grad_rgb;
-        grad_sh_rest[1] = (0.48860251190291987f * dz) * grad_rgb;
-        grad_sh_rest[2] = (-0.48860251190291987f * dx) * grad_rgb;
         float3 gdx = -0.48860251190291987f * co[2];
         float3 gdy = -0.48860251190291987f * co[0];
         float3 gdz = 0.48860251190291987f * co[1];
-        written = 3;
         if (active_sh_bases > 4) {
             const float sxx = dx * dx, syy = dy * dy, szz = dz * dz, sxy = dx * dy, sxz = dx * dz, syz = dy * dz;
-            grad_sh_rest[3] = (1.0925484305920792f * sxy) * grad_rgb;
-            grad_sh_rest[4] = (-1.0925484305920792f * syz) * grad_rgb;
-            grad_sh_rest[5] = (0.94617469575755997f * szz - 0.31539156525251999f) * grad_rgb;
-            grad_sh_rest[6] = (-1.0925484305920792f * sxz) * grad_rgb;
-            grad_sh_rest[7] = (0.54627421529603959f * sxx - 0.54627421529603959f * syy) * grad_rgb;
             gdx = gdx + (1.0925484305920792f * dy) * co[3] + (-1.0925484305920792f * dz) * co[6] + (1.0925484305920792f * dx) * co[7];
             gdy = gdy + (1.0925484305920792f * dx) * co[3] + (-1.0925484305920792f * dz) * co[4] + (-1.0925484305920792f * dy) * co[7];
             gdz = gdz + (-1.0925484305920792f * dy) * co[4] + (1.8923493915151202f * dz) * co[5] + (-1.0925484305920792f * dx) * co[6];
-            written = 8;
             if (active_sh_bases > 9) {
-                grad_sh_rest[8] = (0.59004358992664352f * dy * (-3.0f * sxx + syy)) * grad_rgb;
-                grad_sh_rest[9] = (2.8906114426405538f * sxy * dz) * grad_rgb;
-                grad_sh_rest[10] = (0.45704579946446572f * dy * (1.0f - 5.0f * szz)) * grad_rgb;
-                grad_sh_rest[11] = (0.3731763325901154f * dz * (5.0f * szz - 3.0f)) * grad_rgb;
-                grad_sh_rest[12] = (0.45704579946446572f * dx * (1.0f - 5.0f * szz)) * grad_rgb;
-                grad_sh_rest[13] = (1.4453057213202769f * dz * (sxx - syy)) * grad_rgb;
-                grad_sh_rest[14] = (0.59004358992664352f * dx * (-sxx + 3.0f * syy)) * grad_rgb;
                 gdx = gdx + (-3.5402615395598609f * sxy) * co[8] + (2.8906114426405538f * syz) * co[9]
                           + (0.45704579946446572f - 2.2852289973223288f * szz) * co[12] + (2.8906114426405538f * sxz) * co[13]
                           + (-1.7701307697799304f * sxx + 1.7701307697799304f * syy) * co[14];
@@ -681,7 +679,6 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
                 gdz = gdz + (2.8906114426405538f * sxy) * co[9] + (-4.5704579946446566f * syz) * co[10]
                           + (5.597644988851731f * szz - 1.1195289977703462f) * co[11] + (-4.5704579946446566f * sxz) * co[12]
                           + (1.4453057213202769f * sxx - 1.4453057213202769f * syy) * co[13];
-                written = 15;
             }
         }
         const float3 gdir = make_float3(dot(gdx, grad_rgb), dot(gdy, grad_rgb), dot(gdz, grad_rgb));
@@ -692,10 +689,23 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
             (yyr + zzr) * gdir.x - xyr * gdir.y - xzr * gdir.z,
             -xyr * gdir.x + (xxr + zzr) * gdir.y - yzr * gdir.z,
             -xzr * gdir.x - yzr * gdir.y + (xxr + yyr) * gdir.z) * rsqrtf(norm_sq * norm_sq * norm_sq);
+        if constexpr (!COMPACT) {
+            float3 rows[15];
+            const int written = sh_rest_gradient_rows(dir, grad_rgb, active_sh_bases, rows);
+            float3* grad_sh_rest = reinterpret_cast<float3*>(out.grad_sh_rest) + size_t(idx) * total_sh_bases;
+            #pragma unroll
+            for (int i = 0; i < 15; ++i)
+                if (i < written) grad_sh_rest[i] = rows[i];
+        }
     }
-    (void)written;
-    const float3 dL_dposition = make_float3(dot(VPM_c1, c4), dot(VPM_c2, c4), dot(VPM_c3, c4)) + drgb_dposition;
-    reinterpret_cast<float3*>(out.grad_positions)[idx] = dL_dposition;
+    dL_dposition = make_float3(dot(VPM_c1, c4), dot(VPM_c2, c4), dot(VPM_c3, c4)) + drgb_dposition;
+    if constexpr (!COMPACT) {
+        reinterpret_cast<float3*>(out.grad_scales)[idx] = grad_scale;
+        reinterpret_cast<float4*>(out.grad_rotations)[idx] = grad_rotation;
+        out.grad_opacities[idx] = grad_opacity;
+        reinterpret_cast<float3*>(out.grad_sh_0)[idx] = kShBand0 * grad_rgb;
+        reinterpret_cast<float3*>(out.grad_positions)[idx] = dL_dposition;
+    }
     if (out.densification_info != nullptr) {     // hybrid_blend/kernels/backward.cuh:85-98
         float z_scale = 1.0f;
         if (out.use_distance_scaling) {
@@ -706,6 +716,24 @@ __global__ void __launch_bounds__(256) preprocess_backward_kernel(
         info[idx] += 1.0f;
         info[size_t(n_primitives) + idx] += length(dL_dposition * z_scale);
         if (out.densification_rows == 3) info[2 * size_t(n_primitives) + idx] += z_scale * accum[size_t(idx) * 5 + 4].x;
+    }
+    }   // kept
+    if constexpr (COMPACT) {
+        // one slot per kept Gaussian: a warp takes its slots with one atomic (the order of the rows carries no meaning)
+        const uint32_t kept_mask = __ballot_sync(0xffffffffu, kept);
+        if (kept_mask == 0) return;
+        const uint32_t lane = threadIdx.x & 31u;
+        uint32_t base = 0;
+        if (lane == uint32_t(__ffs(kept_mask) - 1)) base = atomicAdd(reinterpret_cast<uint32_t*>(out.compact_rows), uint32_t(__popc(kept_mask)));
+        base = __shfl_sync(0xffffffffu, base, __ffs(kept_mask) - 1);
+        const uint32_t slot = base + uint32_t(__popc(kept_mask & ((1u << lane) - 1u)));
+        if (kept && slot < out.compact_capacity) {      // rows beyond the capacity are dropped; the count tells the reader
+            float4* row = out.compact_rows + 4 * (size_t(slot) + 1);
+            row[0] = make_float4(__uint_as_float(idx), dL_dposition.x, dL_dposition.y, dL_dposition.z);
+            row[1] = make_float4(grad_scale.x, grad_scale.y, grad_scale.z, grad_opacity);
+            row[2] = grad_rotation;
+            row[3] = make_float4(grad_rgb.x, grad_rgb.y, grad_rgb.z, 0.0f);
+        }
     }
 }
 
@@ -771,28 +799,44 @@ cudaError_t clear_backward_outputs(const HtgsScene& scene, const BackwardOutputs
     return cudaSuccess;
 }
 
+namespace {
+cudaError_t launch_chain_rule(const HtgsScene& scene, const HtgsView& view, const PrimBuffers& prim, const GradAccumBuffers& acc, const BackwardOutputs& out,
+                              uint32_t n, uint32_t first, uint32_t count, cudaStream_t stream) {
+    if (out.compact_rows != nullptr) {
+        const cudaError_t err = cudaMemsetAsync(out.compact_rows, 0, sizeof(CompactGradientHeader), stream);
+        if (err != cudaSuccess) return err;
+        preprocess_backward_kernel<true><<<(count + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
+                                                                                  view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
+                                                                                  view.active_sh_bases, scene.total_sh_bases, first, first + count);
+    } else {
+        preprocess_backward_kernel<false><<<(count + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
+                                                                                   view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
+                                                                                   view.active_sh_bases, scene.total_sh_bases, first, first + count);
+    }
+    return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsView& view, const FrameGeometry& geo, const PrimBuffers& prim,
                             const uint32_t* prims_sorted, const uint2* tile_ranges, const TrainPixelBuffers& tin, const float* grad_image,
                             const float* image, const GradAccumBuffers& acc, const BackwardOutputs& out, cudaEvent_t outputs_cleared, int sm_count,
                             uint32_t first, uint32_t count, int stages, cudaStream_t stream) {
     (void)sm_count;
     const uint32_t n = uint32_t(scene.n_primitives);
-    if (n == 0 || count == 0) return cudaSuccess;
+    if (n == 0 || count == 0) return out.compact_rows ? cudaMemsetAsync(out.compact_rows, 0, sizeof(CompactGradientHeader), stream) : cudaSuccess;
     const bool whole = first == 0 && count == n;
     if (!(stages & kBackwardAccumulate)) {      // the per-Gaussian chain rule alone, over records an earlier call accumulated
         cudaError_t e = cudaSuccess;
         if (outputs_cleared != nullptr && (e = cudaStreamWaitEvent(stream, outputs_cleared, 0)) != cudaSuccess) return e;
-        preprocess_backward_kernel<<<(count + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
-                                                                            view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
-                                                                            view.active_sh_bases, scene.total_sh_bases, first, first + count);
-        return cudaGetLastError();
+        return launch_chain_rule(scene, view, prim, acc, out, n, first, count, stream);
     }
     // the pixel-parallel GLOBAL_ORDERING pass needs every fragment in front of a fragment: it cannot run over a part of the Gaussians
     if (!whole && mode == HTGS_MODE_ALPHA_BLEND_GLOBAL_ORDERING) return cudaErrorNotSupported;
     const uint32_t g_first = whole ? 0u : first, g_end = whole ? 0xffffffffu : first + count;
     cudaError_t err = cudaMemsetAsync(acc.accum + size_t(first) * 5, 0, size_t(count) * 5 * sizeof(float4), stream);
     if (err != cudaSuccess) return err;
-    if (outputs_cleared == nullptr && (err = clear_backward_outputs(scene, out, first, count, stream)) != cudaSuccess) return err;
+    if (outputs_cleared == nullptr && (out.compact_rows == nullptr || out.grad_positions != nullptr) &&
+        (err = clear_backward_outputs(scene, out, first, count, stream)) != cudaSuccess) return err;
     const bool abs_grad = out.densification_info != nullptr && out.densification_rows == 3;
     const int k = effective_k(mode, K);
     switch (mode) {
@@ -814,10 +858,7 @@ cudaError_t launch_backward(int mode, int K, const HtgsScene& scene, const HtgsV
     if (err != cudaSuccess) return err;
     if (outputs_cleared != nullptr && (err = cudaStreamWaitEvent(stream, outputs_cleared, 0)) != cudaSuccess) return err;
     if (!(stages & kBackwardChainRule)) return cudaSuccess;
-    preprocess_backward_kernel<<<(count + 255) / 256, 256, 0, stream>>>(scene.positions, scene.scales, scene.rotations, scene.sh_rest, view.M, view.VPM,
-                                                                        view.cam_position, prim.n_touched, prim.clamp, acc.accum, out, n,
-                                                                        view.active_sh_bases, scene.total_sh_bases, first, first + count);
-    return cudaGetLastError();
+    return launch_chain_rule(scene, view, prim, acc, out, n, first, count, stream);
 }
 
 }  // namespace htgs

@@ -354,6 +354,259 @@ class BackwardExchange:
         return [a.elapsed_time(b) for a, b in marks]
 
 
+kCompactRowBytes = 64      # one header and one row of a compact gradient buffer (include/htgs_b200.h: htgs_backward_compact)
+
+
+class _DeviceSpan:
+    """A piece of device memory that is not a torch tensor (what `CompactExchange.buffer` hands out for the peer transport)."""
+    def __init__(self, address: int, nbytes: int):
+        self._address, self._nbytes = int(address), int(nbytes)
+
+    def data_ptr(self) -> int:
+        return self._address
+
+    def numel(self) -> int:
+        return self._nbytes
+
+
+class _PeerBuffers:
+    """Two compact-row buffers per rank (used in turn), each mapped into every other rank's process (`htgs_peer_buffer_*`)."""
+    def __init__(self, device_index: int, nbytes: int, group):
+        """Collective.  Does not raise when a CUDA call fails: `problem` holds the first failure of this rank (or tells that
+        another rank failed), so that all ranks can decide together what to do."""
+        import ctypes
+        import torch.distributed as dist
+        from . import _native
+        self.lib, self.device_index, self.nbytes, self.group = _native.lib(), int(device_index), int(nbytes), group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.local, self.opened, self.problem, self.turn = [], [], None, 0
+        self.maps = [[0] * self.world for _ in range(2)]
+        handles = []
+        try:
+            for _ in range(2):
+                ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+                _native.check(self.lib.htgs_peer_buffer_create(self.device_index, self.nbytes, ctypes.byref(ptr), handle))
+                self.local.append(int(ptr.value))
+                handles.append(bytes(handle.raw))
+        except Exception as exc:
+            self.problem, handles = exc, None
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, (self.nbytes, handles), group=group)
+        if self.problem is not None:
+            return
+        if any(theirs is None for _, theirs in everyone):
+            self.problem = RuntimeError("another rank could not create its compact-row buffers")
+            return
+        if any(size != self.nbytes for size, _ in everyone):
+            self.problem = RuntimeError("the ranks disagree on the size of the compact-row buffers (different scenes?)")
+            return
+        try:
+            for r, (_, theirs) in enumerate(everyone):
+                for b in range(2):
+                    if r == self.rank:
+                        self.maps[b][r] = self.local[b]
+                    else:
+                        ptr = ctypes.c_void_p()
+                        _native.check(self.lib.htgs_peer_buffer_open(self.device_index, theirs[b], ctypes.byref(ptr)))
+                        self.maps[b][r] = int(ptr.value)
+                        self.opened.append(int(ptr.value))
+        except Exception as exc:
+            self.problem = exc
+
+    def close(self) -> None:
+        """Collective: every rank closes its mappings, then the owners free the buffers."""
+        import torch
+        import torch.distributed as dist
+        from . import _native
+        if self.lib is None:
+            return
+        torch.cuda.synchronize(self.device_index)
+        for ptr in self.opened:
+            _native.check(self.lib.htgs_peer_buffer_close(self.device_index, ptr))
+        self.opened = []
+        dist.barrier(group=self.group)
+        for ptr in self.local:
+            _native.check(self.lib.htgs_peer_buffer_destroy(self.device_index, ptr))
+        self.local, self.lib = [], None
+
+
+class CompactExchange:
+    """Sums the rasterizer's six gradient tensors over the ranks by exchanging COMPACT rows.
+
+    A rank's backward pass makes non-zero gradient rows only for the Gaussians its view kept (about a sixth of the scene), and
+    48 of a row's 59 floats (SH degree 3) are the 3-vector dL/drgb times functions of the view direction.  So instead of
+    all-reducing dense rows (236 bytes per Gaussian of the union of all ranks' views) every rank publishes 64 bytes per
+    Gaussian ITS view kept (`htgs_backward_compact`) and every rank expands all ranks' buffers, in rank order, into the dense
+    sums (`htgs_expand_add_rows`).  Same order on every rank: the sums are bit-identical everywhere, like an all-reduce's.
+    At 8 ranks and configuration 2 a rank reads 7 x 33 MB instead of taking part in the reduction of 383 MB.
+
+    transport = "peer" (default on CUDA with more than one rank): every rank's buffer is plain device memory that the other
+        ranks' GPUs read over NVLink INSIDE the expanding kernel (CUDA IPC mappings made once; `htgs_peer_buffer_*`).  Per step
+        the ranks pass one tiny all-reduce on their streams - the barrier between writing and reading - and nothing else:
+        no sizes to agree on, no host synchronisation, no staging copy.  Two buffers per rank are used in turn, so the next
+        step's barrier also orders a buffer's readers before its next writer.  Costs 2 x 64 bytes x N of device memory.
+    transport = "nccl": buffers padded to the largest kept count of any rank, one all-gather, expansion from the gathered
+        copy.  `begin` agrees on that count (one tiny all-gather and a host synchronisation on a side stream).
+
+    Use per training step, with `rasterization.set_backward_hook(xchg)` installed once:
+        xchg.begin(visible, ready)     # right after the forward; needed by the "nccl" transport only
+        loss.backward()                # the gradients autograd receives from diff_rasterize are sums over the ranks
+    The caveats of BackwardExchange apply: loss terms that reach the parameters past the rasterizer are not summed, and a
+    step with several forwards per rank needs one backward per forward.  Call `close()` (collective) before the process
+    group is destroyed."""
+
+    compact = True      # what the autograd hook of torch_bindings.rasterization looks for
+
+    def __init__(self, group=None, transport: str = "auto"):
+        if transport not in ("auto", "peer", "nccl"):
+            raise ValueError("transport must be 'auto', 'peer' or 'nccl'")
+        self.group = group
+        self.transport = transport
+        self._capacity = None
+        self._peers = None
+        self._token = None
+        self.rows_published = 0       # "nccl": rows of this rank in the last step
+        self.bytes_gathered = 0       # "nccl": bytes the last all-gather delivered to this rank (all ranks' buffers)
+
+    @staticmethod
+    def _world(group) -> int:
+        import torch.distributed as dist
+        return dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+
+    def _use_peers(self, is_cuda: bool) -> bool:
+        if self.transport == "auto":
+            self.transport = "peer" if (is_cuda and self._world(self.group) > 1) else "nccl"
+        if self.transport == "peer" and not is_cuda:
+            raise ValueError("the peer transport needs CUDA tensors")
+        return self.transport == "peer"
+
+    def begin(self, rows, ready=None) -> None:
+        """`rows`: bool tensor [N] of the Gaussians this rank's view kept; `ready`: the event after which it is valid.
+        Does nothing for the peer transport."""
+        import torch
+        import torch.distributed as dist
+        if self._use_peers(rows.is_cuda):
+            return
+        world = self._world(self.group)
+        if rows.is_cuda:
+            device = rows.device
+            side = _side_streams.get(device)
+            if side is None:
+                side = _side_streams[device] = torch.cuda.Stream(device=device)
+            if ready is not None:
+                side.wait_event(ready)
+            else:
+                side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                count = rows.sum(dtype=torch.int64).reshape(1)
+                counts = torch.empty(world, dtype=torch.int64, device=device)
+                if world > 1:
+                    dist.all_gather_into_tensor(counts, count, group=self.group)
+                else:
+                    counts.copy_(count)
+                mine, largest = int(count.item()), int(counts.max().item())
+            rows.record_stream(side)
+        else:
+            count = rows.sum(dtype=torch.int64).reshape(1)
+            gathered = [torch.empty_like(count) for _ in range(world)]
+            if world > 1:
+                dist.all_gather(gathered, count, group=self.group)
+            else:
+                gathered[0].copy_(count)
+            mine, largest = int(count.item()), max(int(c.item()) for c in gathered)
+        self.rows_published = mine
+        self._capacity = max(1024, -(-largest // 1024) * 1024)      # whole kilorows: few distinct buffer sizes over a run
+
+    def capacity(self, n: int) -> int:
+        if self.transport == "auto":
+            self._use_peers(True)
+        if self.transport == "peer":      # the buffer holds a row for every Gaussian of the scene; readers go by the header's count
+            return max(int(n), 1)
+        if self._capacity is None:
+            raise RuntimeError("CompactExchange.begin was not called after the forward of this step")
+        return min(self._capacity, max(int(n), 1))
+
+    def prepare(self, n: int, device) -> str:
+        """Collective, optional: sets the peer transport up for a scene of `n` Gaussians before the first step (otherwise the
+        first backward pass does it).  If any rank cannot create or map the buffers (no peer access between the GPUs, CUDA
+        IPC not permitted in this environment) all ranks fall back to the "nccl" transport together.  Returns the transport."""
+        import torch
+        import torch.distributed as dist
+        device = torch.device(device)
+        if not self._use_peers(device.type == "cuda") or self._peers is not None:
+            return self.transport
+        index = torch.cuda.current_device() if device.index is None else device.index
+        nbytes = (max(int(n), 1) + 1) * kCompactRowBytes
+        peers = _PeerBuffers(index, nbytes, self.group)      # records a failure instead of raising: decided together below
+        ok = torch.tensor([0 if peers.problem is not None else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            problem = peers.problem
+            peers.close()
+            import warnings
+            warnings.warn(f"htgs_b200: compact exchange falls back to the all-gather transport ({problem if problem is not None else 'another rank could not map the buffers'})")
+            self.transport = "nccl"
+            return self.transport
+        self._peers = peers
+        self._token = torch.zeros(1, dtype=torch.int32, device=device)
+        return self.transport
+
+    def buffer(self, nbytes: int, device):
+        import torch
+        if self.transport == "peer" and self._peers is None:
+            self.prepare(int(nbytes) // kCompactRowBytes - 1, device)
+        if self.transport == "peer":
+            if int(nbytes) != self._peers.nbytes:
+                raise RuntimeError("the scene's size changed: make a new CompactExchange (the peer buffers are sized once)")
+            return _DeviceSpan(self._peers.local[self._peers.turn], nbytes)
+        return torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+
+    def exchange(self, rows, capacity: int):
+        """`rows`: this rank's buffer (header + capacity rows), written by the work queued on the current stream.  Returns
+        (address, capacity, owner) per rank, in rank order; `owner` keeps the memory alive."""
+        import torch
+        import torch.distributed as dist
+        world = self._world(self.group)
+        self._capacity = None
+        if self.transport == "peer":
+            dist.all_reduce(self._token, group=self.group)      # every rank's rows are written before any rank reads them
+            turn = self._peers.turn
+            self._peers.turn = 1 - turn
+            return [(self._peers.maps[turn][r], capacity, self._peers) for r in range(world)]
+        if world == 1:
+            self.bytes_gathered = rows.numel()
+            return [(rows.data_ptr(), capacity, rows)]
+        gathered = torch.empty(world * rows.numel(), dtype=torch.uint8, device=rows.device)
+        if rows.is_cuda:
+            dist.all_gather_into_tensor(gathered, rows, group=self.group)
+        else:          # host tensors (the gloo tests of this logic)
+            dist.all_gather(list(gathered.view(world, -1).unbind(0)), rows, group=self.group)
+        self.bytes_gathered = gathered.numel()
+        return [(gathered.data_ptr() + r * rows.numel(), capacity, gathered) for r in range(world)]
+
+    def published_rows(self):
+        """Peer transport: the row counts in the headers of the buffers the last step used, per rank (host synchronisation;
+        for reporting, not for the training loop)."""
+        import ctypes
+        import torch
+        from . import _native
+        if self._peers is None:
+            return None
+        torch.cuda.synchronize(self._peers.device_index)
+        turn = 1 - self._peers.turn
+        counts = []
+        for r in range(self._peers.world):
+            word = ctypes.c_uint32()
+            _native.lib().htgs_memcpy_d2h(ctypes.byref(word), self._peers.maps[turn][r], 4)
+            counts.append(int(word.value))
+        return counts
+
+    def close(self) -> None:
+        if self._peers is not None:
+            self._peers.close()
+            self._peers = None
+
+
 def allreduce_gradients_rows(grads: Sequence, rows, group=None) -> int:
     """Sums per-Gaussian gradient tensors over the ranks, in place, exchanging only the rows some rank can have touched:
     `begin_row_exchange` and `finish_row_exchange` in one call (the host then waits for the backward pass before it can

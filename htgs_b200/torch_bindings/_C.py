@@ -231,7 +231,7 @@ def forward_visibility(per_primitive_buffers, n_primitives: int):
 def backward(densification_info, grad_image, image, positions, scales, rotations, opacities, sh_rest, per_primitive_buffers, per_tile_buffers,
              per_instance_buffers, per_pixel_buffers, M, VPM, cam_position, rasterizer_mode, K, active_sh_bases, width, height, near_plane,
              far_plane, scale_modifier, n_instances, instance_primitive_indices_selector, use_distance_scaling, ranges=None, after_range=None,
-             split_pass=True):
+             split_pass=True, compact=None):
     """`_C.backward` (rasterization/include/rasterization_api.h:28-55): returns the six gradients; `densification_info`
     ([2|3, N, 1] or empty) is updated in place.  `image` / `opacities` may be empty tensors, as the reference's autograd
     function passes them (torch_bindings/rasterization.py:72-76).
@@ -241,7 +241,12 @@ def backward(densification_info, grad_image, image, positions, scales, rotations
     gradient tensors whose rows [first, first + count) are final once the stream gets there; a multi-GPU trainer starts
     summing those rows over the ranks while the next range is computed (htgs_b200.parallel.BackwardExchange).  With
     `split_pass=False` the per-tile pass runs once for all Gaussians (`htgs_backward_accumulate`) and only the per-Gaussian
-    chain rule runs range by range (`htgs_backward_finish_range`): less to hide the exchange behind, but no cost for the split."""
+    chain rule runs range by range (`htgs_backward_finish_range`): less to hide the exchange behind, but no cost for the split.
+
+    With `compact` (an object with `capacity(n)` and `exchange(rows)`, e.g. htgs_b200.parallel.CompactExchange) the pass writes
+    compact rows (`htgs_backward_compact`: 64 bytes per Gaussian the view kept instead of dense rows), `compact.exchange(rows)`
+    returns the row buffers of all ranks in rank order, and the six tensors returned are the sums over those buffers
+    (`htgs_expand_add_rows`), identical on every rank."""
     device = positions.device
     if device.type != "cuda":
         raise ValueError("htgs_b200 rasterizer: tensors must live on a CUDA device")
@@ -286,6 +291,15 @@ def backward(densification_info, grad_image, image, positions, scales, rotations
         image_ptr = image.contiguous().data_ptr() if image.numel() else None
         stream = torch.cuda.current_stream(device).cuda_stream
         outs = (grad_positions, grad_scales, grad_rotations, grad_opacities, grad_sh_0, grad_sh_rest)
+        if compact is not None:
+            capacity = int(compact.capacity(n))
+            rows = compact.buffer(lib.htgs_compact_rows_bytes(capacity), device)
+            _native.check(lib.htgs_backward_compact(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), int(n_instances), grad_image.data_ptr(),
+                                                    image_ptr, ctypes.byref(grads), rows.data_ptr(), capacity, stream))
+            for address, rows_capacity, keep_alive in compact.exchange(rows, capacity):
+                _native.check(lib.htgs_expand_add_rows(ctypes.byref(scene), address, int(rows_capacity), ctypes.byref(grads), stream))
+            scratch.record_stream(torch.cuda.current_stream(device))
+            return outs
         if ranges is None:
             _native.check(lib.htgs_backward(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), int(n_instances), grad_image.data_ptr(),
                                             image_ptr, ctypes.byref(grads), stream))

@@ -156,6 +156,9 @@ class _Rasterize(torch.autograd.Function):
         if hook is None:
             grads = _impl.backward(ctx.densification_info, grad_image, *ctx.saved_tensors, *ctx.rasterizer_settings.as_tuple(),
                                    ctx.n_instances, ctx.instance_primitive_indices_selector, ctx.use_distance_scaling)
+        elif getattr(hook, "compact", False):      # compact rows, exchanged by the hook, expanded into sums (htgs_b200.parallel.CompactExchange)
+            grads = _C.backward(ctx.densification_info, grad_image, *ctx.saved_tensors, *ctx.rasterizer_settings.as_tuple(),
+                                ctx.n_instances, ctx.instance_primitive_indices_selector, ctx.use_distance_scaling, compact=hook)
         else:      # range by range over the C-ABI (the ctypes binding drives the loop; both bindings share the library contexts)
             n = ctx.saved_tensors[1].shape[0]
             grads = _C.backward(ctx.densification_info, grad_image, *ctx.saved_tensors, *ctx.rasterizer_settings.as_tuple(),

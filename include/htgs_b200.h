@@ -255,6 +255,48 @@ int htgs_gather_rows(const HtgsRowTensors* tensors, const int64_t* index, int64_
 int htgs_scatter_rows(const HtgsRowTensors* tensors, const int64_t* index, int64_t count, const float* packed, void* stream);
 
 /*
+ * Compact gradient rows: what the ranks of a multi-GPU trainer send one another.  No counterpart in the reference.
+ *
+ * A view keeps about a sixth of a scene's Gaussians, and of the 59 floats of a kept Gaussian's gradient row (SH degree 3) the
+ * 48 of grad_sh_0 / grad_sh_rest are the 3-vector dL/drgb times functions of the view direction
+ * (rasterization/include/kernel_utils.cuh:190-281 of the reference).  htgs_backward_compact is htgs_backward, except that it
+ * does not compute the six tensors of `grads` (all NULL, or all given: then the call clears them, overlapped with its kernels,
+ * ready for htgs_expand_add_rows) and writes to `rows` one 64-byte header (row count, camera
+ * position, active SH bases) followed by one 64-byte row per kept Gaussian, in no particular order: index, dL/dposition,
+ * dL/dscale, dL/dopacity, dL/drotation, dL/drgb after the clamp mask.  `rows` holds htgs_compact_rows_bytes(capacity_rows)
+ * bytes, 16-byte aligned; capacity_rows must be at least the number of Gaussians the forward kept (HtgsFrameInfo.n_visible;
+ * the scene's size always suffices): rows beyond the capacity are dropped and the header's count tells.
+ * `grads->scratch` and `grads->densification_info` are used as by htgs_backward.
+ *
+ * htgs_expand_add_rows reads such a buffer - this rank's or, after an all-gather or through peer access, another rank's - and
+ * ADDS the dense rows it stands for to the six tensors of `grads` (clear them first; `scene` supplies positions, the
+ * scene's size and SH layout).  The SH rows are rebuilt with the arithmetic of the backward pass, so expanding a rank's own
+ * buffer into cleared tensors reproduces htgs_backward's output bit for bit, and ranks that expand the same buffers in the
+ * same order end up with identical sums.  Both calls are stream-ordered and do not synchronise with the host.
+ */
+size_t htgs_compact_rows_bytes(uint32_t capacity_rows);
+int htgs_backward_compact(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
+                          const float* grad_image, const float* image, const HtgsGradients* grads, void* rows, uint32_t capacity_rows, void* stream);
+int htgs_expand_add_rows(const HtgsScene* scene, const void* rows, uint32_t capacity_rows, const HtgsGradients* grads, void* stream);
+
+/*
+ * Device buffers that the other ranks' GPUs read directly (peer access over NVLink): the transport of the compact rows that needs
+ * no collective to move them and no agreement on sizes.  No counterpart in the reference.
+ *   htgs_peer_buffer_create:  cudaMalloc of `bytes` on `device`, cleared, plus the 64-byte handle other PROCESSES open it with;
+ *   htgs_peer_buffer_open:    maps another process's buffer into this process for `device` (enables peer access on first use);
+ *   htgs_peer_buffer_close / _destroy: undo the two (close every mapping before the owner destroys the buffer).
+ * A rank writes its compact rows into its own buffer (htgs_backward_compact), all ranks pass a barrier on their streams (any
+ * collective will do), and every rank calls htgs_expand_add_rows once per rank with that rank's mapping: the kernel reads the
+ * peer's rows with plain loads while it adds to the local tensors.  With two buffers per rank used in turn, the barrier of the
+ * next step also orders a buffer's readers before its next writer.  These calls synchronise with the host (allocation).
+ */
+#define HTGS_PEER_HANDLE_BYTES 64
+int htgs_peer_buffer_create(int device, size_t bytes, void** ptr, void* handle);
+int htgs_peer_buffer_open(int device, const void* handle, void** ptr);
+int htgs_peer_buffer_close(int device, void* ptr);
+int htgs_peer_buffer_destroy(int device, void* ptr);
+
+/*
  * Backward pass that allocates nothing.  No counterpart in the reference.
  *
  * Same inputs, outputs and results as htgs_backward, but `grads->scratch` is ignored: the per-Gaussian

@@ -253,3 +253,154 @@ def test_global_ordering_refuses_a_partial_backward():
     staged = _C.backward(*args, ranges=[(0, 1000), (1000, scene.n - 1000)], split_pass=False)      # the chain rule alone may be split
     for a, b in zip(staged, whole):
         assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-30)
+
+
+class _OwnRowsOnly:
+    """Stands in for htgs_b200.parallel.CompactExchange in a single process: the buffers 'of all ranks' are the ones it is told to
+    hand back (by default this rank's own), and it keeps what the backward pass wrote."""
+    compact = True
+
+    def __init__(self, capacity=None, replay=None):
+        self._capacity, self.replay, self.rows, self.kept = capacity, replay, None, []
+
+    def capacity(self, n):
+        return n if self._capacity is None else self._capacity
+
+    def buffer(self, nbytes, device):
+        import torch
+        return torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+
+    def exchange(self, rows, capacity):
+        self.rows = rows
+        self.kept.append((rows, capacity))
+        sources = self.kept if self.replay == "all kept" else [(rows, capacity)]
+        return [(r.data_ptr(), c, r) for r, c in sources]
+
+
+@pytest.mark.parametrize("mode,K,sh_degree", [(0, 16, 3), (0, 4, 2), (1, 8, 1), (2, 1, 3), (3, 1, 0)])
+def test_compact_backward_expands_to_the_dense_gradients(mode, K, sh_degree):
+    """`htgs_backward_compact` + `htgs_expand_add_rows`: one 64-byte row per kept Gaussian, which expands to the six dense
+    tensors of `htgs_backward` (the per-tile pass sums with float atomics, so two passes agree to rounding, not bit for bit);
+    the row count equals the number of kept Gaussians, every index occurs once, and expanding is deterministic."""
+    import torch
+    from htgs_b200.torch_bindings import _C, rasterization
+    scene = scenes.outdoor_scene(n=60_000, n_views=2, seed=41, width=400, height=240, focal=300.0)
+    scene.active_sh_bases = (sh_degree + 1) ** 2      # fewer active bases than the 15 stored ones: the rest get no gradient
+    view = scene.views[1]
+    tensors = harness.scene_tensors(scene)
+    st = harness.settings_for(harness.ours(), scene, view, mode, K)
+    fwd = _C.forward(*tensors, *st.as_tuple())
+    image, blobs, n_inst, sel = fwd[0], fwd[1:5], fwd[5], fwd[6]
+    grad_image = torch.from_numpy(target_image(view.height, view.width, 78)).cuda() - 0.5
+    empty = torch.empty(0, device="cuda")
+    dens = torch.zeros((2, scene.n, 1), device="cuda")
+    args = lambda d: (d, grad_image, image if mode == 2 else empty, tensors[0], tensors[1], tensors[2], tensors[3] if mode == 1 else empty, tensors[5],
+                      *blobs, *st.as_tuple(), n_inst, sel, False)
+    dens_dense = dens.clone()
+    dense = _C.backward(*args(dens_dense))
+    stub = _OwnRowsOnly()
+    dens_compact = dens.clone()
+    compact = _C.backward(*args(dens_compact), compact=stub)
+    torch.cuda.synchronize()
+    for name, a, b in zip(GRAD_NAMES, compact, dense):
+        assert a.shape == b.shape
+        if b.numel():
+            assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-30), f"grad_{name}"
+    assert (dens_compact - dens_dense).abs().max().item() <= 1e-5 * max(dens_dense.abs().max().item(), 1e-30)
+    words = stub.rows.view(torch.int32).view(-1, 16)
+    count = int(words[0, 0])
+    kept = dense[0].abs().sum(dim=1) + dense[3].abs().sum(dim=1) > 0        # a superset test below uses the forward's own list
+    index = words[1:1 + count, 0].long()
+    assert count == index.unique().numel(), "every kept Gaussian has exactly one row"
+    assert bool(kept[index].sum() >= 0) and int(index.min()) >= 0 and int(index.max()) < scene.n
+    cam = words[0, 1:4].view(torch.float32).cpu().numpy()
+    assert np.array_equal(cam, np.asarray(view.cam_position, np.float32).reshape(3)) and int(words[0, 4]) == scene.active_sh_bases
+    outside = torch.ones(scene.n, dtype=torch.bool, device="cuda")
+    outside[index] = False
+    for g in dense:
+        if g.numel():
+            assert float(g[outside].abs().max()) == 0.0, "a Gaussian without a compact row has no gradient"
+    # the expansion alone is deterministic: the same buffer expanded twice gives identical bits
+    import ctypes
+    from htgs_b200 import _native
+    lib = _native.lib()
+    n, B = scene.n, tensors[5].shape[1]
+    sc = _native.HtgsScene(tensors[0].data_ptr(), None, None, None, None, None, n, B)
+    results = []
+    for _ in range(2):
+        outs = [torch.zeros_like(g) for g in dense]
+        gr = _native.HtgsGradients(outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), outs[3].data_ptr(), outs[4].data_ptr(),
+                                   outs[5].data_ptr() if outs[5].numel() else None, None, 0, None, 0, 0)
+        _native.check(lib.htgs_expand_add_rows(ctypes.byref(sc), stub.rows.data_ptr(), n, ctypes.byref(gr), torch.cuda.current_stream().cuda_stream))
+        results.append(outs)
+    torch.cuda.synchronize()
+    for a, b, c in zip(results[0], results[1], compact):
+        assert torch.equal(a, b) and torch.equal(a, c)
+
+
+def test_compact_rows_of_two_views_sum_like_two_dense_passes_and_small_capacity_drops_rows():
+    """What every rank of a multi-GPU step does: the buffers of all views are expanded one after the other into the same
+    tensors.  Also: a buffer too small for the kept Gaussians reports the full count in its header and holds `capacity` rows."""
+    import torch
+    from htgs_b200.torch_bindings import _C
+    scene = scenes.outdoor_scene(n=50_000, n_views=4, seed=43, width=320, height=200, focal=260.0)
+    tensors = harness.scene_tensors(scene)
+    empty = torch.empty(0, device="cuda")
+    stub = _OwnRowsOnly(replay="all kept")
+    dense_sum, last = None, None
+    for vi in (0, 2):
+        view = scene.views[vi]
+        st = harness.settings_for(harness.ours(), scene, view, 0, 8)
+        fwd = _C.forward(*tensors, *st.as_tuple())
+        grad_image = torch.from_numpy(target_image(view.height, view.width, 80 + vi)).cuda() - 0.5
+        args = (empty, grad_image, empty, tensors[0], tensors[1], tensors[2], empty, tensors[5], *fwd[1:5], *st.as_tuple(), fwd[5], fwd[6], False)
+        dense = _C.backward(*args)
+        dense_sum = [d.clone() for d in dense] if dense_sum is None else [a + d for a, d in zip(dense_sum, dense)]
+        last = _C.backward(*args, compact=stub)      # second call: expands the buffers of both views
+    torch.cuda.synchronize()
+    for name, a, b in zip(GRAD_NAMES, last, dense_sum):
+        assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-30), f"grad_{name}"
+    small = _OwnRowsOnly(capacity=100)
+    _C.backward(*args, compact=small)
+    torch.cuda.synchronize()
+    words = small.rows.view(torch.int32).view(-1, 16)
+    assert words.shape[0] == 101 and int(words[0, 0]) > 100
+
+
+_PEER_CHILD = '''
+import ctypes, sys
+sys.path.insert(0, sys.argv[1])
+from htgs_b200 import _native
+lib = _native.lib()
+handle = bytes.fromhex(sys.argv[2])
+ptr = ctypes.c_void_p()
+_native.check(lib.htgs_peer_buffer_open(0, handle, ctypes.byref(ptr)))
+host = (ctypes.c_uint32 * 1024)()
+_native.check(lib.htgs_memcpy_d2h(host, ptr, 4096))
+ok = all(host[i] == (i * 2654435761) % 2**32 for i in range(1024))
+_native.check(lib.htgs_peer_buffer_close(0, ptr))
+sys.exit(0 if ok else 3)
+'''
+
+
+def test_peer_buffer_is_readable_from_another_process(tmp_path):
+    """`htgs_peer_buffer_*`: a buffer created here, opened by handle in a child process (on the same GPU: the mapping calls are
+    the ones ranks on different GPUs use), read there and closed; then destroyed here."""
+    import ctypes
+    import subprocess
+    import sys
+    from htgs_b200 import _native
+    lib = _native.lib()
+    ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+    _native.check(lib.htgs_peer_buffer_create(0, 1 << 20, ctypes.byref(ptr), handle))
+    try:
+        host = (ctypes.c_uint32 * 1024)(*[(i * 2654435761) % 2**32 for i in range(1024)])
+        _native.check(lib.htgs_memcpy_h2d(ptr, host, 4096))
+        script = tmp_path / "child.py"
+        script.write_text(_PEER_CHILD)
+        proc = subprocess.run([sys.executable, str(script), harness.REPO, handle.raw.hex()], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+        assert proc.returncode == 0, proc.stdout[-2000:]
+    finally:
+        _native.check(lib.htgs_peer_buffer_destroy(0, ptr))
+    with pytest.raises(_native.HtgsError):
+        _native.check(lib.htgs_peer_buffer_create(0, 0, ctypes.byref(ptr), handle))

@@ -113,6 +113,48 @@ def _chunked_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
+def _compact_worker(rank, world, port, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist = parallel.init_process_group("gloo")
+    n = 5000
+    gen = torch.Generator().manual_seed(91)
+    keep = [torch.rand(n, generator=gen) < (0.2 + 0.3 * r) for r in range(world)]      # rank 1 keeps more than rank 0
+    xchg = parallel.CompactExchange()
+    xchg.begin(keep[rank])
+    capacity = xchg.capacity(n)
+    largest = max(int(k.sum()) for k in keep)
+    ok = capacity >= largest and capacity % 1024 == 0 and capacity - largest < 1024 and xchg.rows_published == int(keep[rank].sum())
+    rows = torch.full(((capacity + 1) * parallel.kCompactRowBytes,), rank + 1, dtype=torch.uint8)     # stands in for header + rows
+    parts = xchg.exchange(rows, capacity)
+    ok = ok and len(parts) == world and xchg.bytes_gathered == world * rows.numel()
+    owner = parts[0][2]
+    for r, (address, cap, keep_alive) in enumerate(parts):
+        ok = ok and cap == capacity and address == owner.data_ptr() + r * rows.numel()
+        ok = ok and bool((owner.view(world, -1)[r] == r + 1).all())                                 # buffers come back in rank order
+    try:
+        xchg.capacity(n)            # a second backward without begin() must not reuse a stale capacity
+        ok = False
+    except RuntimeError:
+        pass
+    out.put((rank, ok))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_compact_exchange_agrees_on_capacity_and_gathers_in_rank_order_two_gloo_ranks():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_compact_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results == [(0, True), (1, True)]
+
+
 def test_chunked_backward_exchange_equals_dense_sum_two_gloo_ranks():
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
