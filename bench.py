@@ -60,6 +60,7 @@ def parse_args():
                          "dense sums, reading the peers' buffers over NVLink inside the kernel (default; compact-nccl: through one all-gather instead); rows = the gradient rows of Gaussians some rank kept, summed after the backward; "
                          "overlap = the chain rule (optionally the whole backward pass) runs in ranges of Gaussians and each finished range's rows are summed "
                          "while the next is computed; dense = the dense tensors, after the backward")
+    ap.add_argument("--exchange-single-rank", action="store_true", help="train at N = 1 with --exchange compact: run the exchange's machinery anyway (its local cost; what the ncu summaries of its kernels use)")
     ap.add_argument("--exchange-chunks", type=int, default=4, help="ranges of Gaussians the backward pass is split into for --exchange overlap")
     ap.add_argument("--exchange-split-pass", action="store_true", help="--exchange overlap: split the per-tile pass along the ranges too (default: only the per-Gaussian chain rule)")
     ap.add_argument("--reference-kind", default="auto", choices=["auto", "cuda", "cpu"])
@@ -196,7 +197,8 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
 
     # Exchange: this library's arm sums only the gradient rows of Gaussians some rank's view kept (the others are zero on
     # every rank); the reference has no multi-GPU path and no such list, its arm all-reduces the dense tensors.
-    sparse = dist is not None and not is_reference and args.exchange in ("rows", "overlap", "compact", "compact-nccl")
+    sparse = not is_reference and ((dist is not None and args.exchange in ("rows", "overlap", "compact", "compact-nccl")) or
+                                   (dist is None and args.exchange_single_rank and args.exchange in ("compact", "compact-nccl")))
     overlap = sparse and args.exchange == "overlap"
     compact = sparse and args.exchange in ("compact", "compact-nccl")
     xchg = None

@@ -182,6 +182,26 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_add_rows_kernel(cons
     }
 }
 
+// Copies a compact-row buffer (header + the rows its header counts, at most `capacity`) with 16-byte loads and stores, every
+// thread with several loads in flight.  `src` is typically another GPU's buffer: a rank pulls the other ranks' buffers into
+// local memory one after the other, each rank starting with a different peer, so that at any time every GPU's memory is read by
+// one other GPU instead of by all of them.
+constexpr int kCopyInFlight = 8;
+__global__ void __launch_bounds__(256) copy_rows_kernel(const float4* __restrict__ src, float4* __restrict__ dst, uint32_t capacity) {
+    const CompactGradientHeader* header = reinterpret_cast<const CompactGradientHeader*>(src);
+    const size_t n4 = (size_t(min(header->count, capacity)) + 1) * kCompactRowFloat4s;      // header included
+    const size_t stride = size_t(gridDim.x) * 256;
+    for (size_t i = size_t(blockIdx.x) * 256 + threadIdx.x; i < n4; i += stride * kCopyInFlight) {
+        float4 v[kCopyInFlight];
+        #pragma unroll
+        for (int k = 0; k < kCopyInFlight; ++k)
+            if (i + k * stride < n4) v[k] = src[i + k * stride];
+        #pragma unroll
+        for (int k = 0; k < kCopyInFlight; ++k)
+            if (i + k * stride < n4) dst[i + k * stride] = v[k];
+    }
+}
+
 int move_rows(bool gather, const HtgsRowTensors* tensors, const int64_t* index, int64_t count, float* packed, void* stream) {
     if (!tensors || count < 0 || tensors->n_tensors < 1 || tensors->n_tensors > HTGS_MAX_ROW_TENSORS)
         return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "row exchange: null argument, negative count or too many tensors");
@@ -236,6 +256,16 @@ int htgs_expand_add_rows(const HtgsScene* scene, const void* rows, uint32_t capa
     const uint32_t blocks = (capacity_rows + rows_per_block - 1u) / rows_per_block;
     expand_add_rows_kernel<<<blocks < 148u * 32u ? blocks : 148u * 32u, kExpandWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const float4*>(rows), capacity_rows, scene->positions, out, uint32_t(scene->n_primitives), int(scene->total_sh_bases));
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HTGS_OK : exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
+}
+
+int htgs_copy_rows(void* dst, const void* src, uint32_t capacity_rows, void* stream) {
+    using namespace htgs;
+    if (!dst || !src) return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "copy rows: null argument");
+    if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15u) != 0)
+        return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "copy rows: the buffers must be 16-byte aligned");
+    copy_rows_kernel<<<148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const float4*>(src), static_cast<float4*>(dst), capacity_rows);
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? HTGS_OK : exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
 }

@@ -465,6 +465,8 @@ class CompactExchange:
         self._capacity = None
         self._peers = None
         self._token = None
+        self._staging = None
+        self.always_stage = False     # tests: take the copy-then-expand path with two ranks too
         self.rows_published = 0       # "nccl": rows of this rank in the last step
         self.bytes_gathered = 0       # "nccl": bytes the last all-gather delivered to this rank (all ranks' buffers)
 
@@ -474,6 +476,8 @@ class CompactExchange:
         return dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
 
     def _use_peers(self, is_cuda: bool) -> bool:
+        if self._world(self.group) == 1:      # a single rank expands its own buffer: nothing to map
+            self.transport = "nccl"
         if self.transport == "auto":
             self.transport = "peer" if (is_cuda and self._world(self.group) > 1) else "nccl"
         if self.transport == "peer" and not is_cuda:
@@ -572,7 +576,23 @@ class CompactExchange:
             dist.all_reduce(self._token, group=self.group)      # every rank's rows are written before any rank reads them
             turn = self._peers.turn
             self._peers.turn = 1 - turn
-            return [(self._peers.maps[turn][r], capacity, self._peers) for r in range(world)]
+            if world == 2 and not self.always_stage:      # one peer: the expanding kernel reads its buffer directly
+                return [(self._peers.maps[turn][r], capacity, self._peers) for r in range(world)]
+            # More peers: pull their buffers into local memory first, this rank starting with its right-hand neighbour, so that
+            # at any time every GPU is read by ONE other GPU.  (Expanding straight from the mappings would have all ranks read
+            # rank 0's buffer at once, then rank 1's, ...: the order of the sums has to be the same everywhere.)
+            import ctypes
+            from . import _native
+            lib, rank, nbytes = _native.lib(), self._peers.rank, self._peers.nbytes
+            if self._staging is None or self._staging.numel() != (world - 1) * nbytes:
+                self._staging = torch.empty((world - 1) * nbytes, dtype=torch.uint8, device=self._token.device)
+            stream = torch.cuda.current_stream(self._token.device).cuda_stream
+            local = {rank: self._peers.maps[turn][rank]}
+            for k in range(1, world):
+                src = (rank + k) % world
+                local[src] = self._staging.data_ptr() + (k - 1) * nbytes
+                _native.check(lib.htgs_copy_rows(local[src], self._peers.maps[turn][src], int(capacity), stream))
+            return [(local[r], capacity, self._staging) for r in range(world)]
         if world == 1:
             self.bytes_gathered = rows.numel()
             return [(rows.data_ptr(), capacity, rows)]
@@ -605,6 +625,7 @@ class CompactExchange:
         if self._peers is not None:
             self._peers.close()
             self._peers = None
+        self._staging = None
 
 
 def allreduce_gradients_rows(grads: Sequence, rows, group=None) -> int:

@@ -192,9 +192,11 @@ def fast_rasterize(positions, scales, rotations, opacities, sh_0, sh_rest, setti
 def set_max_weights_tail_credit(enable: bool) -> None:
     """HYBRID_BLEND `update_max_weights` only.  The reference's kernel source walks every tile's list a second time and
     credits `alpha * tail weight` to each fragment (hybrid_blend/kernels/update_max_weights.cuh:170-210), but the extension
-    built from it with nvcc 12.9 for sm_100a never does (a Gaussian that only lands in the tail keeps weight 0; the same
-    source compiled without device-code optimisation does credit it).  The default (False) reproduces the extension's
-    output bit for bit; True gives what the source describes.  No counterpart in the reference."""
+    built from it never runs that kernel: the function template that picks the kernel for K has the same name and signature in
+    hybrid_blend/update_max_weights.cu:15-28 and alpha_blend_first_k/update_max_weights.cu:15-28, the linker keeps one of the
+    two definitions, and HYBRID_BLEND ends up launching FIRST_K's kernel, which credits K-buffer weights only (a Gaussian that
+    only lands in the tail keeps weight 0).  The default (False) reproduces the extension's output bit for bit; True gives what
+    the source describes.  No counterpart in the reference."""
     _impl.set_max_weights_tail_credit(bool(enable))
 
 

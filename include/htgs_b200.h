@@ -275,6 +275,9 @@ int htgs_scatter_rows(const HtgsRowTensors* tensors, const int64_t* index, int64
  * same order end up with identical sums.  Both calls are stream-ordered and do not synchronise with the host.
  */
 size_t htgs_compact_rows_bytes(uint32_t capacity_rows);
+/* Copies a compact-row buffer - header and the rows it counts, at most capacity_rows - from `src`, which may be another GPU's
+ * buffer (htgs_peer_buffer_open), to `dst` (htgs_compact_rows_bytes(capacity_rows) bytes).  Stream-ordered. */
+int htgs_copy_rows(void* dst, const void* src, uint32_t capacity_rows, void* stream);
 int htgs_backward_compact(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                           const float* grad_image, const float* image, const HtgsGradients* grads, void* rows, uint32_t capacity_rows, void* stream);
 int htgs_expand_add_rows(const HtgsScene* scene, const void* rows, uint32_t capacity_rows, const HtgsGradients* grads, void* stream);
@@ -286,9 +289,12 @@ int htgs_expand_add_rows(const HtgsScene* scene, const void* rows, uint32_t capa
  *   htgs_peer_buffer_open:    maps another process's buffer into this process for `device` (enables peer access on first use);
  *   htgs_peer_buffer_close / _destroy: undo the two (close every mapping before the owner destroys the buffer).
  * A rank writes its compact rows into its own buffer (htgs_backward_compact), all ranks pass a barrier on their streams (any
- * collective will do), and every rank calls htgs_expand_add_rows once per rank with that rank's mapping: the kernel reads the
- * peer's rows with plain loads while it adds to the local tensors.  With two buffers per rank used in turn, the barrier of the
- * next step also orders a buffer's readers before its next writer.  These calls synchronise with the host (allocation).
+ * collective will do), and every rank reads every other rank's buffer through its mapping, with plain loads: either
+ * htgs_expand_add_rows directly on the mapping (fine for two ranks), or htgs_copy_rows into local memory first, each rank
+ * starting with a different peer, and htgs_expand_add_rows on the copies.  The second form keeps every GPU's memory read by one
+ * peer at a time; with the first, all ranks expand rank 0's buffer at the same moment (the sums must be formed in one order on
+ * all ranks) and queue on rank 0's links.  With two buffers per rank used in turn, the barrier of the next step also orders a
+ * buffer's readers before its next writer.  create / open / close / destroy synchronise with the host (allocation).
  */
 #define HTGS_PEER_HANDLE_BYTES 64
 int htgs_peer_buffer_create(int device, size_t bytes, void** ptr, void* handle);

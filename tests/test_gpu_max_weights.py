@@ -2,9 +2,11 @@
 
 The result is a maximum over pixels, independent of evaluation order, so every mode must match the reference extension bit
 for bit.  HYBRID_BLEND has two behaviours.  The reference's kernel SOURCE credits `alpha * tail_weight` to every fragment in
-a second walk over the tile list (hybrid_blend/kernels/update_max_weights.cuh:170-210); the EXTENSION built from it with
-nvcc 12.9 for sm_100a and the reference's own flags never does (a Gaussian that only ever lands in the tail keeps weight 0),
-while the same source compiled without device-code optimisation does (`oracle/umw_probe.cu`, run below).  The default of
+a second walk over the tile list (hybrid_blend/kernels/update_max_weights.cuh:170-210); the EXTENSION built from it never
+does (a Gaussian that only ever lands in the tail keeps weight 0): the template that picks the kernel for K is defined with
+the same name and signature for HYBRID and for FIRST_K (hybrid_blend/update_max_weights.cu:15-28,
+alpha_blend_first_k/update_max_weights.cu:15-28), the link keeps one definition, and HYBRID launches FIRST_K's kernel
+(`oracle/umw_probe.cu` links the reference's host function alone and beside FIRST_K's, in both orders; run below).  The default of
 this library reproduces the extension (bit-exact, tested against golden vectors and the live reference); with
 `set_max_weights_tail_credit(True)` it does what the source describes, which is what the CPU oracle restates: then the
 result is >= the extension's, equal to the oracle's, and bounded from above by the largest alpha of each Gaussian."""

@@ -50,7 +50,8 @@ def _worker(rank, world, port, transport, out):
         return [l.grad for l in leaves]
 
     rasterization.track_training_visibility(True)
-    xchg = parallel.CompactExchange(transport=transport)
+    xchg = parallel.CompactExchange(transport="peer" if transport == "peer-staged" else transport)
+    xchg.always_stage = transport == "peer-staged"      # the path more than two ranks take: peers' buffers copied to local memory, then expanded
     ok, worst = True, 0.0
     for s in range(3):                                      # three steps: both buffers of the peer transport get reused
         vi = (2 * s + 4 * rank) % 8
@@ -74,7 +75,7 @@ def _worker(rank, world, port, transport, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["peer", "nccl"])
+@pytest.mark.parametrize("transport", ["peer", "peer-staged", "nccl"])
 def test_compact_exchange_sums_like_a_dense_allreduce_and_is_identical_on_all_ranks(transport):
     import torch
     import torch.multiprocessing as mp
@@ -93,5 +94,5 @@ def test_compact_exchange_sums_like_a_dense_allreduce_and_is_identical_on_all_ra
     for rank, ok, worst, counts in results:
         assert ok, f"rank {rank}: the summed gradients differ from rank 0's"
         assert worst <= 1e-5, f"rank {rank}: compact sums differ from the dense all-reduce by {worst:.2e} of a tensor's scale"
-        if transport == "peer":
+        if transport.startswith("peer"):
             assert counts is not None and len(counts) == 2 and all(0 < c < 80_000 for c in counts)
