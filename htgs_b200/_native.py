@@ -149,6 +149,10 @@ def lib():
                 l.htgs_compact_rows_bytes.argtypes = [ctypes.c_uint32]
                 l.htgs_backward_compact.argtypes = l.htgs_backward.argtypes[:8] + [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p]
                 l.htgs_expand_add_rows.argtypes = [ctypes.POINTER(HtgsScene), ctypes.c_void_p, ctypes.c_uint32, ctypes.POINTER(HtgsGradients), ctypes.c_void_p]
+                l.htgs_expand_sum_scratch_bytes.restype = ctypes.c_size_t
+                l.htgs_expand_sum_scratch_bytes.argtypes = [ctypes.POINTER(HtgsScene), ctypes.c_int]
+                l.htgs_expand_sum_rows.argtypes = [ctypes.POINTER(HtgsScene), ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_uint32, ctypes.c_void_p,
+                                                   ctypes.c_size_t, ctypes.POINTER(HtgsGradients), ctypes.c_void_p]
                 l.htgs_copy_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p]
                 l.htgs_peer_buffer_create.argtypes = [ctypes.c_int, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
                 l.htgs_peer_buffer_open.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]

@@ -395,9 +395,6 @@ static int finish_frame(HtgsContext* ctx, HtgsFrameInfo* info) {
         li.kernel_launches = f.launches; li.reserved = 0;
         li.candidate_pairs = st.candidate_pairs; li.accepted_fragments = st.accepted_fragments;
         li.warp_trips = st.warp_trips; li.warp_trips_inserting = st.warp_trips_inserting; li.lane_insertions = st.lane_insertions;
-#ifdef HTGS_PROBE_FLOOR
-        li.lane_insertions = ((unsigned long long)st.reserved[0] << 32) | st.reserved[1];
-#endif
         li.workspace_bytes = carve_frame(nullptr, f.scene.n_primitives, f.geo.n_tiles, f.plan, st.overflow ? needed_capacity : f.capacity, false).bytes;
         if (info) *info = li;
         if (st.error) { f.active = false; return fail(HTGS_ERR_DEVICE_FLAG, "a kernel reported an internal error (bounded wait gave up)"); }

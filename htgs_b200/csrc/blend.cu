@@ -190,9 +190,6 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
     uint32_t phase = 0;
     bool wait_failed = false;
     [[maybe_unused]] uint32_t stat_candidates = 0, stat_accepted = 0, stat_trips = 0, stat_trips_inserting = 0, stat_insertions = 0;
-#ifdef HTGS_PROBE_FLOOR
-    [[maybe_unused]] uint32_t probe_floor_chain = 0, probe_floor_eval = 0;
-#endif
     // pixel rectangle of this warp (tw x rows_per_warp pixels; lane = row * tw + column)
     const float rect_x0 = float(tile_x * TS::tw);
     const float rect_y0 = float(tile_y * TS::th + warp * TS::rows_per_warp);
@@ -275,9 +272,6 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
             }
             const uint32_t n_cand = __popcll(cand);
             if constexpr (STATS) stat_candidates += n_cand;
-#ifdef HTGS_PROBE_FLOOR
-            uint32_t probe_ins = 0;
-#endif
             const uint32_t n_iter = __reduce_max_sync(0xffffffffu, n_cand);
             const uint32_t chunk_base = chunk * TS::chunk;
             auto pop_candidate = [&](bool& valid) -> uint32_t {
@@ -325,81 +319,6 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                     }
                     transmittance *= 1.0f - frag.w;
                 };
-#ifdef HTGS_BLEND_DECOUPLED
-                // Evaluation and K-buffer insertion decoupled in time.  A lane whose next fragment has to be inserted parks it
-                // (and the fragment evaluated with it) and stops evaluating; the other lanes go on.  The warp runs the
-                // insertion chain when HTGS_BLEND_DECOUPLED lanes are parked or no lane can go on without it, so one pass over
-                // the K levels serves more lanes.  Every lane still commits its own fragments in list order: same bits.
-                {
-                    bool pend = false, held = false;
-                    float pd = 0.0f, hd = 0.0f;
-                    float4 pf = make_float4(0, 0, 0, 0), hf = pf;
-                    uint32_t pj = 0, hj = 0;
-                    auto needs_insert = [&](float depth, const float4& frag) { return depth < kd[K - 1] && frag.w >= MT::min_alpha_core; };
-                    auto to_tail = [&](float depth, const float4& frag) {
-                        if constexpr (STATS) ++stat_accepted;
-                        if constexpr (TRAIN) {
-                            acc += make_float4(frag.x * frag.w, frag.y * frag.w, frag.z * frag.w, frag.w);
-                        } else {
-                            acc += frag;
-                            if (!use_median_depth) acc_depth += depth * frag.w;
-                        }
-                        transmittance *= 1.0f - frag.w;
-                    };
-                    // every trip pops a candidate of some lane or runs the chain for a parked one: at most 32 lanes x (32 pairs + 64
-                    // insertions) trips.  The bound only keeps an impossible state from spinning.
-                    #pragma unroll 1
-                    for (uint32_t trip = 0; ; ++trip) {
-                        if (trip >= 32u * 96u) { wait_failed = true; break; }
-                        const bool want = !pend && cand != 0;
-                        if (__any_sync(0xffffffffu, want)) {
-                            if constexpr (STATS) stat_trips += 2;
-                            if (want) {
-                                bool v0, v1;
-                                const uint32_t j0 = pop_candidate(v0);
-                                const uint32_t j1 = pop_candidate(v1);
-                                float depth0, depth1;
-                                float4 frag0, frag1;
-                                const bool ok0 = evaluate(v0, j0, depth0, frag0);
-                                const bool ok1 = evaluate(v1, j1, depth1, frag1);
-                                if (ok0) {
-                                    if (needs_insert(depth0, frag0)) {
-                                        pend = true; pd = depth0; pf = frag0; pj = j0;
-                                        held = ok1; hd = depth1; hf = frag1; hj = j1;
-                                    } else {
-                                        to_tail(depth0, frag0);
-                                    }
-                                }
-                                if (!pend && ok1) {
-                                    if (needs_insert(depth1, frag1)) { pend = true; pd = depth1; pf = frag1; pj = j1; }
-                                    else to_tail(depth1, frag1);
-                                }
-                            }
-                        }
-                        const uint32_t parked = __ballot_sync(0xffffffffu, pend);
-                        const uint32_t going = __ballot_sync(0xffffffffu, !pend && cand != 0);
-                        if (parked == 0) {
-                            if (going == 0) break;
-                            continue;
-                        }
-                        if (going == 0 || __popc(parked) >= HTGS_BLEND_DECOUPLED) {
-                            if constexpr (STATS) { stat_trips_inserting += 1; stat_insertions += pend ? 1 : 0; }
-                            if (pend) {
-                                pool4[free_slot * TS::threads + tid] = pf;
-                                if constexpr (TRAIN) pool_idx[free_slot * TS::threads + tid] = batch_begin - range.x + pj;
-                                free_slot = slot_index(kbuffer_insert<K>(kd, ks, pd, slot_t(free_slot)));
-                                to_tail(pd, pool4[free_slot * TS::threads + tid]);
-                                pend = false;
-                                if (held) {
-                                    held = false;
-                                    if (needs_insert(hd, hf)) { pend = true; pd = hd; pf = hf; pj = hj; }
-                                    else to_tail(hd, hf);
-                                }
-                            }
-                        }
-                    }
-                }
-#else
                 for (uint32_t it = 0; it < n_iter; it += 2) {
                     bool v0, v1;
                     const uint32_t j0 = pop_candidate(v0);
@@ -411,24 +330,14 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
                     if constexpr (STATS) {   // how often the insertion chain runs for the warp (the branch in commit is the warp vote)
                         const bool in0 = ok0 && depth0 < kd[K - 1] && frag0.w >= MT::min_alpha_core;
                         stat_trips += 1; stat_trips_inserting += __any_sync(0xffffffffu, in0) ? 1 : 0; stat_insertions += in0 ? 1 : 0;
-#ifdef HTGS_PROBE_FLOOR
-                        probe_ins += in0 ? 1 : 0;
-#endif
                     }
                     if (ok0) commit(depth0, frag0, j0);
                     if constexpr (STATS) {
                         const bool in1 = ok1 && depth1 < kd[K - 1] && frag1.w >= MT::min_alpha_core;
                         stat_trips += 1; stat_trips_inserting += __any_sync(0xffffffffu, in1) ? 1 : 0; stat_insertions += in1 ? 1 : 0;
-#ifdef HTGS_PROBE_FLOOR
-                        probe_ins += in1 ? 1 : 0;
-#endif
                     }
                     if (ok1) commit(depth1, frag1, j1);
                 }
-#endif
-#ifdef HTGS_PROBE_FLOOR
-                if constexpr (STATS) { probe_floor_chain += __reduce_max_sync(0xffffffffu, probe_ins); probe_floor_eval += n_iter; }
-#endif
             } else {
                 // The other three modes use the same two-candidates-per-trip shape: both evaluations (divide, expf, depth) are
                 // independent instruction streams; the state updates happen in list order.  A fragment counts iff it passes
@@ -506,9 +415,6 @@ __global__ void __launch_bounds__(TileShape<MODE>::threads) blend_kernel(
         if (lane == 0 && stat_trips) {
             atomicAdd(&status->warp_trips, (unsigned long long)stat_trips); atomicAdd(&status->warp_trips_inserting, (unsigned long long)stat_trips_inserting);
             atomicAdd(&status->lane_insertions, (unsigned long long)ins);
-#ifdef HTGS_PROBE_FLOOR
-            atomicAdd(&status->reserved[0], probe_floor_chain); atomicAdd(&status->reserved[1], probe_floor_eval);
-#endif
         }
     }
     if (!inside) return;

@@ -182,6 +182,140 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_add_rows_kernel(cons
     }
 }
 
+// Sum of several compact-row buffers as dense gradients, every dense row written ONCE (htgs_expand_sum_rows).
+// Expanding buffer after buffer with expand_add_rows_kernel reads and writes a dense row once per buffer that holds it; with
+// many buffers (8 ranks) that is most of the exchange's time.  Here a table is built first - table[s][g] = row of Gaussian g in
+// buffer s, or -1 - and then one kernel walks the Gaussians: a warp takes 32 consecutive ones, every lane adds up its
+// Gaussian's rows from all buffers in registers, in buffer order starting from zero (the very additions the buffer-by-buffer
+// expansion performs, so the bits are the same), and the warp stores the 32 dense rows of each tensor as one contiguous block.
+// Rows of Gaussians no buffer holds are written as zeros: the tensors need not be cleared.
+constexpr int kMaxSources = 16;
+constexpr int kGatherGroup = 2;
+static_assert(kMaxSources % kGatherGroup == 0, "groups of buffers");
+struct CompactSources {
+    const float4* rows[kMaxSources];
+    int n;
+};
+__global__ void __launch_bounds__(256) build_slot_table_kernel(const __grid_constant__ CompactSources src, uint32_t capacity, int32_t* __restrict__ table,
+                                                               uint32_t n_primitives) {
+    const int s = int(blockIdx.y);
+    const float4* rows = src.rows[s];
+    const uint32_t count = min(reinterpret_cast<const CompactGradientHeader*>(rows)->count, capacity);
+    int32_t* mine = table + size_t(s) * n_primitives;
+    for (uint32_t r = blockIdx.x * 256 + threadIdx.x; r < count; r += gridDim.x * 256) {
+        const uint32_t idx = __float_as_uint(reinterpret_cast<const float*>(rows + kCompactRowFloat4s * (size_t(r) + 1))[0]);
+        if (idx < n_primitives) mine[idx] = int32_t(r);
+    }
+}
+
+__global__ void __launch_bounds__(kExpandWarps * 32) gather_sum_rows_kernel(const __grid_constant__ CompactSources src, uint32_t capacity,
+                                                                            const int32_t* __restrict__ table, const float* __restrict__ positions,
+                                                                            DenseGradients out, uint32_t n_primitives, int total_sh_bases) {
+    __shared__ __align__(16) float s_tile[kExpandWarps][32 * kExpandValues];      // 32 x 45 for grad_sh_rest, then the narrow tensors' 32 x (3 + 3 + 3 + 4 + 1)
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    float* tile = s_tile[warp];
+    const uint32_t n_chunks = (n_primitives + 31u) / 32u;
+    const uint32_t n_warps = gridDim.x * kExpandWarps;
+    const uint32_t sh_width = uint32_t(total_sh_bases) * 3u;
+    for (uint32_t chunk = blockIdx.x * kExpandWarps + warp; chunk < n_chunks; chunk += n_warps) {
+        const uint32_t g = chunk * 32u + lane;
+        const bool inside = g < n_primitives;
+        const uint32_t here = min(32u, n_primitives - chunk * 32u);
+        float acc[kExpandValues];
+        #pragma unroll
+        for (int i = 0; i < kExpandValues; ++i) acc[i] = 0.0f;
+        float3 position = make_float3(0, 0, 0);
+        bool have_position = false;
+        // buffers in groups of kGatherGroup: the group's table entries, then its rows, are all in flight before the first is used
+        #pragma unroll 1
+        for (int s0 = 0; s0 < src.n; s0 += kGatherGroup) {
+            int32_t slot[kGatherGroup];
+            #pragma unroll
+            for (int j = 0; j < kGatherGroup; ++j) slot[j] = (s0 + j < src.n && inside) ? table[size_t(s0 + j) * n_primitives + g] : -1;
+            float4 ra[kGatherGroup], rb[kGatherGroup], rc[kGatherGroup], rd[kGatherGroup];
+            #pragma unroll
+            for (int j = 0; j < kGatherGroup; ++j) {
+                ra[j] = make_float4(__uint_as_float(0xffffffffu), 0, 0, 0);
+                if (slot[j] >= 0) {
+                    const float4* rows = src.rows[s0 + j];
+                    if (uint32_t(slot[j]) < min(reinterpret_cast<const CompactGradientHeader*>(rows)->count, capacity)) {
+                        const float4* row = rows + kCompactRowFloat4s * (size_t(slot[j]) + 1);
+                        ra[j] = row[0]; rb[j] = row[1]; rc[j] = row[2]; rd[j] = row[3];
+                    }
+                }
+            }
+            #pragma unroll
+            for (int j = 0; j < kGatherGroup; ++j) {
+                if (slot[j] < 0 || __float_as_uint(ra[j].x) != g) continue;      // no row, a stale table entry or a foreign row: adds nothing
+                const float4 a = ra[j], b = rb[j], c = rc[j], d = rd[j];
+                const CompactGradientHeader* header = reinterpret_cast<const CompactGradientHeader*>(src.rows[s0 + j]);
+                // __fadd_rn: the products below must be rounded before they are added (no multiply-add contraction), as they
+                // are when the buffer-by-buffer expansion passes them through shared memory
+                acc[0] = __fadd_rn(acc[0], a.y); acc[1] = __fadd_rn(acc[1], a.z); acc[2] = __fadd_rn(acc[2], a.w);
+                acc[3] = __fadd_rn(acc[3], b.x); acc[4] = __fadd_rn(acc[4], b.y); acc[5] = __fadd_rn(acc[5], b.z);
+                acc[6] = __fadd_rn(acc[6], c.x); acc[7] = __fadd_rn(acc[7], c.y); acc[8] = __fadd_rn(acc[8], c.z); acc[9] = __fadd_rn(acc[9], c.w);
+                acc[10] = __fadd_rn(acc[10], b.w);
+                const float3 grad_rgb = make_float3(d.x, d.y, d.z);
+                const float3 band0 = kShBand0 * grad_rgb;
+                acc[11] = __fadd_rn(acc[11], band0.x); acc[12] = __fadd_rn(acc[12], band0.y); acc[13] = __fadd_rn(acc[13], band0.z);
+                const int active = min(int(header->active_sh_bases), total_sh_bases + 1);
+                if (active > 1) {
+                    if (!have_position) {
+                        position = make_float3(__ldg(positions + 3 * size_t(g)), __ldg(positions + 3 * size_t(g) + 1), __ldg(positions + 3 * size_t(g) + 2));
+                        have_position = true;
+                    }
+                    const float3 dir = normalize(position - make_float3(header->cam_x, header->cam_y, header->cam_z));
+                    float3 sh[15];
+                    const int written = sh_rest_gradient_rows(dir, grad_rgb, active, sh);
+                    #pragma unroll
+                    for (int i = 0; i < 15; ++i)
+                        if (i < written) {
+                            acc[14 + 3 * i] = __fadd_rn(acc[14 + 3 * i], sh[i].x); acc[15 + 3 * i] = __fadd_rn(acc[15 + 3 * i], sh[i].y);
+                            acc[16 + 3 * i] = __fadd_rn(acc[16 + 3 * i], sh[i].z);
+                        }
+                }
+            }
+        }
+        // The chunk's 32 rows of a tensor are one contiguous, 16-byte aligned block of the tensor (32 rows x width x 4 bytes): the
+        // lanes lay their values out in shared memory exactly like that block and the warp stores it with 16-byte stores.
+        float* t_sh = tile;                                  // [32][sh_width]
+        float* t_pos = tile + 32 * 45;                       // [32][3]
+        float* t_scale = t_pos + 96;                         // [32][3]
+        float* t_sh0 = t_scale + 96;                         // [32][3]
+        float* t_rot = t_sh0 + 96;                           // [32][4]
+        float* t_opacity = t_rot + 128;                      // [32]
+        t_pos[lane * 3] = acc[0]; t_pos[lane * 3 + 1] = acc[1]; t_pos[lane * 3 + 2] = acc[2];
+        t_scale[lane * 3] = acc[3]; t_scale[lane * 3 + 1] = acc[4]; t_scale[lane * 3 + 2] = acc[5];
+        reinterpret_cast<float4*>(t_rot)[lane] = make_float4(acc[6], acc[7], acc[8], acc[9]);
+        t_opacity[lane] = acc[10];
+        t_sh0[lane * 3] = acc[11]; t_sh0[lane * 3 + 1] = acc[12]; t_sh0[lane * 3 + 2] = acc[13];
+        #pragma unroll
+        for (int i = 0; i < 45; ++i)
+            if (uint32_t(i) < sh_width) t_sh[lane * sh_width + i] = acc[14 + i];
+        __syncwarp();
+        const size_t first = size_t(chunk) * 32u;
+        if (here == 32u) {
+            float4* dst = reinterpret_cast<float4*>(out.sh_rest + first * sh_width);
+            for (uint32_t e = lane; e < 8u * sh_width; e += 32) dst[e] = reinterpret_cast<const float4*>(t_sh)[e];
+            if (lane < 24u) {
+                reinterpret_cast<float4*>(out.positions + first * 3)[lane] = reinterpret_cast<const float4*>(t_pos)[lane];
+                reinterpret_cast<float4*>(out.scales + first * 3)[lane] = reinterpret_cast<const float4*>(t_scale)[lane];
+                reinterpret_cast<float4*>(out.sh_0 + first * 3)[lane] = reinterpret_cast<const float4*>(t_sh0)[lane];
+            }
+            reinterpret_cast<float4*>(out.rotations + first * 4)[lane] = reinterpret_cast<const float4*>(t_rot)[lane];
+            if (lane < 8u) reinterpret_cast<float4*>(out.opacities + first)[lane] = reinterpret_cast<const float4*>(t_opacity)[lane];
+        } else {      // the scene's last, partial chunk
+            for (uint32_t e = lane; e < here * sh_width; e += 32) out.sh_rest[first * sh_width + e] = t_sh[e];
+            for (uint32_t e = lane; e < here * 3u; e += 32) {
+                out.positions[first * 3 + e] = t_pos[e]; out.scales[first * 3 + e] = t_scale[e]; out.sh_0[first * 3 + e] = t_sh0[e];
+            }
+            for (uint32_t e = lane; e < here * 4u; e += 32) out.rotations[first * 4 + e] = t_rot[e];
+            if (lane < here) out.opacities[first + lane] = t_opacity[lane];
+        }
+        __syncwarp();
+    }
+}
+
 // Copies a compact-row buffer (header + the rows its header counts, at most `capacity`) with 16-byte loads and stores, every
 // thread with several loads in flight.  `src` is typically another GPU's buffer: a rank pulls the other ranks' buffers into
 // local memory one after the other, each rank starting with a different peer, so that at any time every GPU's memory is read by
@@ -257,6 +391,50 @@ int htgs_expand_add_rows(const HtgsScene* scene, const void* rows, uint32_t capa
     expand_add_rows_kernel<<<blocks < 148u * 32u ? blocks : 148u * 32u, kExpandWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const float4*>(rows), capacity_rows, scene->positions, out, uint32_t(scene->n_primitives), int(scene->total_sh_bases));
     const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HTGS_OK : exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
+}
+
+size_t htgs_expand_sum_scratch_bytes(const HtgsScene* scene, int n_buffers) {
+    if (!scene || scene->n_primitives <= 0 || n_buffers <= 0) return 0;
+    return size_t(n_buffers) * size_t(scene->n_primitives) * sizeof(int32_t);
+}
+
+int htgs_expand_sum_rows(const HtgsScene* scene, const void* const* buffers, int n_buffers, uint32_t capacity_rows, void* scratch, size_t scratch_bytes,
+                         const HtgsGradients* grads, void* stream_ptr) {
+    using namespace htgs;
+    if (!scene || !buffers || !grads) return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand sum: null argument");
+    if (n_buffers < 1 || n_buffers > kMaxSources) return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand sum: between 1 and 16 buffers");
+    if (scene->n_primitives < 0 || scene->total_sh_bases < 0 || scene->total_sh_bases > 15)
+        return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand sum: bad scene sizes");
+    if (scene->n_primitives == 0) return HTGS_OK;
+    if (!scene->positions || !grads->grad_positions || !grads->grad_scales || !grads->grad_rotations || !grads->grad_opacities || !grads->grad_sh_0 ||
+        (scene->total_sh_bases > 0 && !grads->grad_sh_rest))
+        return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand sum: positions and the six gradient tensors must not be null");
+    if (!scratch || scratch_bytes < htgs_expand_sum_scratch_bytes(scene, n_buffers)) return exchange_fail(HTGS_ERR_WORKSPACE_TOO_SMALL, "expand sum: scratch too small");
+    if (((reinterpret_cast<uintptr_t>(grads->grad_positions) | reinterpret_cast<uintptr_t>(grads->grad_scales) | reinterpret_cast<uintptr_t>(grads->grad_rotations) |
+          reinterpret_cast<uintptr_t>(grads->grad_opacities) | reinterpret_cast<uintptr_t>(grads->grad_sh_0) | reinterpret_cast<uintptr_t>(grads->grad_sh_rest)) & 15u) != 0)
+        return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand sum: the six gradient tensors must be 16-byte aligned (they are written with 16-byte stores)");
+    CompactSources src{};
+    src.n = n_buffers;
+    for (int s = 0; s < n_buffers; ++s) {
+        if (!buffers[s] || (reinterpret_cast<uintptr_t>(buffers[s]) & 15u) != 0)
+            return exchange_fail(HTGS_ERR_INVALID_ARGUMENT, "expand sum: a buffer is null or not 16-byte aligned");
+        src.rows[s] = static_cast<const float4*>(buffers[s]);
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    const uint32_t n = uint32_t(scene->n_primitives);
+    cudaError_t err = cudaMemsetAsync(scratch, 0xff, size_t(n_buffers) * n * sizeof(int32_t), stream);
+    if (err != cudaSuccess) return exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
+    if (capacity_rows > 0) {
+        const uint32_t blocks = (capacity_rows + 255u) / 256u;
+        build_slot_table_kernel<<<dim3(blocks < 148u * 4u ? blocks : 148u * 4u, unsigned(n_buffers), 1), 256, 0, stream>>>(src, capacity_rows, static_cast<int32_t*>(scratch), n);
+        if ((err = cudaGetLastError()) != cudaSuccess) return exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
+    }
+    const DenseGradients out{grads->grad_positions, grads->grad_scales, grads->grad_rotations, grads->grad_opacities, grads->grad_sh_0, grads->grad_sh_rest};
+    const uint32_t chunk_blocks = ((n + 31u) / 32u + kExpandWarps - 1u) / kExpandWarps;
+    gather_sum_rows_kernel<<<chunk_blocks < 148u * 32u ? chunk_blocks : 148u * 32u, kExpandWarps * 32, 0, stream>>>(
+        src, capacity_rows, static_cast<const int32_t*>(scratch), scene->positions, out, n, int(scene->total_sh_bases));
+    err = cudaGetLastError();
     return err == cudaSuccess ? HTGS_OK : exchange_fail(HTGS_ERR_CUDA, cudaGetErrorString(err));
 }
 

@@ -521,6 +521,15 @@ class CompactExchange:
         self.rows_published = mine
         self._capacity = max(1024, -(-largest // 1024) * 1024)      # whole kilorows: few distinct buffer sizes over a run
 
+    def expansion(self) -> str:
+        """How the autograd hook turns the buffers into dense sums: "sum" = one pass that writes every dense row once
+        (`htgs_expand_sum_rows`; needs all buffers in local memory), "add" = buffer after buffer (`htgs_expand_add_rows`; reads
+        the one peer's buffer of a two-rank job in place)."""
+        world = self._world(self.group)
+        if self.transport == "auto":
+            self._use_peers(True)
+        return "sum" if (world > 2 or (world == 2 and (self.transport == "nccl" or self.always_stage))) else "add"
+
     def capacity(self, n: int) -> int:
         if self.transport == "auto":
             self._use_peers(True)

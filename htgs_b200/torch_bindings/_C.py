@@ -276,15 +276,15 @@ def backward(densification_info, grad_image, image, positions, scales, rotations
         view = HtgsView(M.data_ptr(), VPM.data_ptr(), cam_position.data_ptr(), int(rasterizer_mode), int(K), int(active_sh_bases), int(width), int(height),
                         float(near_plane), float(far_plane), 1.0)
         scratch = torch.empty(lib.htgs_backward_scratch_bytes(ctypes.byref(scene)), dtype=torch.uint8, device=device)
-        rows = int(densification_info.shape[0]) if densification_info.numel() > 0 else 0
-        if rows not in (0, 2, 3):
+        rows_d = int(densification_info.shape[0]) if densification_info.numel() > 0 else 0
+        if rows_d not in (0, 2, 3):
             raise ValueError("densification_info must be empty or have 2 or 3 rows")
-        if rows and (densification_info.dtype != torch.float32 or densification_info.device != device or not densification_info.is_contiguous()
-                     or densification_info.numel() != rows * n):
+        if rows_d and (densification_info.dtype != torch.float32 or densification_info.device != device or not densification_info.is_contiguous()
+                       or densification_info.numel() != rows_d * n):
             raise ValueError("densification_info must be a contiguous float32 tensor of shape [rows, N, 1] on the same device")
         grads = _native.HtgsGradients(grad_positions.data_ptr(), grad_scales.data_ptr(), grad_rotations.data_ptr(), grad_opacities.data_ptr(),
                                       grad_sh_0.data_ptr(), grad_sh_rest.data_ptr() if grad_sh_rest.numel() else None, scratch.data_ptr(), scratch.numel(),
-                                      densification_info.data_ptr() if rows else None, rows, int(bool(use_distance_scaling)))
+                                      densification_info.data_ptr() if rows_d else None, rows_d, int(bool(use_distance_scaling)))
         blobs = _native.HtgsTrainBlobs(per_primitive_buffers.data_ptr(), per_primitive_buffers.numel(), per_tile_buffers.data_ptr(),
                                        per_tile_buffers.numel(), per_instance_buffers.data_ptr(), per_instance_buffers.numel(),
                                        per_pixel_buffers.data_ptr(), per_pixel_buffers.numel())
@@ -294,10 +294,22 @@ def backward(densification_info, grad_image, image, positions, scales, rotations
         if compact is not None:
             capacity = int(compact.capacity(n))
             rows = compact.buffer(lib.htgs_compact_rows_bytes(capacity), device)
+            # "sum": all buffers are local memory and one pass writes every dense row once (htgs_expand_sum_rows; nothing to clear);
+            # "add": buffer after buffer into tensors the backward call cleared (htgs_expand_add_rows; reads a peer's buffer in place)
+            one_pass = getattr(compact, "expansion", lambda: "add")() == "sum"
+            no_dense = _native.HtgsGradients(None, None, None, None, None, None, scratch.data_ptr(), scratch.numel(),
+                                             densification_info.data_ptr() if rows_d else None, rows_d, int(bool(use_distance_scaling)))
             _native.check(lib.htgs_backward_compact(ctx, ctypes.byref(scene), ctypes.byref(view), ctypes.byref(blobs), int(n_instances), grad_image.data_ptr(),
-                                                    image_ptr, ctypes.byref(grads), rows.data_ptr(), capacity, stream))
-            for address, rows_capacity, keep_alive in compact.exchange(rows, capacity):
-                _native.check(lib.htgs_expand_add_rows(ctypes.byref(scene), address, int(rows_capacity), ctypes.byref(grads), stream))
+                                                    image_ptr, ctypes.byref(no_dense if one_pass else grads), rows.data_ptr(), capacity, stream))
+            parts = compact.exchange(rows, capacity)
+            if one_pass:
+                addresses = (ctypes.c_void_p * len(parts))(*[int(address) for address, _, _ in parts])
+                table = torch.empty(lib.htgs_expand_sum_scratch_bytes(ctypes.byref(scene), len(parts)), dtype=torch.uint8, device=device)
+                _native.check(lib.htgs_expand_sum_rows(ctypes.byref(scene), addresses, len(parts), capacity, table.data_ptr(), table.numel(), ctypes.byref(grads), stream))
+                table.record_stream(torch.cuda.current_stream(device))
+            else:
+                for address, rows_capacity, keep_alive in parts:
+                    _native.check(lib.htgs_expand_add_rows(ctypes.byref(scene), address, int(rows_capacity), ctypes.byref(grads), stream))
             scratch.record_stream(torch.cuda.current_stream(device))
             return outs
         if ranges is None:

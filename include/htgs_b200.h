@@ -281,6 +281,16 @@ int htgs_copy_rows(void* dst, const void* src, uint32_t capacity_rows, void* str
 int htgs_backward_compact(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
                           const float* grad_image, const float* image, const HtgsGradients* grads, void* rows, uint32_t capacity_rows, void* stream);
 int htgs_expand_add_rows(const HtgsScene* scene, const void* rows, uint32_t capacity_rows, const HtgsGradients* grads, void* stream);
+/* The same sums with every dense row written once: SETS all rows of the six tensors of `grads` to the sum over `buffers`
+ * (n_buffers of them, 1..16, each with room for capacity_rows rows), added up per Gaussian in the order given, starting from
+ * zero - the additions htgs_expand_add_rows performs buffer after buffer on cleared tensors, so the results are bit-identical to
+ * that - and zero for Gaussians no buffer holds; the tensors need not be cleared.  With many buffers this is several times
+ * faster (one write per dense row instead of a read and a write per buffer that holds it).  The buffers must be memory of this
+ * GPU (rows are fetched one by one: copy a peer's buffer with htgs_copy_rows first).  `scratch`:
+ * htgs_expand_sum_scratch_bytes(scene, n_buffers) bytes (4 bytes per Gaussian and buffer).  Stream-ordered. */
+size_t htgs_expand_sum_scratch_bytes(const HtgsScene* scene, int n_buffers);
+int htgs_expand_sum_rows(const HtgsScene* scene, const void* const* buffers, int n_buffers, uint32_t capacity_rows, void* scratch, size_t scratch_bytes,
+                         const HtgsGradients* grads, void* stream);
 
 /*
  * Device buffers that the other ranks' GPUs read directly (peer access over NVLink): the transport of the compact rows that needs

@@ -54,7 +54,7 @@ def _worker(rank, world, port, transport, out):
     xchg.always_stage = transport == "peer-staged"      # the path more than two ranks take: peers' buffers copied to local memory, then expanded
     ok, worst = True, 0.0
     for s in range(3):                                      # three steps: both buffers of the peer transport get reused
-        vi = (2 * s + 4 * rank) % 8
+        vi = (2 * s + (8 // world) * rank) % 8
         dense = step(vi, None)
         parallel.allreduce_gradients(dense)
         compact = step(vi, xchg)
@@ -81,10 +81,12 @@ def test_compact_exchange_sums_like_a_dense_allreduce_and_is_identical_on_all_ra
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
+    # two ranks read the one peer's buffer in place; with four, every rank pulls three peers' buffers in its own order and sums in one pass
+    world = 4 if (torch.cuda.device_count() >= 4 and transport != "peer") else 2
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, transport, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, transport, out)) for r in range(world)]
     for p in procs:
         p.start()
     results = sorted(out.get(timeout=600) for _ in procs)
@@ -95,4 +97,4 @@ def test_compact_exchange_sums_like_a_dense_allreduce_and_is_identical_on_all_ra
         assert ok, f"rank {rank}: the summed gradients differ from rank 0's"
         assert worst <= 1e-5, f"rank {rank}: compact sums differ from the dense all-reduce by {worst:.2e} of a tensor's scale"
         if transport.startswith("peer"):
-            assert counts is not None and len(counts) == 2 and all(0 < c < 80_000 for c in counts)
+            assert counts is not None and len(counts) == world and all(0 < c < 80_000 for c in counts)

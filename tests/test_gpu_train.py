@@ -260,8 +260,11 @@ class _OwnRowsOnly:
     hand back (by default this rank's own), and it keeps what the backward pass wrote."""
     compact = True
 
-    def __init__(self, capacity=None, replay=None):
-        self._capacity, self.replay, self.rows, self.kept = capacity, replay, None, []
+    def __init__(self, capacity=None, replay=None, expansion="add"):
+        self._capacity, self.replay, self.rows, self.kept, self._expansion = capacity, replay, None, [], expansion
+
+    def expansion(self):
+        return self._expansion
 
     def capacity(self, n):
         return n if self._capacity is None else self._capacity
@@ -360,6 +363,38 @@ def test_compact_rows_of_two_views_sum_like_two_dense_passes_and_small_capacity_
     torch.cuda.synchronize()
     for name, a, b in zip(GRAD_NAMES, last, dense_sum):
         assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-30), f"grad_{name}"
+    # one pass over all buffers (htgs_expand_sum_rows) against buffer after buffer (htgs_expand_add_rows): the same bits
+    import ctypes
+    from htgs_b200 import _native
+    lib = _native.lib()
+    n, B = scene.n, tensors[5].shape[1]
+    sc = _native.HtgsScene(tensors[0].data_ptr(), None, None, None, None, None, n, B)
+    stream = torch.cuda.current_stream().cuda_stream
+    buffers = [stub.kept[0][0], stub.kept[1][0], stub.kept[0][0], stub.kept[1][0], stub.kept[1][0]]      # five "ranks", views repeated
+
+    def gradients(fill):
+        outs = [torch.full_like(g, fill) for g in last]
+        return outs, _native.HtgsGradients(outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), outs[3].data_ptr(), outs[4].data_ptr(),
+                                           outs[5].data_ptr(), None, 0, None, 0, 0)
+    added, gr = gradients(0.0)
+    for b in buffers:
+        _native.check(lib.htgs_expand_add_rows(ctypes.byref(sc), b.data_ptr(), n, ctypes.byref(gr), stream))
+    summed, gr = gradients(7.0)                                  # not cleared: every row is written
+    table = torch.empty(lib.htgs_expand_sum_scratch_bytes(ctypes.byref(sc), len(buffers)), dtype=torch.uint8, device="cuda")
+    addresses = (ctypes.c_void_p * len(buffers))(*[b.data_ptr() for b in buffers])
+    _native.check(lib.htgs_expand_sum_rows(ctypes.byref(sc), addresses, len(buffers), n, table.data_ptr(), table.numel(), ctypes.byref(gr), stream))
+    torch.cuda.synchronize()
+    for name, a, b in zip(GRAD_NAMES, summed, added):
+        assert torch.equal(a, b), f"grad_{name}: one pass and buffer-after-buffer differ"
+    with pytest.raises(_native.HtgsError):
+        _native.check(lib.htgs_expand_sum_rows(ctypes.byref(sc), addresses, len(buffers), n, table.data_ptr(), 16, ctypes.byref(gr), stream))
+    # the autograd hook's one-pass route
+    one_pass = _OwnRowsOnly(replay="all kept", expansion="sum")
+    one_pass.kept = list(stub.kept[:1])
+    via_hook = _C.backward(*args, compact=one_pass)
+    torch.cuda.synchronize()
+    for name, a, b in zip(GRAD_NAMES, via_hook, dense_sum):
+        assert (a - b).abs().max().item() <= 1e-5 * max(b.abs().max().item(), 1e-30), f"grad_{name} (one pass)"
     small = _OwnRowsOnly(capacity=100)
     _C.backward(*args, compact=small)
     torch.cuda.synchronize()
