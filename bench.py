@@ -61,6 +61,7 @@ def parse_args():
                          "overlap = the chain rule (optionally the whole backward pass) runs in ranges of Gaussians and each finished range's rows are summed "
                          "while the next is computed; dense = the dense tensors, after the backward")
     ap.add_argument("--exchange-single-rank", action="store_true", help="train at N = 1 with --exchange compact: run the exchange's machinery anyway (its local cost; what the ncu summaries of its kernels use)")
+    ap.add_argument("--exchange-one-pass", action="store_true", help="--exchange compact with one or two ranks: form the sums the way more than two ranks do (local copies, one pass)")
     ap.add_argument("--exchange-chunks", type=int, default=4, help="ranges of Gaussians the backward pass is split into for --exchange overlap")
     ap.add_argument("--exchange-split-pass", action="store_true", help="--exchange overlap: split the per-tile pass along the ranges too (default: only the per-Gaussian chain rule)")
     ap.add_argument("--reference-kind", default="auto", choices=["auto", "cuda", "cpu"])
@@ -210,6 +211,7 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
         rasterization.set_backward_hook(xchg)
     if compact:
         xchg = parallel.CompactExchange(transport="peer" if args.exchange == "compact" else "nccl")
+        xchg.always_stage = bool(args.exchange_one_pass)
         compact_transport = xchg.prepare(scene.n, device)      # falls back to the all-gather transport on all ranks if the buffers cannot be mapped
         rasterization.set_backward_hook(xchg)
     exchanged_rows = []

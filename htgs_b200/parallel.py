@@ -466,7 +466,7 @@ class CompactExchange:
         self._peers = None
         self._token = None
         self._staging = None
-        self.always_stage = False     # tests: take the copy-then-expand path with two ranks too
+        self.always_stage = False     # tests and profiles: take the route of more than two ranks (copy, then one-pass sums) with fewer
         self.rows_published = 0       # "nccl": rows of this rank in the last step
         self.bytes_gathered = 0       # "nccl": bytes the last all-gather delivered to this rank (all ranks' buffers)
 
@@ -528,7 +528,9 @@ class CompactExchange:
         world = self._world(self.group)
         if self.transport == "auto":
             self._use_peers(True)
-        return "sum" if (world > 2 or (world == 2 and (self.transport == "nccl" or self.always_stage))) else "add"
+        if world > 2:
+            return "sum"
+        return "sum" if (self.always_stage or (world == 2 and self.transport == "nccl")) else "add"
 
     def capacity(self, n: int) -> int:
         if self.transport == "auto":
