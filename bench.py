@@ -285,7 +285,7 @@ def run_training(args, mod, is_reference, scene, tensors, cams_dev, settings, de
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name.replace("config1", "config2 (fwd+bwd, L1, one view per GPU)"), "views_per_step": world,
                        "allreduce_bytes_per_rank": grad_bytes if world > 1 else 0,
-                       "gradient_exchange": ("none" if world == 1 else
+                       "gradient_exchange": ("none" if (world == 1 and not sparse) else
                                              f"rows of the union of the ranks' visible Gaussians, summed range by range ({args.exchange_chunks} ranges{', per-tile pass split too' if args.exchange_split_pass else ''}) while the backward pass runs" if overlap else
                                              ("compact rows (64 B per Gaussian a rank's view kept), read from the peers' buffers over NVLink by the kernel that expands them" if compact_transport == "peer"
                                               else "compact rows (64 B per Gaussian a rank's view kept), all-gathered and expanded on every rank") if compact else
