@@ -130,6 +130,8 @@ def lib():
                 l.htgs_get_intermediates.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsIntermediates)]
                 l.htgs_forward_blob_sizes.argtypes = [ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.POINTER(ctypes.c_size_t),
                                                       ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
+                l.htgs_forward_instance_capacity.restype = ctypes.c_uint64
+                l.htgs_forward_instance_capacity.argtypes = [ctypes.c_uint64]
                 l.htgs_forward_instance_bytes.restype = ctypes.c_size_t
                 l.htgs_forward_instance_bytes.argtypes = [ctypes.POINTER(HtgsView), ctypes.c_uint64]
                 l.htgs_forward_begin.argtypes = [ctypes.c_void_p, ctypes.POINTER(HtgsScene), ctypes.POINTER(HtgsView), ctypes.c_void_p, ctypes.c_size_t,

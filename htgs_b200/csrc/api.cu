@@ -655,6 +655,15 @@ int htgs_forward_blob_sizes(const HtgsScene* scene, const HtgsView* view, size_t
     return HTGS_OK;
 }
 
+uint64_t htgs_forward_instance_capacity(uint64_t n_instances) {
+    if (n_instances <= 4096) return 4096;
+    int top = 63;
+    while (!(n_instances >> top)) --top;                      // index of the highest set bit
+    const uint64_t step = uint64_t(1) << (top - 3);           // eight sizes per power of two
+    const uint64_t rounded = (n_instances + step - 1) / step * step;
+    return rounded < n_instances ? n_instances : rounded;     // (overflow: cannot happen below 2^60)
+}
+
 size_t htgs_forward_instance_bytes(const HtgsView* view, uint64_t n_instances) {
     if (!view || view->mode < 0 || view->mode > 3 || view->width <= 0 || view->height <= 0) return 0;
     const FrameGeometry geo = make_geometry(view->mode, view->width, view->height);

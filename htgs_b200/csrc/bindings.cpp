@@ -206,7 +206,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, int, int> forward(
         ready->record(torch_stream);
         g_visibility[a.device.index()] = VisibilityRecord{visible, ready};
     }
-    const size_t pi_bytes = htgs_forward_instance_bytes(&a.view, n_instances);
+    // a few sizes per power of two: the instance count changes from view to view, and exact sizes would miss torch's block cache
+    const size_t pi_bytes = htgs_forward_instance_bytes(&a.view, htgs_forward_instance_capacity(n_instances));
     Tensor per_instance = bytes_on(a.device, pi_bytes);
     HtgsTrainBlobs blobs{per_primitive.data_ptr(), pp_bytes, per_tile.data_ptr(), pt_bytes, per_instance.data_ptr(), pi_bytes, per_pixel.data_ptr(), px_bytes};
     HtgsFrameInfo info{};

@@ -157,7 +157,8 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
                 mask |= earlier[0]          # several forwards per step: a row any of them kept can be non-zero
             ready.record(torch.cuda.current_stream(device))
             last_visibility[key] = (mask, ready)
-        per_instance = torch.empty(lib.htgs_forward_instance_bytes(ctypes.byref(view), n_inst.value), **byte)
+        # a few sizes per power of two: the instance count changes from view to view, and exact sizes would miss torch's block cache
+        per_instance = torch.empty(lib.htgs_forward_instance_bytes(ctypes.byref(view), lib.htgs_forward_instance_capacity(n_inst.value)), **byte)
         blobs = _native.HtgsTrainBlobs(per_primitive.data_ptr(), per_primitive.numel(), per_tile.data_ptr(), per_tile.numel(),
                                        per_instance.data_ptr(), per_instance.numel(), per_pixel.data_ptr(), per_pixel.numel())
         info = HtgsFrameInfo()

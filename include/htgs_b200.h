@@ -181,6 +181,11 @@ typedef struct HtgsTrainBlobs {
 
 int htgs_forward_blob_sizes(const HtgsScene* scene, const HtgsView* view, size_t* per_primitive_bytes, size_t* per_tile_bytes, size_t* per_pixel_bytes);
 size_t htgs_forward_instance_bytes(const HtgsView* view, uint64_t n_instances);
+/* n_instances rounded up to one of eight sizes per power of two (at most 12.5 % more).  The per-instance blob may be larger than
+ * htgs_forward_instance_bytes(view, n_instances); a caller whose allocator caches freed blocks by size should allocate
+ * htgs_forward_instance_bytes(view, htgs_forward_instance_capacity(n_instances)) bytes: the instance count differs from view to
+ * view, and an exact-size request misses the cache (a cudaMalloc inside the training step) whenever it grows by a few percent. */
+uint64_t htgs_forward_instance_capacity(uint64_t n_instances);
 int htgs_forward_begin(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, void* per_primitive, size_t per_primitive_bytes,
                        void* stream, uint32_t* n_instances);
 int htgs_forward_finish(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, const HtgsTrainBlobs* blobs, uint32_t n_instances,
