@@ -659,7 +659,7 @@ uint64_t htgs_forward_instance_capacity(uint64_t n_instances) {
     if (n_instances <= 4096) return 4096;
     int top = 63;
     while (!(n_instances >> top)) --top;                      // index of the highest set bit
-    const uint64_t step = uint64_t(1) << (top - 3);           // eight sizes per power of two
+    const uint64_t step = uint64_t(1) << (top - 1);           // two sizes per power of two: 2^k and 1.5 * 2^k
     const uint64_t rounded = (n_instances + step - 1) / step * step;
     return rounded < n_instances ? n_instances : rounded;     // (overflow: cannot happen below 2^60)
 }

@@ -206,8 +206,19 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, int, int> forward(
         ready->record(torch_stream);
         g_visibility[a.device.index()] = VisibilityRecord{visible, ready};
     }
-    // a few sizes per power of two: the instance count changes from view to view, and exact sizes would miss torch's block cache
-    const size_t pi_bytes = htgs_forward_instance_bytes(&a.view, htgs_forward_instance_capacity(n_instances));
+    // The instance count changes from view to view; exact sizes would miss torch's block cache on every heavier view, and the
+    // allocator would carve the request out of some other tensor's cached block.  So: two sizes per power of two, and never
+    // smaller than the largest size this device has needed so far (unless that is over four times too much: another scene) -
+    // the same request step after step.
+    static std::atomic<uint64_t> largest_capacity[64];
+    uint64_t capacity = htgs_forward_instance_capacity(n_instances);
+    if (a.device.index() >= 0 && a.device.index() < 64) {
+        std::atomic<uint64_t>& seen = largest_capacity[a.device.index()];
+        uint64_t before = seen.load();
+        while (before < capacity && !seen.compare_exchange_weak(before, capacity)) {}
+        if (before > capacity && before <= 4 * capacity) capacity = before;
+    }
+    const size_t pi_bytes = htgs_forward_instance_bytes(&a.view, capacity);
     Tensor per_instance = bytes_on(a.device, pi_bytes);
     HtgsTrainBlobs blobs{per_primitive.data_ptr(), pp_bytes, per_tile.data_ptr(), pt_bytes, per_instance.data_ptr(), pi_bytes, per_pixel.data_ptr(), px_bytes};
     HtgsFrameInfo info{};

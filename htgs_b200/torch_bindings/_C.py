@@ -157,8 +157,15 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
                 mask |= earlier[0]          # several forwards per step: a row any of them kept can be non-zero
             ready.record(torch.cuda.current_stream(device))
             last_visibility[key] = (mask, ready)
-        # a few sizes per power of two: the instance count changes from view to view, and exact sizes would miss torch's block cache
-        per_instance = torch.empty(lib.htgs_forward_instance_bytes(ctypes.byref(view), lib.htgs_forward_instance_capacity(n_inst.value)), **byte)
+        # The instance count changes from view to view; exact sizes would miss torch's block cache on every heavier view.  Two
+        # sizes per power of two, and never smaller than the largest this device has needed (unless that is over four times too
+        # much: another scene): the same request step after step.
+        capacity = int(lib.htgs_forward_instance_capacity(n_inst.value))
+        largest = max(capacity, _largest_instance_capacity.get(_device_index(device), 0))
+        _largest_instance_capacity[_device_index(device)] = largest
+        if largest <= 4 * capacity:
+            capacity = largest
+        per_instance = torch.empty(lib.htgs_forward_instance_bytes(ctypes.byref(view), capacity), **byte)
         blobs = _native.HtgsTrainBlobs(per_primitive.data_ptr(), per_primitive.numel(), per_tile.data_ptr(), per_tile.numel(),
                                        per_instance.data_ptr(), per_instance.numel(), per_pixel.data_ptr(), per_pixel.numel())
         info = HtgsFrameInfo()
@@ -172,6 +179,7 @@ def forward(positions, scales, rotations, opacities, sh_0, sh_rest, M, VPM, cam_
 # written) here, per device; see torch_bindings.rasterization.track_training_visibility.
 track_visibility = False
 last_visibility: dict = {}
+_largest_instance_capacity: dict = {}      # device index -> largest per-instance capacity a training forward has allocated
 accumulate_visibility = False     # OR the masks of successive forwards until the mask is reset (several forwards per training step)
 
 

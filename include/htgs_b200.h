@@ -181,10 +181,11 @@ typedef struct HtgsTrainBlobs {
 
 int htgs_forward_blob_sizes(const HtgsScene* scene, const HtgsView* view, size_t* per_primitive_bytes, size_t* per_tile_bytes, size_t* per_pixel_bytes);
 size_t htgs_forward_instance_bytes(const HtgsView* view, uint64_t n_instances);
-/* n_instances rounded up to one of eight sizes per power of two (at most 12.5 % more).  The per-instance blob may be larger than
+/* n_instances rounded up to 2^k or 1.5 * 2^k (at most 50 % more).  The per-instance blob may be larger than
  * htgs_forward_instance_bytes(view, n_instances); a caller whose allocator caches freed blocks by size should allocate
- * htgs_forward_instance_bytes(view, htgs_forward_instance_capacity(n_instances)) bytes: the instance count differs from view to
- * view, and an exact-size request misses the cache (a cudaMalloc inside the training step) whenever it grows by a few percent. */
+ * htgs_forward_instance_bytes(view, c) bytes with c = htgs_forward_instance_capacity(n_instances), or the largest c it has used
+ * so far: the instance count differs from view to view, and a request that outgrows the cached block costs a cudaMalloc inside
+ * the training step - and more of them when the allocator then carves the request out of another tensor's cached block. */
 uint64_t htgs_forward_instance_capacity(uint64_t n_instances);
 int htgs_forward_begin(HtgsContext* ctx, const HtgsScene* scene, const HtgsView* view, void* per_primitive, size_t per_primitive_bytes,
                        void* stream, uint32_t* n_instances);
