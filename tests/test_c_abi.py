@@ -85,3 +85,20 @@ def test_extension_modules_expose_the_reference_entry_points():
     assert callable(mod_b.benchmark)
     assert [n for n in dir(mod_b) if not n.startswith("_")] == ["benchmark"]
     assert "arg18: bool) -> tuple[torch.Tensor, torch.Tensor]" in mod_c.render.__doc__      # 17 settings-order arguments + to_chw + use_median_depth
+
+
+def test_instance_capacity_rounds_up_to_two_sizes_per_power_of_two():
+    """`htgs_forward_instance_capacity` (host arithmetic only): never below the request, at most half more, stable under repetition,
+    monotone, and only 2^k or 1.5 * 2^k above the floor of 4096."""
+    import ctypes
+    from htgs_b200 import _native
+    lib = _native.lib()
+    previous = 0
+    for n in [0, 1, 4095, 4096, 4097, 6143, 6144, 6145, 8192, 8193, 1_000_000, 7_872_978, 12_582_912, 12_582_913, 150_000_000, 2**32 - 1]:
+        c = int(lib.htgs_forward_instance_capacity(n))
+        assert c >= max(n, 4096) and c >= previous
+        assert c <= max(4096, n + n // 2 + 1)
+        assert int(lib.htgs_forward_instance_capacity(c)) == c
+        top = c.bit_length() - 1
+        assert c in (1 << top, 3 << (top - 1))
+        previous = c
