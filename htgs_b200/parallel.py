@@ -436,15 +436,18 @@ class CompactExchange:
     A rank's backward pass makes non-zero gradient rows only for the Gaussians its view kept (about a sixth of the scene), and
     48 of a row's 59 floats (SH degree 3) are the 3-vector dL/drgb times functions of the view direction.  So instead of
     all-reducing dense rows (236 bytes per Gaussian of the union of all ranks' views) every rank publishes 64 bytes per
-    Gaussian ITS view kept (`htgs_backward_compact`) and every rank expands all ranks' buffers, in rank order, into the dense
-    sums (`htgs_expand_add_rows`).  Same order on every rank: the sums are bit-identical everywhere, like an all-reduce's.
-    At 8 ranks and configuration 2 a rank reads 7 x 33 MB instead of taking part in the reduction of 383 MB.
+    Gaussian ITS view kept (`htgs_backward_compact`) and every rank forms the dense sums itself from all ranks' buffers, in
+    rank order (`htgs_expand_add_rows` / `htgs_expand_sum_rows`).  Same order on every rank: the sums are bit-identical
+    everywhere, like an all-reduce's.  At 8 ranks and configuration 2 a rank reads 7 x 33 MB instead of taking part in the
+    reduction of 383 MB.
 
     transport = "peer" (default on CUDA with more than one rank): every rank's buffer is plain device memory that the other
-        ranks' GPUs read over NVLink INSIDE the expanding kernel (CUDA IPC mappings made once; `htgs_peer_buffer_*`).  Per step
-        the ranks pass one tiny all-reduce on their streams - the barrier between writing and reading - and nothing else:
-        no sizes to agree on, no host synchronisation, no staging copy.  Two buffers per rank are used in turn, so the next
-        step's barrier also orders a buffer's readers before its next writer.  Costs 2 x 64 bytes x N of device memory.
+        ranks' GPUs read over NVLink with ordinary loads (CUDA IPC mappings made once; `htgs_peer_buffer_*`).  Per step the
+        ranks pass one tiny all-reduce on their streams - the barrier between writing and reading - and nothing else: no
+        sizes to agree on, no host synchronisation.  Two ranks: the expanding kernel reads the peer's rows in place.  More:
+        each rank first pulls the peers' buffers into local memory, starting with a different peer each, and sums all buffers
+        in one pass (see `exchange`).  Two buffers per rank are used in turn, so the next step's barrier also orders a buffer's
+        readers before its next writer.  Costs 2 x 64 bytes x N of device memory, plus (ranks - 1) x 64 x N for the copies.
     transport = "nccl": buffers padded to the largest kept count of any rank, one all-gather, expansion from the gathered
         copy.  `begin` agrees on that count (one tiny all-gather and a host synchronisation on a side stream).
 
